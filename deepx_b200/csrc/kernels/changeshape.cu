@@ -1,0 +1,649 @@
+// dx_transpose / dx_concat / dx_broadcast_to / dx_indexselect / dx_repeat.
+//
+// All five are pure data movement, so the kernels are written over W-byte words
+// (W = 16 when extents and pointers allow, else the widest power of two that
+// divides every contiguous run and aligns every pointer, never below the element
+// size) and are instantiated per word width, not per dtype.  Index arithmetic is
+// done once per word with 32-bit multiply-shift division by launch-time constants
+// carried in the kernel parameters; nothing is uploaded to or allocated on the
+// device per call (the reference uploads three stride vectors per call and, for
+// concat, calls malloc inside the kernel:
+// executor/op-cuda/src/deepx/tensorfunc/changeshape_miaobyte.cu:52-54,127-128).
+#include <algorithm>
+#include <vector>
+
+#include "common.cuh"
+
+namespace dx {
+namespace {
+
+constexpr int CB = 256;
+constexpr int CUNROLL = 4;
+constexpr int MAXD = DX_MAX_DIMS;
+
+template <int W> struct word_of;
+template <> struct word_of<16> { using type = int4; };
+template <> struct word_of<8> { using type = int2; };
+template <> struct word_of<4> { using type = int; };
+template <> struct word_of<2> { using type = short; };
+template <> struct word_of<1> { using type = char; };
+template <int W> using word_t = typename word_of<W>::type;
+
+struct Dims {
+    int n;
+    FastDiv fd[MAXD];     // extents, outermost first
+    int64_t stride[MAXD]; // source stride in BYTES for each extent
+};
+
+__device__ __forceinline__ int64_t unravel_bytes(uint32_t idx, const Dims &g) {
+    int64_t off = 0;
+#pragma unroll 1
+    for (int i = g.n - 1; i > 0; --i) {
+        uint32_t q = fd_div(idx, g.fd[i]);
+        off += int64_t(idx - q * g.fd[i].d) * g.stride[i];
+        idx = q;
+    }
+    if (g.n > 0) off += int64_t(idx) * g.stride[0];
+    return off;
+}
+
+int widest_word(int es, std::initializer_list<int64_t> run_bytes, std::initializer_list<const void *> ptrs) {
+    int w = 16;
+    auto ok = [&](int w_) {
+        for (int64_t b : run_bytes)
+            if (b % w_ != 0) return false;
+        for (const void *p : ptrs)
+            if (!aligned_to(p, w_)) return false;
+        return true;
+    };
+    while (w > es && !ok(w)) w >>= 1;
+    return w;
+}
+
+#define DISPATCH_W(w, ...)                                 \
+    switch (w) {                                           \
+        case 16: { constexpr int W = 16; __VA_ARGS__; } break; \
+        case 8: { constexpr int W = 8; __VA_ARGS__; } break;   \
+        case 4: { constexpr int W = 4; __VA_ARGS__; } break;   \
+        case 2: { constexpr int W = 2; __VA_ARGS__; } break;   \
+        default: { constexpr int W = 1; __VA_ARGS__; } break;  \
+    }
+
+int grid_for(int64_t units, unsigned *grid) {
+    const int64_t per = int64_t(CB) * CUNROLL;
+    int64_t g = (units + per - 1) / per;
+    if (units >= (1ll << 31)) return fail(DX_E_SHAPE, "changeshape: %lld words exceed the 2^31 per-launch limit", (long long)units);
+    *grid = (unsigned)g;
+    return DX_OK;
+}
+
+// ---- generic gather of contiguous runs ------------------------------------------------
+// out word v = (row, pos): row is a row-major index over `rows` whose strides point into
+// the source; pos walks a contiguous run of `run.d` words.  Serves transpose with the
+// innermost axis preserved, and broadcastTo whose innermost axis is not broadcast.
+struct RunGatherParams {
+    Dims rows;
+    FastDiv run;  // words per contiguous run
+    uint32_t units;
+};
+
+template <int W>
+__global__ void __launch_bounds__(CB) run_gather_kernel(const char *__restrict__ in, char *__restrict__ out, RunGatherParams p,
+                                                        bool stream_src) {
+    const uint32_t v0 = blockIdx.x * (CB * CUNROLL) + threadIdx.x;
+    word_t<W> w[CUNROLL];
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k) {
+        const uint32_t v = v0 + k * CB;
+        if (v < p.units) {
+            const uint32_t row = fd_div(v, p.run);
+            const uint32_t pos = v - row * p.run.d;
+            const char *src = in + unravel_bytes(row, p.rows) + int64_t(pos) * W;
+            w[k] = stream_src ? __ldcs(reinterpret_cast<const word_t<W> *>(src))
+                              : *reinterpret_cast<const word_t<W> *>(src);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k) {
+        const uint32_t v = v0 + k * CB;
+        if (v < p.units) __stcs(reinterpret_cast<word_t<W> *>(out + int64_t(v) * W), w[k]);
+    }
+}
+
+// ---- tiled transpose (innermost axis moves) ------------------------------------------------
+// Source axis B is contiguous in the input, destination axis A is contiguous in the
+// output.  A CTA moves a TILE×TILE patch of the (A, B) plane through shared memory so
+// both sides see coalesced rows; the remaining axes are a batch index.
+struct TileParams {
+    Dims batch;            // strides: source bytes
+    Dims batch_out;        // same extents, strides: destination bytes
+    uint32_t na, nb;       // extents of A and B
+    int64_t a_src_stride;  // bytes between consecutive A in the source
+    int64_t b_dst_stride;  // bytes between consecutive B in the destination
+    FastDiv tiles_a, tiles_b;
+};
+
+template <typename E, int TILE>
+__global__ void __launch_bounds__(CB) tile_transpose_kernel(const char *__restrict__ in, char *__restrict__ out, TileParams p) {
+    __shared__ E tile[TILE][TILE + 1];
+    uint32_t b = blockIdx.x;
+    uint32_t q = fd_div(b, p.tiles_b);
+    const uint32_t tb = b - q * p.tiles_b.d;
+    const uint32_t bt = fd_div(q, p.tiles_a);
+    const uint32_t ta = q - bt * p.tiles_a.d;
+    const char *src = in + unravel_bytes(bt, p.batch);
+    char *dst = out + unravel_bytes(bt, p.batch_out);
+    constexpr int NY = CB / TILE;
+    const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
+    // load: x walks B (contiguous in the source), y walks A
+    {
+        const uint32_t ib = tb * TILE + tx;
+#pragma unroll
+        for (int y = ty; y < TILE; y += NY) {
+            const uint32_t ia = ta * TILE + y;
+            if (ia < p.na && ib < p.nb)
+                tile[y][tx] = *reinterpret_cast<const E *>(src + int64_t(ia) * p.a_src_stride + int64_t(ib) * sizeof(E));
+        }
+    }
+    __syncthreads();
+    // store: x walks A (contiguous in the destination), y walks B
+    {
+        const uint32_t ia = ta * TILE + tx;
+#pragma unroll
+        for (int y = ty; y < TILE; y += NY) {
+            const uint32_t ib = tb * TILE + y;
+            if (ia < p.na && ib < p.nb)
+                *reinterpret_cast<E *>(dst + int64_t(ib) * p.b_dst_stride + int64_t(ia) * sizeof(E)) = tile[tx][y];
+        }
+    }
+}
+
+// ---- concat -----------------------------------------------------------------------------------
+constexpr int CONCAT_MAX = 16;
+struct ConcatParams {
+    const char *src[CONCAT_MAX];
+    uint32_t start[CONCAT_MAX + 1];  // first word of each input inside a group row; start[n] = group row words
+    int n;
+    FastDiv group_row;     // words per output row that this launch covers
+    int64_t out_row_bytes; // full output row pitch
+    int64_t out_col_bytes; // where this launch's inputs start inside an output row
+    uint32_t units;        // outer * group_row
+};
+
+template <int W>
+__global__ void __launch_bounds__(CB) concat_kernel(char *__restrict__ out, ConcatParams p) {
+    const uint32_t v0 = blockIdx.x * (CB * CUNROLL) + threadIdx.x;
+    word_t<W> w[CUNROLL];
+    int64_t dst[CUNROLL];
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k) {
+        const uint32_t v = v0 + k * CB;
+        if (v < p.units) {
+            const uint32_t outer = fd_div(v, p.group_row);
+            const uint32_t pos = v - outer * p.group_row.d;
+            int j = 0;
+#pragma unroll 1
+            while (j + 1 < p.n && pos >= p.start[j + 1]) ++j;
+            const uint32_t len = p.start[j + 1] - p.start[j];
+            const char *s = p.src[j] + (int64_t(outer) * len + (pos - p.start[j])) * W;
+            w[k] = __ldcs(reinterpret_cast<const word_t<W> *>(s));
+            dst[k] = int64_t(outer) * p.out_row_bytes + p.out_col_bytes + int64_t(pos) * W;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k)
+        if (v0 + k * CB < p.units) __stcs(reinterpret_cast<word_t<W> *>(out + dst[k]), w[k]);
+}
+
+// ---- broadcast with the innermost axis replicated ---------------------------------------------
+// Every output word of W bytes holds W/sizeof(E) copies of ONE source element.
+struct SplatParams {
+    Dims rows;    // outer output axes; stride 0 where broadcast
+    FastDiv run;  // words per innermost (replicated) run
+    uint32_t units;
+};
+template <int W, typename E>
+__global__ void __launch_bounds__(CB) splat_kernel(const char *__restrict__ in, char *__restrict__ out, SplatParams p) {
+    const uint32_t v0 = blockIdx.x * (CB * CUNROLL) + threadIdx.x;
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k) {
+        const uint32_t v = v0 + k * CB;
+        if (v < p.units) {
+            const uint32_t row = fd_div(v, p.run);
+            const E e = *reinterpret_cast<const E *>(in + unravel_bytes(row, p.rows));
+            Pack<E, W / sizeof(E)> w;
+#pragma unroll
+            for (int i = 0; i < int(W / sizeof(E)); ++i) w.v[i] = e;
+            st_stream<E, W / sizeof(E)>(reinterpret_cast<E *>(out + int64_t(v) * W), w);
+        }
+    }
+}
+
+// ---- indexselect -------------------------------------------------------------------------------
+struct GatherParams {
+    FastDiv run;      // words per gathered slice (post bytes / W)
+    FastDiv nidx;     // number of indices
+    int64_t axis_len; // extent of the gathered axis
+    int64_t slice_bytes;
+    uint32_t units;
+};
+template <int W, typename I>
+__global__ void __launch_bounds__(CB) indexselect_kernel(const char *__restrict__ in, const I *__restrict__ idx,
+                                                         char *__restrict__ out, GatherParams p, int32_t *oob) {
+    const uint32_t v0 = blockIdx.x * (CB * CUNROLL) + threadIdx.x;
+    word_t<W> w[CUNROLL];
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k) {
+        const uint32_t v = v0 + k * CB;
+        if (v < p.units) {
+            const uint32_t row = fd_div(v, p.run);
+            const uint32_t pos = v - row * p.run.d;
+            const uint32_t pre = fd_div(row, p.nidx);
+            const uint32_t qi = row - pre * p.nidx.d;
+            const int64_t ix = static_cast<int64_t>(idx[qi]);
+            if (ix >= 0 && ix < p.axis_len) {
+                const char *s = in + (int64_t(pre) * p.axis_len + ix) * p.slice_bytes + int64_t(pos) * W;
+                w[k] = *reinterpret_cast<const word_t<W> *>(s);
+            } else {
+                w[k] = word_t<W>{};
+                if (oob && pos == 0) atomicOr(oob, 1);
+            }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k) {
+        const uint32_t v = v0 + k * CB;
+        if (v < p.units) __stcs(reinterpret_cast<word_t<W> *>(out + int64_t(v) * W), w[k]);
+    }
+}
+
+// ---- repeat (per element; not on the bandwidth-critical list) -----------------------------------
+struct RepeatParams {
+    Dims outd;                 // output extents; stride = source bytes
+    FastDiv rep[MAXD];         // repeats per axis
+    uint32_t units;
+};
+template <typename E>
+__global__ void __launch_bounds__(CB) repeat_kernel(const char *__restrict__ in, E *__restrict__ out, RepeatParams p) {
+    const uint32_t v = blockIdx.x * CB + threadIdx.x;
+    if (v >= p.units) return;
+    uint32_t idx = v;
+    int64_t off = 0;
+#pragma unroll 1
+    for (int i = p.outd.n - 1; i >= 0; --i) {
+        uint32_t q = (i > 0) ? fd_div(idx, p.outd.fd[i]) : 0;
+        uint32_t c = idx - q * p.outd.fd[i].d;
+        off += int64_t(fd_div(c, p.rep[i])) * p.outd.stride[i];
+        idx = q;
+    }
+    out[v] = *reinterpret_cast<const E *>(in + off);
+}
+
+template <int W, typename E>
+void launch_splat(unsigned grid, cudaStream_t st, const void *a, void *out, const SplatParams &p) {
+    if constexpr (W >= int(sizeof(E))) splat_kernel<W, E><<<grid, CB, 0, st>>>((const char *)a, (char *)out, p);
+}
+
+int check_shape(const char *what, const int64_t *shape, int ndim, int64_t *count) {
+    if (ndim < 0 || ndim > MAXD) return fail(DX_E_SHAPE, "%s: rank %d outside [0, %d]", what, ndim, MAXD);
+    if (ndim > 0 && !shape) return fail(DX_E_ARG, "%s: null shape", what);
+    int64_t n = 1;
+    for (int i = 0; i < ndim; ++i) {
+        if (shape[i] < 0) return fail(DX_E_SHAPE, "%s: negative extent", what);
+        n *= shape[i];
+    }
+    *count = n;
+    return DX_OK;
+}
+
+bool overlaps(const void *a, int64_t abytes, const void *b, int64_t bbytes) {
+    const char *x = (const char *)a, *y = (const char *)b;
+    return x < y + bbytes && y < x + abytes;
+}
+
+}  // namespace
+}  // namespace dx
+
+using namespace dx;
+
+// ==================================================================================================
+extern "C" int dx_transpose(int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *perm, void *out,
+                            void *stream) {
+    cudaStream_t st = as_stream(stream);
+    const int es = dx_dtype_size(dtype);
+    if (es == 0) return fail(DX_E_DTYPE, "transpose: unsupported dtype code %d", dtype);
+    int64_t n;
+    if (int e = check_shape("transpose", shape, ndim, &n)) return e;
+    if (ndim > 0 && !perm) return fail(DX_E_ARG, "transpose: null dim order");
+    bool seen[MAXD] = {false};
+    for (int i = 0; i < ndim; ++i) {
+        if (perm[i] < 0 || perm[i] >= ndim || seen[perm[i]])
+            return fail(DX_E_SHAPE, "transpose: dim order is not a permutation of 0..%d", ndim - 1);
+        seen[perm[i]] = true;
+    }
+    if (n == 0) return DX_OK;
+    if (!a || !out) return fail(DX_E_ARG, "transpose: null pointer");
+    if (overlaps(a, n * es, out, n * es)) return fail(DX_E_ALIAS, "transpose: output overlaps input");
+
+    // source strides (elements) and the output axes as (extent, source stride)
+    int64_t sstride[MAXD];
+    {
+        int64_t s = 1;
+        for (int i = ndim - 1; i >= 0; --i) { sstride[i] = s; s *= shape[i]; }
+    }
+    struct Ax { int64_t size, stride; };
+    std::vector<Ax> ax;  // outermost first, extent-1 axes dropped, source-contiguous neighbours merged
+    for (int i = 0; i < ndim; ++i) {
+        const int64_t sz = shape[perm[i]], sd = sstride[perm[i]];
+        if (sz == 1) continue;
+        if (!ax.empty() && ax.back().stride == sd * sz) { ax.back().size *= sz; ax.back().stride = sd; }
+        else ax.push_back({sz, sd});
+    }
+    if (ax.empty() || (ax.size() == 1)) {  // identity layout
+        cudaError_t e = cudaMemcpyAsync(out, a, size_t(n) * es, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return fail(DX_E_CUDA, "transpose(copy): %s", cudaGetErrorString(e));
+        return DX_OK;
+    }
+    for (auto &x : ax)
+        if (x.size >= (1ll << 31)) return fail(DX_E_SHAPE, "transpose: merged axis too long");
+
+    if (ax.back().stride == 1) {
+        // innermost axis preserved: gather contiguous runs
+        const int64_t run_bytes = ax.back().size * es;
+        const int w = widest_word(es, {run_bytes}, {a, out});
+        RunGatherParams p;
+        p.rows.n = int(ax.size()) - 1;
+        for (int i = 0; i < p.rows.n; ++i) {
+            p.rows.fd[i] = make_fastdiv((uint32_t)ax[i].size);
+            p.rows.stride[i] = ax[i].stride * es;
+        }
+        p.run = make_fastdiv((uint32_t)(run_bytes / w));
+        const int64_t units = n * es / w;
+        unsigned grid;
+        if (int e = grid_for(units, &grid)) return e;
+        p.units = (uint32_t)units;
+        DISPATCH_W(w, run_gather_kernel<W><<<grid, CB, 0, st>>>((const char *)a, (char *)out, p, true));
+        return check_launch("transpose(runs)");
+    }
+
+    // innermost axis moves: tile over A (output-innermost) and B (source-innermost)
+    const int na_i = int(ax.size()) - 1;
+    int nb_i = -1;
+    for (int i = 0; i < int(ax.size()); ++i)
+        if (ax[i].stride == 1) nb_i = i;
+    if (nb_i < 0) return fail(DX_E_SHAPE, "transpose: internal: no unit-stride axis");
+    TileParams p;
+    p.na = (uint32_t)ax[na_i].size;
+    p.nb = (uint32_t)ax[nb_i].size;
+    p.a_src_stride = ax[na_i].stride * es;
+    // destination strides of the merged output axes
+    std::vector<int64_t> dstride(ax.size());
+    {
+        int64_t s = 1;
+        for (int i = int(ax.size()) - 1; i >= 0; --i) { dstride[i] = s; s *= ax[i].size; }
+    }
+    p.b_dst_stride = dstride[nb_i] * es;
+    p.batch.n = p.batch_out.n = 0;
+    int64_t nbatch = 1;
+    for (int i = 0; i < int(ax.size()); ++i) {
+        if (i == na_i || i == nb_i) continue;
+        p.batch.fd[p.batch.n] = p.batch_out.fd[p.batch.n] = make_fastdiv((uint32_t)ax[i].size);
+        p.batch.stride[p.batch.n] = ax[i].stride * es;
+        p.batch_out.stride[p.batch.n] = dstride[i] * es;
+        ++p.batch.n;
+        ++p.batch_out.n;
+        nbatch *= ax[i].size;
+    }
+    const int tile = (es >= 4) ? 32 : 64;
+    const int64_t ta = (p.na + tile - 1) / tile, tb = (p.nb + tile - 1) / tile;
+    p.tiles_a = make_fastdiv((uint32_t)ta);
+    p.tiles_b = make_fastdiv((uint32_t)tb);
+    const int64_t ctas = ta * tb * nbatch;
+    if (ctas >= (1ll << 31)) return fail(DX_E_SHAPE, "transpose: grid too large");
+    switch (es) {
+        case 8: tile_transpose_kernel<uint64_t, 32><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
+        case 4: tile_transpose_kernel<uint32_t, 32><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
+        case 2: tile_transpose_kernel<uint16_t, 64><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
+        default: tile_transpose_kernel<uint8_t, 64><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
+    }
+    return check_launch("transpose(tiles)");
+}
+
+// ==================================================================================================
+extern "C" int dx_concat(int dtype, const void *const *inputs, const int64_t *axis_len, int ninputs,
+                         const int64_t *out_shape, int ndim, int axis, void *out, void *stream) {
+    cudaStream_t st = as_stream(stream);
+    const int es = dx_dtype_size(dtype);
+    if (es == 0) return fail(DX_E_DTYPE, "concat: unsupported dtype code %d", dtype);
+    int64_t n;
+    if (int e = check_shape("concat", out_shape, ndim, &n)) return e;
+    if (ninputs < 1 || !inputs || !axis_len) return fail(DX_E_ARG, "concat: no inputs");
+    if (axis < 0 || axis >= ndim) return fail(DX_E_SHAPE, "concat: axis %d out of range for rank %d", axis, ndim);
+    int64_t total = 0;
+    for (int i = 0; i < ninputs; ++i) {
+        if (axis_len[i] < 0) return fail(DX_E_SHAPE, "concat: negative extent");
+        total += axis_len[i];
+    }
+    if (total != out_shape[axis])
+        return fail(DX_E_SHAPE, "concat: inputs cover %lld along axis %d, output has %lld", (long long)total, axis,
+                    (long long)out_shape[axis]);
+    if (n == 0) return DX_OK;
+    if (!out) return fail(DX_E_ARG, "concat: null output");
+    int64_t outer = 1, inner = 1;
+    for (int i = 0; i < axis; ++i) outer *= out_shape[i];
+    for (int i = axis + 1; i < ndim; ++i) inner *= out_shape[i];
+    // word width: must divide every input's row and align every pointer
+    int w = 16;
+    auto fits = [&](int w_) {
+        if (!aligned_to(out, w_)) return false;
+        for (int i = 0; i < ninputs; ++i) {
+            if (axis_len[i] == 0) continue;
+            if ((axis_len[i] * inner * es) % w_ != 0) return false;
+            if (!aligned_to(inputs[i], w_)) return false;
+        }
+        return true;
+    };
+    while (w > es && !fits(w)) w >>= 1;
+    for (int i = 0; i < ninputs; ++i) {
+        if (axis_len[i] == 0) continue;
+        if (!inputs[i]) return fail(DX_E_ARG, "concat: inputs[%d] is null", i);
+        if (overlaps(inputs[i], outer * axis_len[i] * inner * es, out, n * es))
+            return fail(DX_E_ALIAS, "concat: output overlaps inputs[%d]", i);
+    }
+    const int64_t out_row_bytes = total * inner * es;
+    int64_t col = 0;  // byte offset inside an output row
+    int i = 0;
+    while (i < ninputs) {
+        ConcatParams p;
+        p.n = 0;
+        int64_t words = 0;
+        const int64_t col0 = col;
+        while (i < ninputs && p.n < CONCAT_MAX) {
+            if (axis_len[i] > 0) {
+                p.src[p.n] = (const char *)inputs[i];
+                p.start[p.n] = (uint32_t)words;
+                const int64_t row_words = axis_len[i] * inner * es / w;
+                words += row_words;
+                col += row_words * w;
+                ++p.n;
+            }
+            ++i;
+        }
+        if (p.n == 0) break;
+        if (words >= (1ll << 31)) return fail(DX_E_SHAPE, "concat: row too long");
+        p.start[p.n] = (uint32_t)words;
+        for (int k = p.n; k < CONCAT_MAX; ++k) p.src[k] = nullptr;
+        p.group_row = make_fastdiv((uint32_t)words);
+        p.out_row_bytes = out_row_bytes;
+        p.out_col_bytes = col0;
+        const int64_t units = outer * words;
+        unsigned grid;
+        if (int e = grid_for(units, &grid)) return e;
+        p.units = (uint32_t)units;
+        DISPATCH_W(w, concat_kernel<W><<<grid, CB, 0, st>>>((char *)out, p));
+        if (int e = check_launch("concat")) return e;
+    }
+    return DX_OK;
+}
+
+// ==================================================================================================
+extern "C" int dx_broadcast_to(int dtype, const void *a, const int64_t *a_shape, int a_ndim, const int64_t *out_shape,
+                               int out_ndim, void *out, void *stream) {
+    cudaStream_t st = as_stream(stream);
+    const int es = dx_dtype_size(dtype);
+    if (es == 0) return fail(DX_E_DTYPE, "broadcastTo: unsupported dtype code %d", dtype);
+    int64_t na, n;
+    if (int e = check_shape("broadcastTo", a_shape, a_ndim, &na)) return e;
+    if (int e = check_shape("broadcastTo", out_shape, out_ndim, &n)) return e;
+    if (a_ndim > out_ndim) return fail(DX_E_SHAPE, "broadcastTo: Shapes are not broadcastable for operation");
+    const int lead = out_ndim - a_ndim;
+    for (int i = 0; i < a_ndim; ++i)
+        if (a_shape[i] != out_shape[lead + i] && a_shape[i] != 1)
+            return fail(DX_E_SHAPE, "broadcastTo: Shapes are not broadcastable for operation");
+    if (n == 0) return DX_OK;
+    if (!a || !out) return fail(DX_E_ARG, "broadcastTo: null pointer");
+    if (overlaps(a, na * es, out, n * es)) return fail(DX_E_ALIAS, "broadcastTo: output overlaps input");
+    if (na == n) {
+        cudaError_t e = cudaMemcpyAsync(out, a, size_t(n) * es, cudaMemcpyDeviceToDevice, st);
+        if (e != cudaSuccess) return fail(DX_E_CUDA, "broadcastTo(copy): %s", cudaGetErrorString(e));
+        return DX_OK;
+    }
+    // output axes as (extent, source stride in elements; 0 = broadcast); merge neighbours of one kind
+    struct Ax { int64_t size, stride; bool bc; };
+    std::vector<Ax> ax;
+    {
+        int64_t sstride[MAXD];
+        int64_t s = 1;
+        for (int i = a_ndim - 1; i >= 0; --i) { sstride[i] = s; s *= a_shape[i]; }
+        for (int i = 0; i < out_ndim; ++i) {
+            const int64_t sz = out_shape[i];
+            if (sz == 1) continue;
+            const bool bc = (i < lead) || a_shape[i - lead] == 1;
+            const int64_t sd = bc ? 0 : sstride[i - lead];
+            if (!ax.empty() && ax.back().bc == bc && (bc || ax.back().stride == sd * sz)) {
+                ax.back().size *= sz;
+                ax.back().stride = sd;
+            } else ax.push_back({sz, sd, bc});
+        }
+    }
+    for (auto &x : ax)
+        if (x.size >= (1ll << 31)) return fail(DX_E_SHAPE, "broadcastTo: merged axis too long");
+    const int64_t run_bytes = ax.back().size * es;
+    if (!ax.back().bc) {
+        const int w = widest_word(es, {run_bytes}, {a, out});
+        RunGatherParams p;
+        p.rows.n = int(ax.size()) - 1;
+        for (int i = 0; i < p.rows.n; ++i) {
+            p.rows.fd[i] = make_fastdiv((uint32_t)ax[i].size);
+            p.rows.stride[i] = ax[i].stride * es;
+        }
+        p.run = make_fastdiv((uint32_t)(run_bytes / w));
+        const int64_t units = n * es / w;
+        unsigned grid;
+        if (int e = grid_for(units, &grid)) return e;
+        p.units = (uint32_t)units;
+        // the source is re-read many times: keep it cached
+        DISPATCH_W(w, run_gather_kernel<W><<<grid, CB, 0, st>>>((const char *)a, (char *)out, p, false));
+        return check_launch("broadcastTo(runs)");
+    }
+    // innermost axis replicated
+    const int w = widest_word(es, {run_bytes}, {out});
+    SplatParams p;
+    p.rows.n = int(ax.size()) - 1;
+    for (int i = 0; i < p.rows.n; ++i) {
+        p.rows.fd[i] = make_fastdiv((uint32_t)ax[i].size);
+        p.rows.stride[i] = ax[i].stride * es;
+    }
+    p.run = make_fastdiv((uint32_t)(run_bytes / w));
+    const int64_t units = n * es / w;
+    unsigned grid;
+    if (int e = grid_for(units, &grid)) return e;
+    p.units = (uint32_t)units;
+#define SPLAT(E) DISPATCH_W(w, launch_splat<W, E>(grid, st, a, out, p))
+    switch (es) {
+        case 8: SPLAT(uint64_t); break;
+        case 4: SPLAT(uint32_t); break;
+        case 2: SPLAT(uint16_t); break;
+        default: SPLAT(uint8_t); break;
+    }
+#undef SPLAT
+    return check_launch("broadcastTo(splat)");
+}
+
+// ==================================================================================================
+extern "C" int dx_indexselect(int dtype, const void *a, const int64_t *a_shape, int a_ndim, int idx_dtype,
+                              const void *idx, const int64_t *idx_shape, int idx_ndim, int axis, void *out,
+                              int32_t *oob_flag, void *stream) {
+    cudaStream_t st = as_stream(stream);
+    const int es = dx_dtype_size(dtype);
+    if (es == 0) return fail(DX_E_DTYPE, "indexselect: unsupported dtype code %d", dtype);
+    if (idx_dtype != DX_I32 && idx_dtype != DX_I64)
+        return fail(DX_E_DTYPE, "indexselect: index dtype must be int64 or int32 (dtype code %d)", idx_dtype);
+    int64_t na, ni;
+    if (int e = check_shape("indexselect", a_shape, a_ndim, &na)) return e;
+    if (int e = check_shape("indexselect", idx_shape, idx_ndim, &ni)) return e;
+    if (axis < 0) axis += a_ndim;
+    if (axis < 0 || axis >= a_ndim) return fail(DX_E_SHAPE, "indexselect: Axis is out of bounds");
+    int64_t pre = 1, post = 1;
+    for (int i = 0; i < axis; ++i) pre *= a_shape[i];
+    for (int i = axis + 1; i < a_ndim; ++i) post *= a_shape[i];
+    const int64_t n = pre * ni * post;
+    if (n == 0) return DX_OK;
+    if (!a || !idx || !out) return fail(DX_E_ARG, "indexselect: null pointer");
+    if (overlaps(a, na * es, out, n * es)) return fail(DX_E_ALIAS, "indexselect: output overlaps input");
+    const int64_t slice_bytes = post * es;
+    const int w = widest_word(es, {slice_bytes}, {a, out});
+    if (ni >= (1ll << 31) || slice_bytes / w >= (1ll << 31)) return fail(DX_E_SHAPE, "indexselect: extent too large");
+    GatherParams p;
+    p.run = make_fastdiv((uint32_t)(slice_bytes / w));
+    p.nidx = make_fastdiv((uint32_t)ni);
+    p.axis_len = a_shape[axis];
+    p.slice_bytes = slice_bytes;
+    const int64_t units = n * es / w;
+    unsigned grid;
+    if (int e = grid_for(units, &grid)) return e;
+    p.units = (uint32_t)units;
+    if (idx_dtype == DX_I32) {
+        DISPATCH_W(w, indexselect_kernel<W, int32_t><<<grid, CB, 0, st>>>((const char *)a, (const int32_t *)idx, (char *)out, p, oob_flag));
+    } else {
+        DISPATCH_W(w, indexselect_kernel<W, int64_t><<<grid, CB, 0, st>>>((const char *)a, (const int64_t *)idx, (char *)out, p, oob_flag));
+    }
+    return check_launch("indexselect");
+}
+
+// ==================================================================================================
+extern "C" int dx_repeat(int dtype, const void *a, const int64_t *a_shape, int ndim, const int64_t *repeats, void *out,
+                         void *stream) {
+    cudaStream_t st = as_stream(stream);
+    const int es = dx_dtype_size(dtype);
+    if (es == 0) return fail(DX_E_DTYPE, "repeat: unsupported dtype code %d", dtype);
+    int64_t na;
+    if (int e = check_shape("repeat", a_shape, ndim, &na)) return e;
+    if (ndim > 0 && !repeats) return fail(DX_E_ARG, "repeat: null repeats");
+    RepeatParams p;
+    p.outd.n = ndim;
+    int64_t n = 1, s = 1;
+    for (int i = ndim - 1; i >= 0; --i) {
+        if (repeats[i] < 1) return fail(DX_E_SHAPE, "repeat: repeats must be >= 1");
+        const int64_t o = a_shape[i] * repeats[i];
+        if (o >= (1ll << 31) || repeats[i] >= (1ll << 31)) return fail(DX_E_SHAPE, "repeat: extent too large");
+        p.outd.fd[i] = make_fastdiv((uint32_t)std::max<int64_t>(o, 1));
+        p.rep[i] = make_fastdiv((uint32_t)repeats[i]);
+        p.outd.stride[i] = s * es;
+        s *= a_shape[i];
+        n *= o;
+    }
+    if (n == 0) return DX_OK;
+    if (!a || !out) return fail(DX_E_ARG, "repeat: null pointer");
+    if (n >= (1ll << 31)) return fail(DX_E_SHAPE, "repeat: output too large");
+    if (overlaps(a, na * es, out, n * es)) return fail(DX_E_ALIAS, "repeat: output overlaps input");
+    p.units = (uint32_t)n;
+    const unsigned grid = (unsigned)((n + CB - 1) / CB);
+    switch (es) {
+        case 8: repeat_kernel<uint64_t><<<grid, CB, 0, st>>>((const char *)a, (uint64_t *)out, p); break;
+        case 4: repeat_kernel<uint32_t><<<grid, CB, 0, st>>>((const char *)a, (uint32_t *)out, p); break;
+        case 2: repeat_kernel<uint16_t><<<grid, CB, 0, st>>>((const char *)a, (uint16_t *)out, p); break;
+        default: repeat_kernel<uint8_t><<<grid, CB, 0, st>>>((const char *)a, (uint8_t *)out, p); break;
+    }
+    return check_launch("repeat");
+}

@@ -1,0 +1,162 @@
+// Elementwise functors.  The arithmetic restates the scalar lambdas of the CPU
+// executor (executor/op-ompsimd/src/deepx/tensorfunc/elementwise_miaobyte.hpp);
+// 16-bit floats are widened to fp32, computed, and rounded once (RNE).
+#pragma once
+#include "common.cuh"
+
+namespace dx {
+
+// ---- binary -------------------------------------------------------------------
+template <int OP, typename T> struct BinaryFn {
+    __device__ __forceinline__ T operator()(T a, T b) const {
+        using C = compute_t<T>;
+        C x = to_compute(a), y = to_compute(b), r;
+        if constexpr (OP == DX_ADD) {
+            if constexpr (std::is_integral<T>::value && std::is_signed<T>::value) {
+                using U = typename std::make_unsigned<T>::type;  // wraparound, not UB
+                r = static_cast<T>(static_cast<U>(x) + static_cast<U>(y));
+            } else r = x + y;  // elementwise_miaobyte.hpp:123
+        } else if constexpr (OP == DX_SUB) {
+            if constexpr (std::is_integral<T>::value && std::is_signed<T>::value) {
+                using U = typename std::make_unsigned<T>::type;
+                r = static_cast<T>(static_cast<U>(x) - static_cast<U>(y));
+            } else r = x - y;  // :164
+        } else if constexpr (OP == DX_MUL) {
+            if constexpr (std::is_integral<T>::value && std::is_signed<T>::value) {
+                using U = typename std::make_unsigned<T>::type;
+                r = static_cast<T>(static_cast<U>(static_cast<U>(x) * static_cast<U>(y)));
+            } else r = x * y;  // :226
+        } else if constexpr (OP == DX_DIV) {
+            r = x / y;  // :267 (integer: truncating; divisor 0 is undefined in the reference)
+        } else if constexpr (OP == DX_MAX) {
+            r = (x < y) ? y : x;  // std::max, :614
+        } else if constexpr (OP == DX_MIN) {
+            r = (y < x) ? y : x;  // std::min, :698
+        } else {
+            static_assert(OP == DX_POW, "binary op");
+            if constexpr (std::is_same<C, double>::value) r = pow(x, y);  // std::pow, :441
+            else r = powf(x, y);
+        }
+        return from_compute<T>(r);
+    }
+};
+
+// ---- tensor ∘ scalar -------------------------------------------------------------
+template <int OP, typename T> struct ScalarFn {
+    T s;
+    __device__ __forceinline__ T operator()(T a) const {
+        if constexpr (OP == DX_ADDS) return BinaryFn<DX_ADD, T>()(a, s);
+        else if constexpr (OP == DX_SUBS) return BinaryFn<DX_SUB, T>()(a, s);
+        else if constexpr (OP == DX_RSUBS) return BinaryFn<DX_SUB, T>()(s, a);  // :204
+        else if constexpr (OP == DX_MULS) return BinaryFn<DX_MUL, T>()(a, s);
+        else if constexpr (OP == DX_DIVS) return BinaryFn<DX_DIV, T>()(a, s);
+        else if constexpr (OP == DX_RDIVS) return BinaryFn<DX_DIV, T>()(s, a);  // :307
+        else if constexpr (OP == DX_MAXS) return BinaryFn<DX_MAX, T>()(a, s);
+        else if constexpr (OP == DX_MINS) return BinaryFn<DX_MIN, T>()(a, s);
+        else if constexpr (OP == DX_POWS) return BinaryFn<DX_POW, T>()(a, s);  // :462
+        else {
+            static_assert(OP == DX_RPOWS, "scalar op");
+            return BinaryFn<DX_POW, T>()(s, a);  // :482
+        }
+    }
+};
+
+// ---- unary ---------------------------------------------------------------------
+template <int OP, typename T> struct UnaryFn {
+    __device__ __forceinline__ T operator()(T a) const {
+        if constexpr (OP == DX_INVERT) {
+            if constexpr (std::is_same<T, uint8_t>::value) return static_cast<uint8_t>(!a);  // bool, :353
+            else return static_cast<T>(~a);                                                  // :332
+        } else {
+            using C = compute_t<T>;
+            C x = to_compute(a), r;
+            if constexpr (std::is_same<C, double>::value) {
+                if constexpr (OP == DX_SQRT) r = sqrt(x);
+                else if constexpr (OP == DX_LOG) r = log(x);
+                else if constexpr (OP == DX_EXP) r = exp(x);
+                else if constexpr (OP == DX_SIN) r = sin(x);
+                else if constexpr (OP == DX_COS) r = cos(x);
+                else r = tan(x);
+            } else {
+                if constexpr (OP == DX_SQRT) r = sqrtf(x);  // IEEE (-prec-sqrt=true)
+                else if constexpr (OP == DX_LOG) r = logf(x);
+                else if constexpr (OP == DX_EXP) r = expf(x);
+                else if constexpr (OP == DX_SIN) r = sinf(x);
+                else if constexpr (OP == DX_COS) r = cosf(x);
+                else r = tanf(x);
+            }
+            return from_compute<T>(r);
+        }
+    }
+};
+
+// ---- compare → 0/1 byte ------------------------------------------------------------
+// EQ/NE with epsilon follow elementwise_miaobyte.hpp:778-845: `std::abs(a-b) <= epsilon`
+// evaluated in the promoted type of (T, float).
+template <typename T> __device__ __forceinline__ bool within_eps(T a, T b, float eps) {
+    if constexpr (std::is_same<T, double>::value) return fabs(a - b) <= static_cast<double>(eps);
+    else if constexpr (is_float_v<T>) return fabsf(to_compute(a) - to_compute(b)) <= eps;
+    else if constexpr (std::is_same<T, int64_t>::value) {
+        int64_t d = a - b;
+        return static_cast<float>(d < 0 ? -d : d) <= eps;
+    } else {
+        int d = static_cast<int>(a) - static_cast<int>(b);
+        return static_cast<float>(d < 0 ? -d : d) <= eps;
+    }
+}
+
+template <int OP, typename T> struct CompareFn {
+    float eps;
+    __device__ __forceinline__ uint8_t operator()(T a, T b) const {
+        using C = compute_t<T>;
+        if constexpr (OP == DX_EQ) {
+            if (eps == 0.f) return to_compute(a) == to_compute(b);
+            return within_eps<T>(a, b, eps);
+        } else if constexpr (OP == DX_NE) {
+            if (eps == 0.f) return to_compute(a) != to_compute(b);
+            return !within_eps<T>(a, b, eps);
+        } else if constexpr (OP == DX_LT) {
+            return C(to_compute(a)) < C(to_compute(b));  // :900
+        } else {
+            static_assert(OP == DX_GT, "compare op");
+            return C(to_compute(a)) > C(to_compute(b));  // :944
+        }
+    }
+};
+
+template <int OP, typename T> struct CompareScalarFn {
+    T s;
+    float eps;
+    __device__ __forceinline__ uint8_t operator()(T a) const { return CompareFn<OP, T>{eps}(a, s); }
+};
+
+// ---- cast (static_cast semantics, elementwise_miaobyte.hpp:103-112) ------------------
+template <typename S, typename D> struct CastFn {
+    __device__ __forceinline__ D operator()(S a) const {
+        if constexpr (std::is_same<S, D>::value) return a;
+        else if constexpr (std::is_same<D, uint8_t>::value) {  // bool
+            if constexpr (is_float_v<S>) return to_compute(a) != compute_t<S>(0);
+            else return a != 0;
+        } else if constexpr (is_float_v<D>) {
+            if constexpr (std::is_same<D, double>::value) return static_cast<double>(to_compute(a));
+            else if constexpr (std::is_same<D, float>::value) return static_cast<float>(to_compute(a));
+            else if constexpr (std::is_same<S, double>::value) {
+                // double → f16/bf16 in one rounding
+                if constexpr (std::is_same<D, f16>::value) return __double2half(a);
+                else return __double2bfloat16(a);
+            } else if constexpr (std::is_same<S, int64_t>::value) {
+                if constexpr (std::is_same<D, f16>::value) return __ll2half_rn(a);
+                else return __ll2bfloat16_rn(a);
+            } else if constexpr (std::is_same<S, int32_t>::value) {
+                if constexpr (std::is_same<D, f16>::value) return __int2half_rn(a);
+                else return __int2bfloat16_rn(a);
+            } else return from_compute<D>(static_cast<float>(to_compute(a)));
+        } else {
+            // → integer: truncation toward zero; out-of-range is undefined in C++ (saturates here)
+            if constexpr (is_float_v<S>) return static_cast<D>(to_compute(a));
+            else return static_cast<D>(a);
+        }
+    }
+};
+
+}  // namespace dx

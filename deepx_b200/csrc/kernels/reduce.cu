@@ -1,0 +1,628 @@
+// dx_reduce: sum / prod / max / min over an arbitrary subset of axes.
+//
+// Host side: size-1 axes are dropped and neighbouring axes of the same class
+// (kept / reduced) are merged, which leaves an alternating list of groups.  Two
+// device strategies cover every case:
+//
+//   rows  (innermost group is REDUCED, contiguous run of L elements per output):
+//         a team of threads (1..32 lanes of a warp, or a whole 256-thread CTA,
+//         or several CTAs when there are few outputs) streams the run(s) of one
+//         output with 16-byte loads, then combines with warp shuffles and shared
+//         memory.
+//   cols  (innermost group is KEPT, Kin contiguous outputs): a CTA owns a strip
+//         of 32 column vectors and walks the reduced rows 8 at a time (coalesced
+//         512-byte row segments), combines the 8 row lanes through shared memory.
+//
+// When one launch cannot fill the machine (few outputs), the reduced range is
+// split over several CTAs which write partials to caller-provided scratch, and a
+// small second kernel combines them in a fixed order.  No atomics anywhere, so a
+// given (shape, dims, device) always produces the same bits.
+//
+// The reference does this with one thread per INPUT element and a global atomic
+// per element (executor/op-cuda/src/deepx/tensorfunc/reduce_miaobyte.cu:22-48),
+// and its max/min are racy read-modify-writes (:230-256, :339-365).
+#include <algorithm>
+#include <limits>
+#include <vector>
+
+#include "common.cuh"
+
+namespace dx {
+namespace {
+
+constexpr int RB = 256;      // threads per CTA
+constexpr int RUNROLL = 4;   // independent 16-byte loads per thread per step
+constexpr int MAXG = 6;      // ≤ 12 axes → ≤ 6 groups of each class
+
+// ---- accumulation types and combine rules ----------------------------------------
+template <typename T> struct acc_of { using type = T; };
+template <> struct acc_of<f16> { using type = float; };
+template <> struct acc_of<bf16> { using type = float; };
+template <> struct acc_of<int16_t> { using type = int32_t; };
+template <> struct acc_of<int8_t> { using type = int32_t; };
+template <typename T> using acc_t = typename acc_of<T>::type;
+
+template <typename T> __host__ __device__ __forceinline__ acc_t<T> widen(T v) {
+    if constexpr (std::is_same<T, f16>::value) return __half2float(v);
+    else if constexpr (std::is_same<T, bf16>::value) return __bfloat162float(v);
+    else return static_cast<acc_t<T>>(v);
+}
+template <typename T> __host__ __device__ __forceinline__ T narrow(acc_t<T> v) {
+    if constexpr (std::is_same<T, f16>::value) return __float2half_rn(v);
+    else if constexpr (std::is_same<T, bf16>::value) return __float2bfloat16_rn(v);
+    else return static_cast<T>(v);  // int16/int8: keeps the low bits = wraparound sum
+}
+
+template <typename T> __host__ __device__ __forceinline__ T lowest_of() {
+    if constexpr (std::is_same<T, f16>::value) return __ushort_as_half((unsigned short)0xFBFF);       // -65504
+    else if constexpr (std::is_same<T, bf16>::value) return __ushort_as_bfloat16((unsigned short)0xFF7F);  // -3.39e38
+    else if constexpr (std::is_same<T, float>::value) return -3.402823466e+38f;
+    else if constexpr (std::is_same<T, double>::value) return -1.7976931348623157e+308;
+    else if constexpr (std::is_same<T, int64_t>::value) return (int64_t)0x8000000000000000ull;
+    else if constexpr (std::is_same<T, int32_t>::value) return (int32_t)0x80000000u;
+    else if constexpr (std::is_same<T, int16_t>::value) return (int16_t)-32768;
+    else return (int8_t)-128;
+}
+template <typename T> __host__ __device__ __forceinline__ T highest_of() {
+    if constexpr (std::is_same<T, f16>::value) return __ushort_as_half((unsigned short)0x7BFF);
+    else if constexpr (std::is_same<T, bf16>::value) return __ushort_as_bfloat16((unsigned short)0x7F7F);
+    else if constexpr (std::is_same<T, float>::value) return 3.402823466e+38f;
+    else if constexpr (std::is_same<T, double>::value) return 1.7976931348623157e+308;
+    else if constexpr (std::is_same<T, int64_t>::value) return (int64_t)0x7fffffffffffffffll;
+    else if constexpr (std::is_same<T, int32_t>::value) return (int32_t)0x7fffffff;
+    else if constexpr (std::is_same<T, int16_t>::value) return (int16_t)32767;
+    else return (int8_t)127;
+}
+
+// Identity = the value the reference pre-fills the output with
+// (reduce_miaobyte.hpp:22 sum 0, :36 prod 1, :49 max lowest(), :63 min max()).
+template <int OP, typename T> __host__ __device__ __forceinline__ acc_t<T> identity() {
+    if constexpr (OP == DX_SUM) return acc_t<T>(0);
+    else if constexpr (OP == DX_PROD) return acc_t<T>(1);
+    else if constexpr (OP == DX_RMAX) return widen<T>(lowest_of<T>());
+    else return widen<T>(highest_of<T>());
+}
+
+template <int OP, typename A> __device__ __forceinline__ A combine(A a, A b) {
+    if constexpr (OP == DX_SUM) {
+        if constexpr (std::is_integral<A>::value) {
+            using U = typename std::make_unsigned<A>::type;
+            return static_cast<A>(static_cast<U>(a) + static_cast<U>(b));
+        } else return a + b;
+    } else if constexpr (OP == DX_PROD) {
+        if constexpr (std::is_integral<A>::value) {
+            using U = typename std::make_unsigned<A>::type;
+            return static_cast<A>(static_cast<U>(a) * static_cast<U>(b));
+        } else return a * b;
+    } else if constexpr (OP == DX_RMAX) return (a < b) ? b : a;  // std::max
+    else return (b < a) ? b : a;                                 // std::min
+}
+
+template <typename A> __device__ __forceinline__ A shfl_down(A v, int delta, int width) {
+    if constexpr (sizeof(A) == 8) {
+        long long t = __shfl_down_sync(0xffffffffu, *reinterpret_cast<long long *>(&v), delta, width);
+        return *reinterpret_cast<A *>(&t);
+    } else {
+        int t = __shfl_down_sync(0xffffffffu, *reinterpret_cast<int *>(&v), delta, width);
+        return *reinterpret_cast<A *>(&t);
+    }
+}
+
+// ---- parameter blocks (by value in the launch, no device-side tables) --------------
+struct Groups {
+    int n;
+    FastDiv fd[MAXG];       // group extents, outermost first
+    int64_t stride[MAXG];   // input stride of each group, in elements
+};
+
+__device__ __forceinline__ int64_t unravel(uint32_t idx, const Groups &g) {
+    // idx is a row-major index over the groups; returns Σ coord·stride.
+    int64_t off = 0;
+#pragma unroll 1
+    for (int i = g.n - 1; i > 0; --i) {
+        uint32_t q = fd_div(idx, g.fd[i]);
+        off += int64_t(idx - q * g.fd[i].d) * g.stride[i];
+        idx = q;
+    }
+    if (g.n > 0) off += int64_t(idx) * g.stride[0];
+    return off;
+}
+
+struct RowsParams {
+    Groups kept;      // all kept groups → base offset of an output's data
+    Groups rout;      // reduced groups other than the innermost run
+    FastDiv lv;       // vectors per innermost run (L / VEC)
+    uint32_t units;   // vectors per output = Π rout · lv
+    uint32_t split;   // CTAs per output (block kernel only)
+    uint32_t chunk;   // vectors per CTA
+    uint32_t nout;    // outputs
+    int team;         // lanes per output (team kernel only)
+};
+
+struct ColsParams {
+    Groups kouter;    // kept groups other than the innermost run
+    Groups red;       // all reduced groups
+    FastDiv ctiles;   // column tiles per kept-outer index
+    FastDiv kouter_n; // number of kept-outer indices
+    uint32_t kv;      // column vectors in the innermost run (Kin / VEC)
+    int64_t kin;      // Kin
+    uint32_t rows;    // Π red
+    uint32_t split, chunk;
+    int64_t nout;     // Π kept
+    int tx;           // threads across columns (power of two ≤ 32); RB/tx rows in flight
+};
+
+// ---- rows: one CTA (or 1/split of the work) per output ----------------------------------
+template <int OP, typename T, int VEC>
+__global__ void __launch_bounds__(RB) rows_block_kernel(const T *__restrict__ in, T *__restrict__ out,
+                                                        acc_t<T> *__restrict__ partial, RowsParams p) {
+    using A = acc_t<T>;
+    const uint32_t o = blockIdx.x / p.split;
+    const uint32_t c = blockIdx.x - o * p.split;
+    const T *base = in + unravel(o, p.kept);
+    const uint32_t u0 = c * p.chunk;
+    const uint32_t u1 = min(p.units, u0 + p.chunk);
+
+    A acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = identity<OP, T>();
+
+    auto addr = [&](uint32_t u) -> const T * {
+        if (p.rout.n == 0) return base + int64_t(u) * VEC;
+        uint32_t seg = fd_div(u, p.lv);
+        uint32_t pos = u - seg * p.lv.d;
+        return base + unravel(seg, p.rout) + int64_t(pos) * VEC;
+    };
+
+    uint32_t u = u0 + threadIdx.x;
+    // u0 + chunk ≤ 2^31 is guaranteed by the host, so u + k·RB cannot wrap.
+    for (; u + (RUNROLL - 1) * RB < u1; u += RUNROLL * RB) {
+        Pack<T, VEC> v[RUNROLL];
+#pragma unroll
+        for (int k = 0; k < RUNROLL; ++k) v[k] = ld_stream<T, VEC>(addr(u + k * RB));
+#pragma unroll
+        for (int k = 0; k < RUNROLL; ++k)
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v[k].v[i]));
+    }
+    for (; u < u1; u += RB) {
+        Pack<T, VEC> v = ld_stream<T, VEC>(addr(u));
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v.v[i]));
+    }
+    A r = acc[0];
+#pragma unroll
+    for (int i = 1; i < VEC; ++i) r = combine<OP>(r, acc[i]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) r = combine<OP>(r, shfl_down(r, d, 32));
+    __shared__ A warp_part[RB / 32];
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = r;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        r = warp_part[0];
+#pragma unroll
+        for (int w = 1; w < RB / 32; ++w) r = combine<OP>(r, warp_part[w]);
+        if (p.split == 1) out[o] = narrow<T>(r);
+        else partial[size_t(o) * p.split + c] = r;
+    }
+}
+
+// ---- rows: a team of 1..32 lanes per output -------------------------------------------------
+template <int OP, typename T, int VEC>
+__global__ void __launch_bounds__(RB) rows_team_kernel(const T *__restrict__ in, T *__restrict__ out, RowsParams p) {
+    using A = acc_t<T>;
+    const int team = p.team;
+    const uint32_t teams_per_cta = RB / team;
+    const uint64_t o64 = uint64_t(blockIdx.x) * teams_per_cta + threadIdx.x / team;
+    const int lane = threadIdx.x & (team - 1);
+    const bool live = o64 < p.nout;
+    const uint32_t o = live ? uint32_t(o64) : 0;
+    const T *base = in + unravel(o, p.kept);
+
+    A acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = identity<OP, T>();
+    auto addr = [&](uint32_t u) -> const T * {
+        if (p.rout.n == 0) return base + int64_t(u) * VEC;
+        uint32_t seg = fd_div(u, p.lv);
+        uint32_t pos = u - seg * p.lv.d;
+        return base + unravel(seg, p.rout) + int64_t(pos) * VEC;
+    };
+    if (live) {
+        uint32_t u = lane;
+        for (; u + (RUNROLL - 1) * team < p.units; u += RUNROLL * team) {
+            Pack<T, VEC> v[RUNROLL];
+#pragma unroll
+            for (int k = 0; k < RUNROLL; ++k) v[k] = ld_stream<T, VEC>(addr(u + k * team));
+#pragma unroll
+            for (int k = 0; k < RUNROLL; ++k)
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v[k].v[i]));
+        }
+        for (; u < p.units; u += team) {
+            Pack<T, VEC> v = ld_stream<T, VEC>(addr(u));
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v.v[i]));
+        }
+    }
+    A r = acc[0];
+#pragma unroll
+    for (int i = 1; i < VEC; ++i) r = combine<OP>(r, acc[i]);
+    for (int d = team >> 1; d > 0; d >>= 1) r = combine<OP>(r, shfl_down(r, d, team));
+    if (live && lane == 0) out[o] = narrow<T>(r);
+}
+
+// partial[nout][split] → out[nout]; one warp per output, fixed order.
+template <int OP, typename T>
+__global__ void __launch_bounds__(RB) rows_finish_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out,
+                                                         uint32_t nout, uint32_t split) {
+    using A = acc_t<T>;
+    const uint32_t o = blockIdx.x * (RB / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (o >= nout) return;  // whole warp exits together
+    A r = identity<OP, T>();
+    for (uint32_t c = lane; c < split; c += 32) r = combine<OP>(r, partial[size_t(o) * split + c]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) r = combine<OP>(r, shfl_down(r, d, 32));
+    if (lane == 0) out[o] = narrow<T>(r);
+}
+
+// ---- cols: innermost group kept ------------------------------------------------------------------
+template <int OP, typename T, int VEC>
+__global__ void __launch_bounds__(RB) cols_kernel(const T *__restrict__ in, T *__restrict__ out,
+                                                  acc_t<T> *__restrict__ partial, ColsParams p) {
+    using A = acc_t<T>;
+    // blockIdx.x = ((ko * split) + c) * ctiles + ct
+    uint32_t b = blockIdx.x;
+    uint32_t q = fd_div(b, p.ctiles);
+    const uint32_t ct = b - q * p.ctiles.d;
+    const uint32_t ko = q / p.split;
+    const uint32_t c = q - ko * p.split;
+
+    const int tx = threadIdx.x & (p.tx - 1);
+    const int ty = threadIdx.x / p.tx;
+    const int ny = RB / p.tx;
+    const uint32_t cv = ct * p.tx + tx;  // column vector index
+    const bool live = cv < p.kv;
+    const T *base = in + unravel(ko, p.kouter) + int64_t(cv) * VEC;
+
+    const uint32_t r0 = c * p.chunk;
+    const uint32_t r1 = min(p.rows, r0 + p.chunk);
+
+    A acc[VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = identity<OP, T>();
+
+    auto addr = [&](uint32_t r) -> const T * {
+        if (p.red.n == 1) return base + int64_t(r) * p.red.stride[0];
+        return base + unravel(r, p.red);
+    };
+    if (live) {
+        uint32_t r = r0 + ty;
+        for (; r + (RUNROLL - 1) * ny < r1; r += RUNROLL * ny) {
+            Pack<T, VEC> v[RUNROLL];
+#pragma unroll
+            for (int k = 0; k < RUNROLL; ++k) v[k] = ld_stream<T, VEC>(addr(r + k * ny));
+#pragma unroll
+            for (int k = 0; k < RUNROLL; ++k)
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v[k].v[i]));
+        }
+        for (; r < r1; r += ny) {
+            Pack<T, VEC> v = ld_stream<T, VEC>(addr(r));
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v.v[i]));
+        }
+    }
+    // combine the ny row lanes of each column through shared memory (fixed order)
+    __shared__ A sm[RB * VEC];
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) sm[(ty * p.tx + tx) * VEC + i] = acc[i];
+    __syncthreads();
+    if (ty == 0 && live) {
+#pragma unroll 1
+        for (int y = 1; y < ny; ++y)
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], sm[(y * p.tx + tx) * VEC + i]);
+        const int64_t o = int64_t(ko) * p.kin + int64_t(cv) * VEC;
+        if (p.split == 1) {
+            Pack<T, VEC> w;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) w.v[i] = narrow<T>(acc[i]);
+            *reinterpret_cast<Pack<T, VEC> *>(out + o) = w;
+        } else {
+            A *dst = partial + int64_t(c) * p.nout + o;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) dst[i] = acc[i];
+        }
+    }
+}
+
+// partial[split][nout] → out[nout]; one thread per output, coalesced across threads.
+template <int OP, typename T>
+__global__ void __launch_bounds__(RB) cols_finish_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out,
+                                                         int64_t nout, uint32_t split) {
+    using A = acc_t<T>;
+    const int64_t o = int64_t(blockIdx.x) * RB + threadIdx.x;
+    if (o >= nout) return;
+    A r = partial[o];
+    for (uint32_t c = 1; c < split; ++c) r = combine<OP>(r, partial[int64_t(c) * nout + o]);
+    out[o] = narrow<T>(r);
+}
+
+template <typename T> __global__ void fill_kernel(T *out, int64_t n, T v) {
+    int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = v;
+}
+
+// ---- host-side plan -----------------------------------------------------------------------------
+enum PlanKind { PLAN_EMPTY_OUT, PLAN_IDENTITY, PLAN_COPY, PLAN_ROWS_TEAM, PLAN_ROWS_BLOCK, PLAN_COLS };
+
+struct Plan {
+    PlanKind kind;
+    int vec;  // elements per vector the kernels will use (before the pointer-alignment check)
+    RowsParams rows;
+    ColsParams cols;
+    int64_t nout, nin;
+    size_t workspace;  // bytes
+    unsigned grid;
+};
+
+int pow2_ceil(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, int ndims, int sms, Plan *pl) {
+    if (ndim < 0 || ndim > DX_MAX_DIMS) return fail(DX_E_SHAPE, "reduce: rank %d outside [0, %d]", ndim, DX_MAX_DIMS);
+    if ((ndim > 0 && !shape) || (ndims > 0 && !dims)) return fail(DX_E_ARG, "reduce: null shape or dims");
+    bool red[DX_MAX_DIMS] = {false};
+    for (int i = 0; i < ndims; ++i) {
+        if (dims[i] < 0 || dims[i] >= ndim) return fail(DX_E_SHAPE, "reduce: axis %d out of range for rank %d", dims[i], ndim);
+        if (red[dims[i]]) return fail(DX_E_SHAPE, "reduce: axis %d listed twice", dims[i]);
+        red[dims[i]] = true;
+    }
+    const int es = dx_dtype_size(dtype);
+    const int acc_size = (es == 8) ? 8 : 4;
+    int64_t nin = 1, nout = 1;
+    for (int i = 0; i < ndim; ++i) {
+        if (shape[i] < 0) return fail(DX_E_SHAPE, "reduce: negative extent");
+        nin *= shape[i];
+        if (!red[i]) nout *= shape[i];
+    }
+    pl->nin = nin;
+    pl->nout = nout;
+    pl->workspace = 0;
+    pl->grid = 0;
+    if (nout == 0) { pl->kind = PLAN_EMPTY_OUT; return DX_OK; }
+    if (nin == 0) { pl->kind = PLAN_IDENTITY; return DX_OK; }
+    if (nin == nout) { pl->kind = PLAN_COPY; return DX_OK; }
+
+    // merge: drop extent-1 axes, fuse neighbours of the same class
+    struct G { int64_t size, stride; bool red; };
+    std::vector<G> g;
+    int64_t stride = 1;
+    for (int i = ndim - 1; i >= 0; --i) {
+        if (shape[i] != 1) {
+            if (!g.empty() && g.back().red == red[i]) g.back().size *= shape[i];  // g is built innermost-first
+            else g.push_back({shape[i], stride, red[i]});
+        }
+        stride *= shape[i];
+    }
+    std::reverse(g.begin(), g.end());  // outermost first
+    auto fill_groups = [&](Groups &dst, bool want_red, size_t skip_last) -> int {
+        dst.n = 0;
+        for (size_t i = 0; i + skip_last < g.size(); ++i)
+            if (g[i].red == want_red) {
+                if (g[i].size >= (1ll << 31)) return fail(DX_E_SHAPE, "reduce: merged axis of %lld elements is too long", (long long)g[i].size);
+                dst.fd[dst.n] = make_fastdiv((uint32_t)g[i].size);
+                dst.stride[dst.n] = g[i].stride;
+                ++dst.n;
+            }
+        return DX_OK;
+    };
+    const int64_t inner = g.back().size;
+    int vec = 16 / es;  // full 16-byte vectors when the contiguous run allows it, else scalar
+    if (inner % vec != 0) vec = 1;
+    pl->vec = vec;
+    const int target_ctas = sms * 8;
+
+    if (g.back().red) {
+        RowsParams &p = pl->rows;
+        if (int e = fill_groups(p.kept, false, 0)) return e;
+        if (int e = fill_groups(p.rout, true, 1)) return e;
+        if (nout >= (1ll << 31)) return fail(DX_E_SHAPE, "reduce: %lld outputs exceed the 2^31 limit", (long long)nout);
+        const int64_t units = (nin / nout) / vec;
+        if (units >= (1ll << 31)) return fail(DX_E_SHAPE, "reduce: %lld elements per output exceed the limit", (long long)(nin / nout));
+        p.lv = make_fastdiv((uint32_t)(inner / vec));
+        p.units = (uint32_t)units;
+        p.nout = (uint32_t)nout;
+        p.split = 1;
+        p.chunk = p.units;
+        p.team = 32;
+        if (units <= 512 && nout >= 64) {
+            pl->kind = PLAN_ROWS_TEAM;
+            p.team = std::min(32, pow2_ceil((int)((units + 3) / 4)));
+            const int64_t teams_per_cta = RB / p.team;
+            pl->grid = (unsigned)((nout + teams_per_cta - 1) / teams_per_cta);
+        } else {
+            pl->kind = PLAN_ROWS_BLOCK;
+            int64_t split = 1;
+            if (nout < target_ctas) {
+                const int64_t by_target = (target_ctas + nout - 1) / nout;
+                const int64_t by_work = std::max<int64_t>(1, units / (RB * RUNROLL * 2));
+                split = std::max<int64_t>(1, std::min(by_target, by_work));
+            }
+            int64_t chunk = (units + split - 1) / split;
+            chunk = (chunk + RB - 1) / RB * RB;  // keeps every CTA's vectors 16-byte·RB aligned
+            split = (units + chunk - 1) / chunk;
+            p.split = (uint32_t)split;
+            p.chunk = (uint32_t)chunk;
+            if (nout * split >= (1ll << 31)) return fail(DX_E_SHAPE, "reduce: grid too large");
+            pl->grid = (unsigned)(nout * split);
+            if (split > 1) pl->workspace = size_t(nout) * split * acc_size;
+        }
+    } else {
+        pl->kind = PLAN_COLS;
+        ColsParams &p = pl->cols;
+        if (int e = fill_groups(p.kouter, false, 1)) return e;
+        if (int e = fill_groups(p.red, true, 0)) return e;
+        const int64_t rows = nin / nout;
+        const int64_t nko = nout / inner;
+        if (rows >= (1ll << 31) || nko >= (1ll << 31) || inner / vec >= (1ll << 31))
+            return fail(DX_E_SHAPE, "reduce: extent too large");
+        p.kin = inner;
+        p.kv = (uint32_t)(inner / vec);
+        p.rows = (uint32_t)rows;
+        p.nout = nout;
+        p.tx = std::min(32, pow2_ceil((int)std::min<int64_t>(p.kv, 32)));
+        const int ny = RB / p.tx;
+        const int64_t ctiles = (p.kv + p.tx - 1) / p.tx;
+        p.ctiles = make_fastdiv((uint32_t)ctiles);
+        p.kouter_n = make_fastdiv((uint32_t)nko);
+        int64_t split = 1;
+        const int64_t ctas = ctiles * nko;
+        if (ctas < target_ctas) {
+            const int64_t by_target = (target_ctas + ctas - 1) / ctas;
+            const int64_t by_work = std::max<int64_t>(1, rows / (ny * RUNROLL * 2));
+            split = std::max<int64_t>(1, std::min(by_target, by_work));
+        }
+        int64_t chunk = (rows + split - 1) / split;
+        split = (rows + chunk - 1) / chunk;
+        p.split = (uint32_t)split;
+        p.chunk = (uint32_t)chunk;
+        if (ctas * split >= (1ll << 31)) return fail(DX_E_SHAPE, "reduce: grid too large");
+        pl->grid = (unsigned)(ctas * split);
+        if (split > 1) pl->workspace = size_t(nout) * split * acc_size;
+    }
+    return DX_OK;
+}
+
+template <int OP, typename T>
+int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cudaStream_t st) {
+    using A = acc_t<T>;
+    switch (pl.kind) {
+        case PLAN_EMPTY_OUT: return DX_OK;
+        case PLAN_IDENTITY: {
+            const unsigned grid = (unsigned)((pl.nout + 255) / 256);
+            fill_kernel<T><<<grid, 256, 0, st>>>(out, pl.nout, narrow<T>(identity<OP, T>()));
+            return check_launch("reduce(identity)");
+        }
+        case PLAN_COPY: {
+            cudaError_t e = cudaMemcpyAsync(out, in, size_t(pl.nin) * sizeof(T), cudaMemcpyDeviceToDevice, st);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "reduce(copy): %s", cudaGetErrorString(e));
+            return DX_OK;
+        }
+        default: break;
+    }
+    if (pl.workspace > 0) {
+        if (!ws || ws_bytes < pl.workspace)
+            return fail(DX_E_WORKSPACE, "reduce: needs %zu bytes of workspace, got %zu", pl.workspace, ws_bytes);
+        if (!aligned_to(ws, 16)) return fail(DX_E_WORKSPACE, "reduce: workspace must be 16-byte aligned");
+    }
+    A *partial = static_cast<A *>(ws);
+    constexpr int FULL = 16 / sizeof(T);
+    // The plan's vector width holds only if the pointers allow it; otherwise scalar.
+    int vec = pl.vec;
+    if (vec > 1 && !aligned_to(in, 16)) vec = 1;
+    if (pl.kind == PLAN_COLS && vec > 1 && !aligned_to(out, 16)) vec = 1;
+    Plan q = pl;
+    if (vec != pl.vec) {
+        const int f = pl.vec;  // pl.vec → 1
+        if (pl.kind == PLAN_COLS) {
+            ColsParams &p = q.cols;
+            p.kv = pl.cols.kv * f;
+            p.tx = std::min(32, pow2_ceil((int)std::min<uint32_t>(p.kv, 32)));
+            const int64_t ctiles = (int64_t(p.kv) + p.tx - 1) / p.tx;
+            p.ctiles = make_fastdiv((uint32_t)ctiles);
+            const int64_t nko = pl.nout / pl.cols.kin;
+            if (ctiles * nko * p.split >= (1ll << 31)) return fail(DX_E_SHAPE, "reduce: grid too large");
+            q.grid = (unsigned)(ctiles * nko * p.split);
+        } else {
+            RowsParams &p = q.rows;
+            if (uint64_t(pl.rows.units) * f >= (1ull << 31)) return fail(DX_E_SHAPE, "reduce: unaligned input too large");
+            p.units = pl.rows.units * f;
+            p.lv = make_fastdiv(pl.rows.lv.d * f);
+            p.chunk = pl.rows.chunk * f;
+        }
+    }
+
+#define LAUNCH_VEC(KERNEL, ...)                                                  \
+    do {                                                                         \
+        if (vec == FULL) KERNEL<OP, T, FULL><<<q.grid, RB, 0, st>>>(__VA_ARGS__); \
+        else KERNEL<OP, T, 1><<<q.grid, RB, 0, st>>>(__VA_ARGS__);                \
+    } while (0)
+
+    if (pl.kind == PLAN_ROWS_TEAM) {
+        LAUNCH_VEC(rows_team_kernel, in, out, q.rows);
+        return check_launch("reduce(rows/team)");
+    }
+    if (pl.kind == PLAN_ROWS_BLOCK) {
+        LAUNCH_VEC(rows_block_kernel, in, out, partial, q.rows);
+        if (int e = check_launch("reduce(rows/block)")) return e;
+        if (q.rows.split > 1) {
+            const unsigned grid = (q.rows.nout + RB / 32 - 1) / (RB / 32);
+            rows_finish_kernel<OP, T><<<grid, RB, 0, st>>>(partial, out, q.rows.nout, q.rows.split);
+            return check_launch("reduce(rows/finish)");
+        }
+        return DX_OK;
+    }
+    LAUNCH_VEC(cols_kernel, in, out, partial, q.cols);
+    if (int e = check_launch("reduce(cols)")) return e;
+    if (q.cols.split > 1) {
+        const unsigned grid = (unsigned)((q.cols.nout + RB - 1) / RB);
+        cols_finish_kernel<OP, T><<<grid, RB, 0, st>>>(partial, out, q.cols.nout, q.cols.split);
+        return check_launch("reduce(cols/finish)");
+    }
+    return DX_OK;
+#undef LAUNCH_VEC
+}
+
+template <typename T>
+int run_op(int op, const Plan &pl, const void *a, void *out, void *ws, size_t wsb, cudaStream_t st) {
+    switch (op) {
+        case DX_SUM: return run_plan<DX_SUM, T>(pl, (const T *)a, (T *)out, ws, wsb, st);
+        case DX_PROD: return run_plan<DX_PROD, T>(pl, (const T *)a, (T *)out, ws, wsb, st);
+        case DX_RMAX: return run_plan<DX_RMAX, T>(pl, (const T *)a, (T *)out, ws, wsb, st);
+        case DX_RMIN: return run_plan<DX_RMIN, T>(pl, (const T *)a, (T *)out, ws, wsb, st);
+        default: return fail(DX_E_ARG, "reduce: unknown op code %d", op);
+    }
+}
+
+}  // namespace
+}  // namespace dx
+
+using namespace dx;
+
+extern "C" size_t dx_reduce_workspace_bytes(int op, int dtype, const int64_t *shape, int ndim, const int32_t *dims,
+                                            int ndims) {
+    (void)op;
+    Plan pl;
+    if (dx_dtype_size(dtype) == 0 || dtype == DX_BOOL) return 0;
+    if (make_plan(dtype, shape, ndim, dims, ndims, sm_count(), &pl) != DX_OK) return 0;
+    return (pl.workspace + 255) / 256 * 256;
+}
+
+extern "C" int dx_reduce(int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
+                         int ndims, void *out, void *workspace, size_t workspace_bytes, void *stream) {
+    cudaStream_t st = as_stream(stream);
+    if (dx_dtype_size(dtype) == 0 || dtype == DX_BOOL)
+        return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
+    Plan pl;
+    if (int e = make_plan(dtype, shape, ndim, dims, ndims, sm_count(), &pl)) return e;
+    if (pl.nout > 0 && !out) return fail(DX_E_ARG, "reduce: null output");
+    if (pl.nin > 0 && !a) return fail(DX_E_ARG, "reduce: null input");
+    if (a == out && pl.nin > 0 && pl.kind != PLAN_COPY) return fail(DX_E_ALIAS, "reduce: output aliases input");
+    switch (dtype) {
+        case DX_F64: return run_op<double>(op, pl, a, out, workspace, workspace_bytes, st);
+        case DX_F32: return run_op<float>(op, pl, a, out, workspace, workspace_bytes, st);
+        case DX_F16: return run_op<f16>(op, pl, a, out, workspace, workspace_bytes, st);
+        case DX_BF16: return run_op<bf16>(op, pl, a, out, workspace, workspace_bytes, st);
+        case DX_I64: return run_op<int64_t>(op, pl, a, out, workspace, workspace_bytes, st);
+        case DX_I32: return run_op<int32_t>(op, pl, a, out, workspace, workspace_bytes, st);
+        case DX_I16: return run_op<int16_t>(op, pl, a, out, workspace, workspace_bytes, st);
+        case DX_I8: return run_op<int8_t>(op, pl, a, out, workspace, workspace_bytes, st);
+        default: return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
+    }
+}

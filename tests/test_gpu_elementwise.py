@@ -1,0 +1,243 @@
+"""GPU parity: elementwise kernels through the C ABI vs the CPU oracle.
+
+Bar: bit-exact for integer dtypes, compares, invert, switch, todtype and for the IEEE
+operations + - * / sqrt max min in every float dtype; exp/log/pow/sin/cos/tan within
+rel 1e-5 (fp32), 1e-12 (fp64), one unit in the last place of the 16-bit formats.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import (ALL_NUMERIC, FLOATS, INTS, NP_DTYPES, TORCH_DTYPES, assert_bit_exact, make, seed_of, to_gpu,
+                     to_np)
+
+pytestmark = pytest.mark.gpu
+
+# sizes: empty, one element, odd (scalar tail), exactly one tile, tiles + ragged tail
+SIZES = [0, 1, 7, 4096, 4096 * 3 + 5, 1 << 20]
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from deepx_b200 import tensorfunc as TF
+    from oracle import oracle as O
+    return TF, O
+
+
+def _close(got, want, dtype, what):
+    g, w = got.astype(np.float64), want.astype(np.float64)
+    tol = {"float64": 1e-12, "float32": 1e-5, "float16": 2e-3, "bfloat16": 1.6e-2}[dtype]
+    ok = np.isclose(g, w, rtol=tol, atol=0) | (np.isnan(g) & np.isnan(w)) | (g == w)
+    assert ok.all(), f"{what}: max rel err {np.nanmax(np.abs(g - w) / np.maximum(np.abs(w), 1e-300))}"
+
+
+@pytest.mark.parametrize("dtype", ALL_NUMERIC)
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "div", "max", "min"])
+def test_binary_exact(mods, op, dtype):
+    TF, O = mods
+    rng = np.random.default_rng(seed_of(op, dtype))
+    for n in SIZES:
+        a = make(rng, dtype, (n,))
+        b = make(rng, dtype, (n,), nonzero=(op == "div"))
+        A, B = to_gpu(a), to_gpu(b)
+        Cc = torch.empty_like(A)
+        getattr(TF, op)(A, B, Cc)
+        assert_bit_exact(to_np(Cc), getattr(O, op)(a, b), f"{op}<{dtype}> n={n}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "int32", "bfloat16"])
+def test_binary_inplace_alias(mods, dtype):
+    """out may be the same tensor as an input (front end's add_/mul_): identical indices only."""
+    TF, O = mods
+    rng = np.random.default_rng(5)
+    a, b = make(rng, dtype, (70001,)), make(rng, dtype, (70001,))
+    A, B = to_gpu(a), to_gpu(b)
+    TF.add(A, B, A)
+    assert_bit_exact(to_np(A), O.add(a, b), "add in place into a")
+    A = to_gpu(a)
+    TF.mul(A, A, A)
+    assert_bit_exact(to_np(A), O.mul(a, a), "mul(a,a)->a")
+    A, B = to_gpu(a), to_gpu(b)
+    TF.sub(A, B, B)
+    assert_bit_exact(to_np(B), O.sub(a, b), "sub in place into b")
+
+
+def test_binary_unaligned_pointers(mods):
+    """Views that start 4 bytes into an allocation take the scalar path and still match."""
+    TF, O = mods
+    rng = np.random.default_rng(6)
+    a, b = make(rng, "float32", (10001,)), make(rng, "float32", (10001,))
+    A, B = to_gpu(a)[1:], to_gpu(b)[1:]
+    Cc = torch.empty(10001, dtype=torch.float32, device="cuda:0")[1:]
+    TF.add(A, B, Cc)
+    assert_bit_exact(to_np(Cc), O.add(a[1:], b[1:]), "add unaligned")
+
+
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+def test_pow(mods, dtype):
+    TF, O = mods
+    rng = np.random.default_rng(7)
+    a = make(rng, dtype, (100003,), 0.1, 4.0)
+    b = make(rng, dtype, (100003,), -3.0, 3.0)
+    A, B = to_gpu(a), to_gpu(b)
+    Cc = torch.empty_like(A)
+    TF.pow(A, B, Cc)
+    _close(to_np(Cc), O.pow(a, b), dtype, "pow")
+    TF.powscalar(A, 2.5, Cc)
+    _close(to_np(Cc), O.powscalar(a, 2.5), dtype, "powscalar")
+    TF.rpowscalar(1.7, B, Cc)
+    _close(to_np(Cc), O.rpowscalar(1.7, b), dtype, "rpowscalar")
+    with pytest.raises(Exception):
+        X = to_gpu(make(rng, "int32", (8,)))
+        TF.pow(X, X, torch.empty_like(X))
+
+
+@pytest.mark.parametrize("dtype", ALL_NUMERIC)
+@pytest.mark.parametrize("op", ["addscalar", "subscalar", "rsubscalar", "mulscalar", "divscalar", "rdivscalar",
+                                "maxscalar", "minscalar"])
+def test_scalar_exact(mods, op, dtype):
+    TF, O = mods
+    rng = np.random.default_rng(seed_of(op, dtype))
+    s = 3 if dtype in INTS else 1.375
+    for n in [0, 5, 4096 * 2 + 3]:
+        a = make(rng, dtype, (n,), nonzero=True)
+        A = to_gpu(a)
+        Cc = torch.empty_like(A)
+        if op.startswith("r"):
+            getattr(TF, op)(s, A, Cc)
+            want = getattr(O, op)(s, a)
+        else:
+            getattr(TF, op)(A, s, Cc)
+            want = getattr(O, op)(a, s)
+        assert_bit_exact(to_np(Cc), want, f"{op}<{dtype}> n={n}")
+
+
+@pytest.mark.parametrize("dtype", FLOATS)
+def test_sqrt_exact(mods, dtype):
+    TF, O = mods
+    rng = np.random.default_rng(11)
+    a = make(rng, dtype, (300007,), 0.0, 1000.0)
+    A = to_gpu(a)
+    Cc = torch.empty_like(A)
+    TF.sqrt(A, Cc)
+    assert_bit_exact(to_np(Cc), O.sqrt(a), f"sqrt<{dtype}>")
+
+
+@pytest.mark.parametrize("dtype", FLOATS)
+@pytest.mark.parametrize("op", ["exp", "log", "sin", "cos", "tan"])
+def test_unary_math(mods, op, dtype):
+    TF, O = mods
+    if op == "tan" and dtype in ("float16", "bfloat16"):
+        pytest.skip("tan is registered for float64/float32 only")
+    rng = np.random.default_rng(12)
+    lo, hi = {"exp": (-10, 10), "log": (1e-3, 1e3), "sin": (-6, 6), "cos": (-6, 6), "tan": (-1.4, 1.4)}[op]
+    a = make(rng, dtype, (200003,), lo, hi)
+    A = to_gpu(a)
+    Cc = torch.empty_like(A)
+    getattr(TF, op)(A, Cc)
+    got, want = to_np(Cc), getattr(O, op)(a)
+    if op in ("sin", "cos") and dtype in ("float32", "float64"):
+        # near zeros of the function a relative bound is meaningless: absolute 1e-6 there
+        g, w = got.astype(np.float64), want.astype(np.float64)
+        assert (np.abs(g - w) <= 1e-6 + 1e-5 * np.abs(w)).all()
+    else:
+        _close(got, want, dtype, f"{op}<{dtype}>")
+
+
+@pytest.mark.parametrize("dtype", INTS + ["bool"])
+def test_invert(mods, dtype):
+    TF, O = mods
+    rng = np.random.default_rng(13)
+    a = make(rng, dtype, (50001,))
+    A = to_gpu(a)
+    Cc = torch.empty_like(A)
+    TF.invert(A, Cc)
+    assert_bit_exact(to_np(Cc), O.invert(a), f"invert<{dtype}>")
+
+
+@pytest.mark.parametrize("dtype", ALL_NUMERIC)
+@pytest.mark.parametrize("op", ["equal", "notequal", "less", "greater"])
+def test_compare(mods, op, dtype):
+    TF, O = mods
+    rng = np.random.default_rng(seed_of(op, dtype))
+    n = 4096 * 2 + 11
+    a = make(rng, dtype, (n,))
+    b = a.copy()
+    flip = rng.random(n) < 0.5
+    b[flip] = make(rng, dtype, (n,))[flip]
+    A, B = to_gpu(a), to_gpu(b)
+    M = torch.empty(n, dtype=torch.bool, device="cuda:0")
+    s = 2 if dtype in INTS else 0.5
+    if op in ("equal", "notequal"):
+        for eps in (0.0, 0.75, 2.0):
+            getattr(TF, op)(A, B, eps, M)
+            assert_bit_exact(to_np(M), getattr(O, op)(a, b, eps), f"{op}<{dtype}> eps={eps}")
+            getattr(TF, op + "scalar")(A, s, eps, M)
+            assert_bit_exact(to_np(M), getattr(O, op + "scalar")(a, s, eps), f"{op}scalar<{dtype}> eps={eps}")
+    else:
+        getattr(TF, op)(A, B, M)
+        assert_bit_exact(to_np(M), getattr(O, op)(a, b), f"{op}<{dtype}>")
+        getattr(TF, op + "scalar")(A, s, M)
+        assert_bit_exact(to_np(M), getattr(O, op + "scalar")(a, s), f"{op}scalar<{dtype}>")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "int64", "int8", "bool"])
+def test_switch(mods, dtype):
+    TF, O = mods
+    rng = np.random.default_rng(17)
+    for n in [1, 33, 4096 * 2 + 7]:
+        ts = [make(rng, dtype, (n,)) for _ in range(3)]
+        Ts = [to_gpu(t) for t in ts]
+        out = torch.empty_like(Ts[0])
+        cb = rng.integers(0, 2, n).astype(np.bool_)
+        TF.Switch(Ts[:2], to_gpu(cb), out)
+        assert_bit_exact(to_np(out), O.Switch(ts[:2], cb), f"switch bool<{dtype}> n={n}")
+        ci = rng.integers(0, 3, n).astype(np.int32)
+        TF.Switch(Ts, to_gpu(ci), out)
+        assert_bit_exact(to_np(out), O.Switch(ts, ci), f"switch int32<{dtype}> n={n}")
+    with pytest.raises(ValueError):
+        TF.Switch(Ts, to_gpu(cb), out)  # bool cases need exactly two tensors
+
+
+@pytest.mark.parametrize("src", ALL_NUMERIC)
+@pytest.mark.parametrize("dst", ALL_NUMERIC)
+def test_todtype(mods, src, dst):
+    TF, O = mods
+    rng = np.random.default_rng(19)
+    a = make(rng, src, (4096 + 77,), -100.0, 100.0)
+    A = to_gpu(a)
+    Cc = torch.empty(a.shape, dtype=TORCH_DTYPES[dst], device="cuda:0")
+    TF.todtype(A, Cc)
+    assert_bit_exact(to_np(Cc), O.todtype(a, NP_DTYPES[dst]), f"todtype {src}->{dst}")
+
+
+@pytest.mark.parametrize("dtype", ALL_NUMERIC + ["bool"])
+def test_constant(mods, dtype):
+    TF, _ = mods
+    t = torch.empty(4096 * 2 + 3, dtype=TORCH_DTYPES[dtype], device="cuda:0")
+    v = True if dtype == "bool" else (7 if dtype in INTS else 0.5)
+    TF.constant(t, v)
+    assert (to_np(t) == NP_DTYPES[dtype](v)).all()
+
+
+def test_shape_and_dtype_errors(mods):
+    TF, _ = mods
+    a = torch.zeros(8, device="cuda:0")
+    with pytest.raises(ValueError, match="shape mismatch"):
+        TF.add(a, a, torch.zeros(9, device="cuda:0"))
+    with pytest.raises(TypeError, match="Type mismatch"):
+        TF.add(a, a, torch.zeros(8, device="cuda:0", dtype=torch.float64))
+    with pytest.raises(ValueError):
+        TF.add(a.cpu(), a.cpu(), a.cpu())
+
+
+def test_config_add_4096x4096(mods):
+    """deepxIR add on float32 [4096,4096], U(-1,1), seed 0 — element for element."""
+    TF, O = mods
+    rng = np.random.default_rng(0)
+    a = rng.uniform(-1, 1, (4096, 4096)).astype(np.float32)
+    b = rng.uniform(-1, 1, (4096, 4096)).astype(np.float32)
+    A, B = to_gpu(a), to_gpu(b)
+    Cc = torch.empty_like(A)
+    TF.add(A, B, Cc)
+    assert_bit_exact(to_np(Cc), O.add(a, b), "add [4096,4096]")
