@@ -6,7 +6,17 @@ Layers, bottom up:
                            meaning, error behaviour) over that ABI, on CUDA tensors
   * ``executor``           the deepxIR text boundary: parser, op registry, tensor store
   * ``sharded``            axis-0 sharding across the GPUs of one node
-"""
-from . import _native  # noqa: F401  (fails loudly when the CUDA library is missing)
 
-__all__ = ["_native"]
+Submodules load on first use (``deepx_b200.build`` must be importable before the native
+library exists).  ``_native`` raises, with the build command, when the library is missing:
+there is no CPU fallback.
+"""
+import importlib
+
+_SUBMODULES = ("_native", "tensorfunc", "executor", "sharded", "build")
+
+
+def __getattr__(name):
+    if name in _SUBMODULES:
+        return importlib.import_module(f"{__name__}.{name}")
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

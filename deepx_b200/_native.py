@@ -53,6 +53,7 @@ SIGNATURES = {
     "dx_indexselect": (_i, [_i, _vp, _pi64, _i, _i, _vp, _pi64, _i, _i, _vp, _vp, _vp]),
     "dx_repeat": (_i, [_i, _vp, _pi64, _i, _pi64, _vp, _vp]),
     "dx_matmul": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "dx_matmul_status": (_i, [_vp]),
     "dx_pool_create": (_vp, [_i, _sz]),
     "dx_pool_destroy": (None, [_vp]),
     "dx_pool_alloc": (_vp, [_vp, _sz]),

@@ -1,7 +1,532 @@
-// dx_matmul placeholder until the tcgen05 kernel lands.
+// dx_matmul: batched row-major C[b,M,N] = A[b,M,K] · B[b,K,N].
+//
+// bf16 / f16: a persistent, warp-specialised tcgen05 kernel (sm_100a).
+//   * one CTA per SM walks output tiles of 128 × 256;
+//   * warp 0 (one elected lane) is the TMA producer: per 64-deep K block it loads an
+//     A tile (128 rows × 64 K, K-major) and four B tiles (64 K × 64 N, N-major) into a
+//     4-stage shared-memory ring with 128-byte swizzle, completing on an mbarrier;
+//   * warp 1 (one elected lane) issues tcgen05.mma (M128 N256 K16, kind::f16, fp32
+//     accumulate) four times per stage, reading operands straight from shared memory
+//     through matrix descriptors; tcgen05.commit releases the stage / publishes the tile;
+//   * accumulators live in TMEM, double-buffered (2 × 256 columns), so the epilogue of
+//     tile i overlaps the main loop of tile i+1;
+//   * warps 2-5 are the epilogue: tcgen05.ld their 32-lane quarter, round fp32 → 16-bit
+//     once, 16-byte stores.
+// B is consumed in its natural [K,N] layout (MN-major operand), so no transpose pass.
+// No cluster launch and no multicast: every CTA loads its own tiles; A and B fit in L2.
+//
+// Every wait on an mbarrier is bounded by a clock: on expiry the kernel records a code in
+// a status word, all roles leave their loops, TMEM is freed and the kernel returns; the
+// host turns the status into DX_E_CUDA.
+//
+// f32 / f64: a register-tiled SIMT FMA kernel (the reference calls cuBLAS Sgemm/Dgemm,
+// executor/op-cuda/src/deepx/tensorfunc/matmul_cublas.hpp:16-145; a 1e-5 bound rules out
+// plain TF32 tensor-core math).
+#include <cuda.h>
+
+#include <mutex>
+
 #include "common.cuh"
+
+namespace dx {
+namespace {
+
+// ---- tile configuration ----------------------------------------------------------------
+constexpr int BM = 128, BN = 256, BK = 64;   // CTA tile; BK·2 bytes = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int ACC_STAGES = 2;
+constexpr int NUM_THREADS = 192;             // TMA warp, MMA warp, 4 epilogue warps
+constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
+constexpr int B_BOX_N = 64;                  // one TMA box of B: 64 K-rows × 64 N (128 bytes wide)
+constexpr int B_BOX_BYTES = BK * B_BOX_N * 2;  // 8 KiB
+constexpr int B_STAGE_BYTES = B_BOX_BYTES * (BN / B_BOX_N);  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+constexpr int TMEM_COLS = ACC_STAGES * BN;   // 512
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;  // ~2 s
+
+enum GemmStatus : int { GEMM_OK = 0, GEMM_TIMEOUT_FULL = 1, GEMM_TIMEOUT_EMPTY = 2, GEMM_TIMEOUT_TMEM_FULL = 3,
+                        GEMM_TIMEOUT_TMEM_EMPTY = 4 };
+
+// ---- PTX wrappers -------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when the clock limit passed or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap *map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- descriptors ----------------------------------------------------------------------------
+// Shared-memory matrix descriptor (64-bit): start address >>4 in [0,14), leading byte offset >>4
+// in [16,30), stride byte offset >>4 in [32,46), descriptor version 1 in [46,48), swizzle mode in
+// [61,64) (2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= uint64_t((saddr >> 4) & 0x3FFF);
+    d |= uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= uint64_t(1) << 46;
+    d |= uint64_t(2) << 61;
+    return d;
+}
+// Instruction descriptor (32-bit) for kind::f16: D format [4,6) 1 = f32; A format [7,10), B format
+// [10,13) (0 = f16, 1 = bf16); A major bit 15, B major bit 16 (0 = K-major, 1 = MN-major);
+// N>>3 in [17,23); M>>4 in [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(int ab_format) {
+    return (1u << 4) | (uint32_t(ab_format) << 7) | (uint32_t(ab_format) << 10) | (0u << 15) | (1u << 16) |
+           (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+}
+
+struct GemmParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, num_tiles, k_blocks;
+    int *status;
+};
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<bf16>(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<f16>(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, T *__restrict__ C,
+                        GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzle atoms are 1024 bytes: stage bases must be 1024-byte aligned
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + ACC_STAGES + a); };
+    const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 2 * ACC_STAGES);
+    uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 2 * ACC_STAGES));
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 2 * ACC_STAGES) + 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < ACC_STAGES; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ===== TMA producer =====
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                const int per_batch = p.tiles_m * p.tiles_n;
+                const int b = tile / per_batch;
+                const int t = tile - b * per_batch;
+                const int tn = t / p.tiles_m, tm = t - tn * p.tiles_m;  // M tiles fastest: neighbours share a B panel
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_EMPTY); }
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+                    tma_load_3d(sa, &tmap_a, full_bar(stage), kb * BK, tm * BM, b);
+#pragma unroll
+                    for (int j = 0; j < BN / B_BOX_N; ++j)
+                        tma_load_3d(sb + j * B_BOX_BYTES, &tmap_b, full_bar(stage), tn * BN + j * B_BOX_N, kb * BK, b);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (*abort_flag) {
+                // give copies already in flight time to land before the CTA's shared memory is released
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000ll) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(std::is_same<T, bf16>::value ? 1 : 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_TMEM_EMPTY); }
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_FULL); }
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // A: K-major, 8-row groups 1024 bytes apart; step 16 K elements = 32 bytes inside the swizzle row
+                        const uint64_t adesc = make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+                        // B: N-major, 64-column panels 8192 bytes apart (LBO), 8-K-row groups 1024 bytes apart (SBO);
+                        // step 16 K rows = 2048 bytes
+                        const uint64_t bdesc = make_smem_desc(sb + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
+                        umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));  // accumulator complete
+                if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ===== epilogue: warps 2..5; a warp may touch TMEM lanes 32·(warp%4) .. +31 =====
+        const int q = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool vec_ok = (p.N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+            const int per_batch = p.tiles_m * p.tiles_n;
+            const int b = tile / per_batch;
+            const int t = tile - b * per_batch;
+            const int tn = t / p.tiles_m, tm = t - tn * p.tiles_m;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+                if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL); }
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * BM + q * 32 + lane;
+            T *crow = C + (size_t(b) * p.M + row) * p.N;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c0, r);
+                tmem_ld_wait();
+                const int col = tn * BN + c0;
+                if (row < p.M) {
+                    if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 o;
+                            o.x = pack2<T>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                            o.y = pack2<T>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                            o.z = pack2<T>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                            o.w = pack2<T>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                            *reinterpret_cast<uint4 *>(crow + col + 8 * v) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < p.N) crow[col + j] = from_compute<T>(__uint_as_float(r[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    // Teardown: everyone meets, then the allocating warp frees TMEM.
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---- SIMT FMA kernel for f32 / f64 (and shapes the TMA path cannot take) -----------------------
+template <typename T, typename A, int TS, int RT>
+__global__ void __launch_bounds__((TS / RT) * (TS / RT))
+    gemm_simt_kernel(const T *__restrict__ Am, const T *__restrict__ Bm, T *__restrict__ Cm, int M, int N, int K) {
+    constexpr int KT = 16;
+    constexpr int NT = (TS / RT) * (TS / RT);
+    __shared__ A sa[KT][TS + 1];
+    __shared__ A sb[KT][TS + 1];
+    const int b = blockIdx.z;
+    Am += size_t(b) * M * K;
+    Bm += size_t(b) * K * N;
+    Cm += size_t(b) * M * N;
+    const int tx = threadIdx.x % (TS / RT), ty = threadIdx.x / (TS / RT);
+    const int m0 = blockIdx.y * TS, n0 = blockIdx.x * TS;
+    A acc[RT][RT];
+#pragma unroll
+    for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int j = 0; j < RT; ++j) acc[i][j] = A(0);
+    for (int k0 = 0; k0 < K; k0 += KT) {
+        for (int i = threadIdx.x; i < TS * KT; i += NT) {
+            const int r = i / KT, c = i % KT;  // A tile: TS rows × KT
+            sa[c][r] = (m0 + r < M && k0 + c < K) ? A(to_compute(Am[size_t(m0 + r) * K + k0 + c])) : A(0);
+        }
+        for (int i = threadIdx.x; i < TS * KT; i += NT) {
+            const int r = i / TS, c = i % TS;  // B tile: KT rows × TS
+            sb[r][c] = (k0 + r < K && n0 + c < N) ? A(to_compute(Bm[size_t(k0 + r) * N + n0 + c])) : A(0);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < KT; ++k) {
+            A av[RT], bv[RT];
+#pragma unroll
+            for (int i = 0; i < RT; ++i) av[i] = sa[k][ty * RT + i];
+#pragma unroll
+            for (int j = 0; j < RT; ++j) bv[j] = sb[k][tx * RT + j];
+#pragma unroll
+            for (int i = 0; i < RT; ++i)
+#pragma unroll
+                for (int j = 0; j < RT; ++j) acc[i][j] += av[i] * bv[j];
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RT; ++i)
+#pragma unroll
+        for (int j = 0; j < RT; ++j) {
+            const int m = m0 + ty * RT + i, n = n0 + tx * RT + j;
+            if (m < M && n < N) Cm[size_t(m) * N + n] = from_compute<T>(static_cast<compute_t<T>>(acc[i][j]));
+        }
+}
+
+template <typename T, typename A>
+int launch_simt(const T *Am, const T *Bm, T *Cm, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+    constexpr int TS = 64, RT = 4;
+    if (batch > 65535) return fail(DX_E_SHAPE, "matmul: batch %lld too large", (long long)batch);
+    dim3 grid((unsigned)((N + TS - 1) / TS), (unsigned)((M + TS - 1) / TS), (unsigned)batch);
+    if (grid.y > 65535) return fail(DX_E_SHAPE, "matmul: M %lld too large for the SIMT path", (long long)M);
+    gemm_simt_kernel<T, A, TS, RT><<<grid, (TS / RT) * (TS / RT), 0, st>>>(Am, Bm, Cm, (int)M, (int)N, (int)K);
+    return check_launch("matmul(simt)");
+}
+
+// ---- tensor maps ----------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+        else cudaGetLastError();
+    });
+    return fn;
+}
+
+int make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t rows, uint64_t batch,
+             uint32_t box_inner, uint32_t box_rows) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return fail(DX_E_CUDA, "matmul: cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {inner, rows, batch};
+    const cuuint64_t strides[2] = {inner * 2, inner * rows * 2};  // bytes, for dims 1 and 2
+    const cuuint32_t box[3] = {box_inner, box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(DX_E_CUDA, "matmul: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return DX_OK;
+}
+
+// Status word of the tensor-core kernel (0 = fine), one per device that loads the module.
+__device__ int g_gemm_status = 0;
+std::mutex g_setup_mu;
+bool g_attr_set[64][2] = {};
+int *g_status_ptr[64] = {};
+
+template <typename T>
+int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return fail(DX_E_CUDA, "matmul: device index %d out of range", dev);
+    int *status;
+    {
+        std::lock_guard<std::mutex> lk(g_setup_mu);
+        if (!g_status_ptr[dev]) {
+            void *sym = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&sym, g_gemm_status);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_status_ptr[dev] = static_cast<int *>(sym);
+        }
+        status = g_status_ptr[dev];
+        const int ti = std::is_same<T, bf16>::value ? 0 : 1;
+        if (!g_attr_set[dev][ti]) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            g_attr_set[dev][ti] = true;
+        }
+    }
+    const CUtensorMapDataType dt = std::is_same<T, bf16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap ma, mb;
+    if (int e = make_map(&ma, dt, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, BK, BM)) return e;
+    if (int e = make_map(&mb, dt, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, B_BOX_N, BK)) return e;
+    GemmParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.tiles_m = (int)((M + BM - 1) / BM);
+    p.tiles_n = (int)((N + BN - 1) / BN);
+    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n * batch;
+    if (tiles >= (1ll << 31)) return fail(DX_E_SHAPE, "matmul: too many tiles");
+    p.num_tiles = (int)tiles;
+    p.k_blocks = (int)((K + BK - 1) / BK);
+    p.status = status;
+    const int grid = (int)std::min<int64_t>(tiles, sm_count());
+    gemm_tcgen05_kernel<T><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, C, p);
+    return check_launch("matmul(tcgen05)");
+}
+
+}  // namespace
+}  // namespace dx
+
+using namespace dx;
+
+// Reads and clears the status word the tensor-core kernel writes when a bounded wait expires.
+// Synchronises the stream; meant for tests and for the executor's error path.
+extern "C" int dx_matmul_status(void *stream) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64 || !g_status_ptr[dev]) return 0;
+    int h = 0;
+    cudaStream_t st = as_stream(stream);
+    if (cudaMemcpyAsync(&h, g_status_ptr[dev], sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+        return fail(DX_E_CUDA, "matmul: cannot read the status word: %s", cudaGetErrorString(cudaGetLastError()));
+    if (h != 0) {
+        cudaMemsetAsync(g_status_ptr[dev], 0, sizeof(int), st);
+        return fail(DX_E_CUDA, "matmul: tensor-core pipeline wait %d expired", h);
+    }
+    return DX_OK;
+}
+
 extern "C" int dx_matmul(int dtype, const void *A, const void *B, void *C, int64_t batch, int64_t M, int64_t N, int64_t K,
                          void *stream) {
-    (void)A; (void)B; (void)C; (void)batch; (void)M; (void)N; (void)K; (void)stream;
-    return dx::fail(DX_E_UNSUPPORTED, "matmul: not built yet (dtype code %d)", dtype);
+    cudaStream_t st = as_stream(stream);
+    if (batch < 0 || M < 0 || N < 0 || K < 0) return fail(DX_E_SHAPE, "matmul: negative extent");
+    if (batch == 0 || M == 0 || N == 0) return DX_OK;
+    if (!A || !B || !C) {
+        if (K == 0 && C) { /* fallthrough to zero fill */ } else return fail(DX_E_ARG, "matmul: null pointer");
+    }
+    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return fail(DX_E_SHAPE, "matmul: extent too large");
+    if (K == 0) return dx_fill(dtype, C, 0.0, 0, batch * M * N, stream);
+    switch (dtype) {
+        case DX_BF16:
+        case DX_F16: {
+            // TMA needs 16-byte aligned bases and row pitches; anything else takes the SIMT path.
+            const bool tma_ok = (K % 8 == 0) && (N % 8 == 0) && aligned_to(A, 16) && aligned_to(B, 16);
+            if (tma_ok) {
+                return dtype == DX_BF16 ? launch_tcgen05<bf16>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, st)
+                                        : launch_tcgen05<f16>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);
+            }
+            return dtype == DX_BF16 ? launch_simt<bf16, float>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, st)
+                                    : launch_simt<f16, float>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);
+        }
+        case DX_F32: return launch_simt<float, float>((const float *)A, (const float *)B, (float *)C, batch, M, N, K, st);
+        case DX_F64: return launch_simt<double, double>((const double *)A, (const double *)B, (double *)C, batch, M, N, K, st);
+        default: return fail(DX_E_DTYPE, "matmul: unsupported dtype code %d (float dtypes only)", dtype);
+    }
 }

@@ -201,6 +201,11 @@ int dx_repeat(int dtype, const void *a, const int64_t *a_shape, int ndim, const 
  * accumulation in the tensor dtype. */
 int dx_matmul(int dtype, const void *A, const void *B, void *C, int64_t batch, int64_t M, int64_t N, int64_t K,
               void *stream);
+/* Every wait inside the tensor-core kernel is bounded; if one expires the kernel records
+ * which and returns.  This reads (and clears) that record: DX_OK, or DX_E_CUDA with the
+ * stage in the message.  Synchronises `stream`.  Stands where the reference checks
+ * cudaGetLastError after a launch (executor/op-cuda/src/deepx/tensorfunc/cuda.hpp:73-78). */
+int dx_matmul_status(void *stream);
 
 /* ---- device memory pool ------------------------------------------------------
  * Replaces the per-tensor cudaMalloc/cudaFree of

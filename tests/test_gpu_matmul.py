@@ -1,0 +1,141 @@
+"""GPU parity: matmul through the C ABI vs the CPU oracle and a float64 reference.
+
+Bar: bf16/f16 within 1e-2 relative (scaled by Σ|a||b| per output, fp32 accumulation, one
+rounding), f32 within 1e-5, f64 within 1e-12, against a float64 GEMM of the same inputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import NP_DTYPES, TORCH_DTYPES, make, seed_of, to_gpu, to_np
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float64": 1e-12, "float32": 1e-5, "float16": 2e-3, "bfloat16": 1e-2}
+
+
+@pytest.fixture(scope="module")
+def mods():
+    from deepx_b200 import _native as N
+    from deepx_b200 import tensorfunc as TF
+    from oracle import oracle as O
+    return TF, O, N
+
+
+def check(TF, N, a, b, dtype, what):
+    A, B = to_gpu(a), to_gpu(b)
+    Cc = torch.empty(list(a.shape[:-1]) + [b.shape[-1]], dtype=TORCH_DTYPES[dtype], device="cuda:0")
+    TF.matmul(A, B, Cc)
+    N.check(N.lib.dx_matmul_status(None))
+    got = to_np(Cc).astype(np.float64)
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    ref = a64 @ b64
+    scale = np.abs(a64) @ np.abs(b64)
+    err = np.abs(got - ref)
+    # one rounding of the result (relative to |ref|) + accumulation error (relative to Σ|a||b|)
+    bound = TOL[dtype] * np.abs(ref) + (1e-6 if dtype != "float64" else 1e-14) * scale + 1e-300
+    bad = err > bound
+    assert not bad.any(), (f"{what}: {bad.sum()} of {bad.size} outside tolerance; max err {err.max():.3e}; "
+                           f"first bad index {np.argwhere(bad)[0].tolist()} got {got[tuple(np.argwhere(bad)[0])]} "
+                           f"ref {ref[tuple(np.argwhere(bad)[0])]}")
+    return got
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("shape", [
+    (128, 256, 64), (128, 256, 256), (256, 512, 128), (384, 768, 1024),   # whole tiles
+    (100, 200, 72), (130, 264, 40), (1, 8, 8), (257, 1000, 520),          # ragged M/N/K (TMA path: N,K % 8 == 0)
+    (64, 100, 30), (7, 5, 3),                                             # N or K not multiple of 8: SIMT path
+])
+def test_matmul_16bit(mods, shape, dtype):
+    TF, O, N = mods
+    M, Nn, K = shape
+    rng = np.random.default_rng(seed_of("mm", shape, dtype))
+    a = make(rng, dtype, (M, K), -1.0, 1.0)
+    b = make(rng, dtype, (K, Nn), -1.0, 1.0)
+    got = check(TF, N, a, b, dtype, f"matmul<{dtype}> {shape}")
+    if M * Nn * K <= 64 * 1024 * 1024:
+        want = O.matmul(a, b).astype(np.float64)
+        # oracle: same fp32 accumulation + one rounding; may differ by the accumulation order only
+        assert np.abs(got - want).max() <= 2 * TOL[dtype] * max(1.0, np.abs(want).max())
+
+
+def test_matmul_identity_exact(mods):
+    """A · I reproduces A bit for bit: exercises every (row, k) → (row, n) path of the tile."""
+    TF, O, N = mods
+    rng = np.random.default_rng(3)
+    a = make(rng, "bfloat16", (256, 512), -2.0, 2.0)
+    eye = np.eye(512, dtype=np.float32).astype(NP_DTYPES["bfloat16"])
+    A, B = to_gpu(a), to_gpu(eye)
+    Cc = torch.empty((256, 512), dtype=torch.bfloat16, device="cuda:0")
+    TF.matmul(A, B, Cc)
+    N.check(N.lib.dx_matmul_status(None))
+    assert np.array_equal(to_np(Cc).view(np.uint16), a.view(np.uint16))
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16"])
+def test_matmul_batched(mods, dtype):
+    TF, O, N = mods
+    rng = np.random.default_rng(5)
+    a = make(rng, dtype, (2, 3, 130, 72), -1.0, 1.0)
+    b = make(rng, dtype, (2, 3, 72, 264), -1.0, 1.0)
+    check(TF, N, a, b, dtype, "matmul batched [2,3,130,72]x[2,3,72,264]")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "float64"])
+def test_matmul_fp32_fp64(mods, dtype):
+    TF, O, N = mods
+    rng = np.random.default_rng(7)
+    for M, Nn, K in [(2, 2, 3), (65, 130, 257), (256, 256, 512)]:
+        a = make(rng, dtype, (M, K), -1.0, 1.0)
+        b = make(rng, dtype, (K, Nn), -1.0, 1.0)
+        check(TF, N, a, b, dtype, f"matmul<{dtype}> {(M, Nn, K)}")
+    a = make(rng, dtype, (2, 3, 4, 5), -1.0, 1.0)
+    b = make(rng, dtype, (2, 3, 5, 6), -1.0, 1.0)
+    check(TF, N, a, b, dtype, "batched [2,3,4,5]x[2,3,5,6]")  # shapes of executor/op-cuda/test/tensorfunc/1_cublas_matmul.cpp:36-62
+
+
+def test_matmul_golden_arange(mods):
+    """arange [2,3,4] x [2,4,5]: the worked example in executor/op-ompsimd/test/tensorfunc/4_tensor_matmul.cpp:22-35."""
+    TF, O, N = mods
+    a = np.arange(24, dtype=np.float32).reshape(2, 3, 4)
+    b = np.arange(40, dtype=np.float32).reshape(2, 4, 5)
+    A, B = to_gpu(a), to_gpu(b)
+    Cc = torch.empty((2, 3, 5), dtype=torch.float32, device="cuda:0")
+    TF.matmul(A, B, Cc)
+    assert np.array_equal(to_np(Cc), a @ b)  # small integers: exact in fp32
+    assert np.array_equal(O.matmul(a, b), a @ b)
+
+
+def test_matmul_shape_errors(mods):
+    TF, O, N = mods
+    a = torch.zeros(4, 5, device="cuda:0")
+    with pytest.raises(ValueError):
+        TF.matmul(a, torch.zeros(6, 7, device="cuda:0"), torch.zeros(4, 7, device="cuda:0"))
+    with pytest.raises(Exception):
+        i = torch.zeros(4, 4, dtype=torch.int32, device="cuda:0")
+        TF.matmul(i, i, i.clone())
+
+
+def test_config_matmul_bf16_8192x4096x4096(mods):
+    """bf16 A[8192,4096] × B[4096,4096] ~ N(0,0.02), fp32 accumulate, bf16 out: sampled rows
+    against float64, plus the size-independent identity (A·B)·1 = A·(B·1)."""
+    TF, O, N = mods
+    rng = np.random.default_rng(0)
+    a = (rng.standard_normal((8192, 4096), dtype=np.float32) * np.float32(0.02)).astype(NP_DTYPES["bfloat16"])
+    b = (rng.standard_normal((4096, 4096), dtype=np.float32) * np.float32(0.02)).astype(NP_DTYPES["bfloat16"])
+    A, B = to_gpu(a), to_gpu(b)
+    Cc = torch.empty((8192, 4096), dtype=torch.bfloat16, device="cuda:0")
+    TF.matmul(A, B, Cc)
+    N.check(N.lib.dx_matmul_status(None))
+    got = to_np(Cc).astype(np.float64)
+    rows = np.concatenate([np.arange(0, 8192, 517), [127, 128, 8191]])
+    a64, b64 = a[rows].astype(np.float64), b.astype(np.float64)
+    ref = a64 @ b64
+    scale = np.abs(a64) @ np.abs(b64)
+    err = np.abs(got[rows] - ref)
+    assert (err <= 1e-2 * np.abs(ref) + 1e-6 * scale).all(), f"max err {err.max()}"
+    lhs = got.sum(axis=1)
+    rhs = a.astype(np.float64) @ b.astype(np.float64).sum(axis=1)
+    # each of the 4096 outputs in a row carries ≤ 2^-9 relative rounding of |c|
+    assert (np.abs(lhs - rhs) <= 2.0 ** -8 * np.abs(got).sum(axis=1) + 1e-9).all()
