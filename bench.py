@@ -1,0 +1,427 @@
+#!/usr/bin/env python
+"""Benchmark of the deepxIR op hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (``config.workload``): the sharded elementwise + reduce chain on float32
+[2048, 1048576] (2^31 elements, U(-1,1)): t=exp(x); t=t*y; z=t+x; s=sum(z) over all axes;
+m=reducemax(z) over axis 1.  The tensor is split on axis 0 over the ranks (total size fixed,
+"strong" scaling); the global sum combines per-rank partials with one NCCL all-reduce.
+One step = that chain once.  ``value`` = algorithmic bytes of the chain (each distinct input
+read once + each output written once, all ranks) / step time, inputs resident in HBM.
+``e2e`` = the same with host buffers: every step copies this rank's x and y rows from pinned
+host memory and reads the two results back.
+
+``--impl reference`` times the CPU restatement of the reference's op-ompsimd executor
+(oracle/) on the host cores, on a bounded row sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+ROWS, COLS = 2048, 1 << 20
+BLOCK_ROWS = 256            # data is generated per 256-row block, seed = block index
+METRIC = "achieved HBM GB/s per op (chain: exp, mul, add, global sum, row max)"
+UNIT = "GB/s"
+
+
+def chain_bytes(rows: int) -> int:
+    """Algorithmic bytes of one chain pass over `rows` rows of f32[.., 1048576]."""
+    t = rows * COLS * 4
+    return 2 * t + 3 * t + 3 * t + (t + 4) + (t + rows * 4)
+
+
+def gen_block(block: int, which: str):
+    import numpy as np
+    rng = np.random.default_rng(block if which == "x" else 100000 + block)
+    return rng.random((BLOCK_ROWS, COLS), dtype=np.float32) * np.float32(2) - np.float32(1)
+
+
+def measured_peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 50 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50",
+                                          "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------------
+def run_reference(args) -> None:
+    """CPU arm: the oracle port of op-ompsimd on the host cores, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import oracle as O
+    O.build()
+    threads = O.num_threads()
+    rows = 32  # bounded sample: 32 of the 2048 rows (32 Mi elements per tensor)
+    x = gen_block(0, "x")[:rows].copy()
+    y = gen_block(0, "y")[:rows].copy()
+
+    def step():
+        t = O.exp(x)
+        t = O.mul(t, y)
+        z = O.add(t, x)
+        s = O.reduce_all_parallel(O.SUM, z)
+        m = O.reducemax(z, [1])
+        return s, m
+
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    gbs = chain_bytes(rows) / dt / 1e9
+    sample = f"{rows} of {ROWS} rows of the same chain per step (f32 [{rows},{COLS}])"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "exp,mul,add,sum(all),reducemax(axis 1) on f32 [2048,1048576] U(-1,1); CPU arm runs a row sample",
+                   "rows": ROWS, "cols": COLS},
+        "cpu_baseline": {"value": round(gbs, 3), "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": round(gbs, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def cpu_baseline_leg() -> dict:
+    """Bounded CPU baseline beside the GPU number (rank 0, N=1): ~10 s of oracle work."""
+    import numpy as np
+    from oracle import oracle as O
+    O.build()
+    rows = 32
+    x = gen_block(0, "x")[:rows].copy()
+    y = gen_block(0, "y")[:rows].copy()
+
+    def step():
+        t = O.exp(x)
+        t = O.mul(t, y)
+        z = O.add(t, x)
+        O.reduce_all_parallel(O.SUM, z)
+        O.reducemax(z, [1])
+
+    step()
+    t0 = time.perf_counter()
+    n = 0
+    while n < 3 or (time.perf_counter() - t0 < 8.0 and n < 200):
+        step()
+        n += 1
+    dt = (time.perf_counter() - t0) / n
+    return {"value": round(chain_bytes(rows) / dt / 1e9, 3), "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+            "sample": f"{n} passes over {rows} of {ROWS} rows of the same chain (f32 [{rows},{COLS}])"}
+
+
+# ------------------------------------------------------------------------------------------------
+def per_op_table(torch, TF, N, peak: float) -> dict:
+    """Single-GPU GB/s of each op of the other configs (rotating buffers so L2 cannot help)."""
+    dev = torch.device("cuda", torch.cuda.current_device())
+    out: dict[str, dict] = {}
+
+    def timed(name, fns, nbytes, flops=None, iters=12):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(iters):
+            fns[i % len(fns)]()
+        e.record()
+        torch.cuda.synchronize()
+        ms = s.elapsed_time(e) / iters
+        if flops is None:
+            g = nbytes / ms / 1e6
+            out[name] = {"us": round(ms * 1e3, 1), "gbs": round(g, 1), "frac_hbm": round(g / peak, 3)}
+        else:
+            out[name] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1)}
+
+    R = 3  # rotating copies
+    g = torch.Generator(device=dev).manual_seed(0)
+    a = [torch.rand(4096, 4096, device=dev, generator=g) * 2 - 1 for _ in range(R)]
+    b = [torch.rand(4096, 4096, device=dev, generator=g) * 2 - 1 for _ in range(R)]
+    c = [torch.empty(4096, 4096, device=dev) for _ in range(R)]
+    timed("add_f32_4096x4096", [lambda i=i: TF.add(a[i], b[i], c[i]) for i in range(R)], 3 * 4096 * 4096 * 4)
+    del a, b, c
+    x = [torch.randn(8192, 8192, device=dev, generator=g) for _ in range(2)]
+    o = torch.empty(8192, device=dev)
+    nb = 8192 * 8192 * 4 + 8192 * 4
+    timed("sum_f32_8192x8192_last", [lambda i=i: TF.sum(x[i], [1], False, o) for i in range(2)], nb)
+    timed("sum_f32_8192x8192_axis0", [lambda i=i: TF.sum(x[i], [0], False, o) for i in range(2)], nb)
+    timed("max_f32_8192x8192_last", [lambda i=i: TF.reducemax(x[i], [1], False, o) for i in range(2)], nb)
+    timed("max_f32_8192x8192_axis0", [lambda i=i: TF.reducemax(x[i], [0], False, o) for i in range(2)], nb)
+    del x
+    k = [torch.randint(-100, 101, (64, 1024, 1024), dtype=torch.int32, device=dev, generator=g) for _ in range(2)]
+    o2 = torch.empty(64, dtype=torch.int32, device=dev)
+    timed("sum_i32_64x1024x1024_axes12", [lambda i=i: TF.sum(k[i], [1, 2], False, o2) for i in range(2)], 64 * 1024 * 1024 * 4 + 256)
+    del k
+    t = [torch.randn(32, 2048, 32, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(2)]
+    to = torch.empty(32, 32, 2048, 128, dtype=torch.bfloat16, device=dev)
+    timed("transpose_bf16_32x2048x32x128_0213", [lambda i=i: TF.transpose(t[i], [0, 2, 1, 3], to) for i in range(2)], 2 * to.numel() * 2)
+    del t, to
+    parts = [torch.randn(8, 1024, 4096, device=dev, generator=g) for _ in range(4)]
+    co = torch.empty(8, 4096, 4096, device=dev)
+    timed("concat_4x_f32_8x1024x4096_axis1", [lambda: TF.concat(parts, 1, co)], 2 * co.numel() * 4)
+    del parts, co
+    r = torch.randn(1, 4096, device=dev, generator=g)
+    bo = [torch.empty(8192, 4096, device=dev) for _ in range(R)]
+    timed("broadcastTo_f32_1x4096_to_8192x4096", [lambda i=i: TF.broadcastTo(r, [8192, 4096], bo[i]) for i in range(R)], 8192 * 4096 * 4 + 4096 * 4)
+    del bo
+    table = torch.randn(151936, 896, device=dev, generator=g) * 0.02
+    idx = [torch.randint(0, 151936, (8, 2048), dtype=torch.int32, device=dev, generator=g) for _ in range(R)]
+    go = [torch.empty(8, 2048, 896, device=dev) for _ in range(R)]
+    timed("indexselect_f32_151936x896_by_8x2048", [lambda i=i: TF.indexselect(table, idx[i], 0, go[i]) for i in range(R)],
+          2 * 8 * 2048 * 896 * 4 + 8 * 2048 * 4)
+    del table, idx, go
+    A = (torch.randn(8192, 4096, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    B = (torch.randn(4096, 4096, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+    Cm = torch.empty(8192, 4096, dtype=torch.bfloat16, device=dev)
+    timed("matmul_bf16_8192x4096x4096", [lambda: TF.matmul(A, B, Cm)], 0, flops=2 * 8192 * 4096 * 4096, iters=20)
+    N.check(N.lib.dx_matmul_status(None))
+    return out
+
+
+def run_ours(args) -> None:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from deepx_b200 import _native as N
+    from deepx_b200.sharded import RowPartition, ShardedOps
+    ops = ShardedOps()
+    part = RowPartition(ROWS, world)
+    my_rows = part.count(rank)
+    row0 = part.start(rank)
+
+    # ---- this rank's rows, generated per 256-row block (seed = block index), pinned on the host
+    hx = torch.empty((my_rows, COLS), dtype=torch.float32).pin_memory()
+    hy = torch.empty((my_rows, COLS), dtype=torch.float32).pin_memory()
+    pieces = []
+    r = row0
+    while r < row0 + my_rows:
+        blk, off = divmod(r, BLOCK_ROWS)
+        n = min(BLOCK_ROWS - off, row0 + my_rows - r)
+        pieces.append((blk, off, n, r - row0))
+        r += n
+
+    def fill(job):
+        (blk, off, n, dst), which = job
+        host = hx if which == "x" else hy
+        host[dst:dst + n].copy_(torch.from_numpy(gen_block(blk, which)[off:off + n]))
+
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(max_workers=min(8, max(1, (os.cpu_count() or 8) // max(world, 1)))) as ex:
+        list(ex.map(fill, [(pc, w) for pc in pieces for w in ("x", "y")]))
+
+    x = torch.empty((my_rows, COLS), dtype=torch.float32, device=dev)
+    y = torch.empty_like(x)
+    t = torch.empty_like(x)
+    z = torch.empty_like(x)
+    s = torch.empty(1, dtype=torch.float32, device=dev)
+    m = torch.empty(my_rows, dtype=torch.float32, device=dev)
+    hs = torch.empty(1, dtype=torch.float32).pin_memory()
+    hm = torch.empty(my_rows, dtype=torch.float32).pin_memory()
+    x.copy_(hx, non_blocking=True)
+    y.copy_(hy, non_blocking=True)
+    torch.cuda.synchronize()
+
+    mul_events: list = []
+
+    def chain(record_mul: bool = False):
+        ops.exp(x, t)
+        if record_mul:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        ops.mul(t, y, t)
+        if record_mul:
+            e1.record()
+            mul_events.append((e0, e1))
+        ops.add(t, x, z)
+        ops.sum(z, [0, 1], False, s)
+        ops.reducemax(z, [1], False, m)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # ---- device-resident number ----------------------------------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        chain()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    l0 = N.lib.dx_launch_count()
+    ms_total = timed(lambda: chain(True), args.steps)
+    launches = N.lib.dx_launch_count() - l0
+    clocks = sampler.stop() if sampler else None
+    ms_step = ms_total / args.steps
+    total_bytes = chain_bytes(ROWS)
+    value = total_bytes / ms_step / 1e6
+
+    # parity guard on the timed outputs: global sum and row max against float64 on this rank's rows
+    torch.cuda.synchronize()
+    z64 = None
+    got_sum = float(s.item())
+    ref_rows = min(my_rows, 8)
+    zz = (np.exp(hx[:ref_rows].numpy().astype(np.float64)).astype(np.float32) * hy[:ref_rows].numpy() + hx[:ref_rows].numpy())
+    got_m = m[:ref_rows].cpu().numpy()
+    if not np.allclose(got_m, zz.max(axis=1), rtol=1e-5, atol=1e-6):
+        raise SystemExit("bench: row max disagrees with the host reference — refusing to report a number")
+
+    mul_ms = statistics.mean(a.elapsed_time(b) for a, b in mul_events)
+    peak, peak_kind = measured_peaks()
+    mul_bytes = 3 * my_rows * COLS * 4
+    achieved = mul_bytes / mul_ms / 1e6
+
+    # ---- end-to-end number: host buffers in, results out, every step ---------------------------------
+    def e2e_step():
+        x.copy_(hx, non_blocking=True)
+        y.copy_(hy, non_blocking=True)
+        chain()
+        hs.copy_(s, non_blocking=True)
+        hm.copy_(m, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 5))
+    e2e_step()
+    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_value = total_bytes / e2e_ms / 1e6
+
+    line = {
+        "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "z=exp(x)*y+x, s=sum(z), m=reducemax(z,axis 1) on f32 [2048,1048576] U(-1,1) sharded on axis 0; "
+                               "deepxIR ops exp,mul,add,sum,reducemax",
+                   "rows": ROWS, "cols": COLS, "rows_per_gpu": my_rows, "parallelism": f"axis0-shard x{world}",
+                   "l2": "inputs larger than L2 (8 GiB per tensor)", "algorithmic_bytes_per_step": total_bytes},
+        "roofline": {"bound": "hbm", "kernel": "ew2_kernel<mul,f32> (t=t*y)", "achieved": round(achieved, 1), "peak": peak,
+                     "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": round(achieved / peak, 4),
+                     "traffic": None, "bytes_per_launch": mul_bytes, "us_per_launch": round(mul_ms * 1e3, 2)},
+        "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": 2 * my_rows * COLS * 4 * world,
+                "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "global_sum": got_sum,
+    }
+    if world == 1 and rank == 0:
+        try:
+            line["cpu_baseline"] = cpu_baseline_leg()
+        except Exception as ex:  # the CPU leg must never take the GPU number down with it
+            line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
+        if not args.no_ops:
+            del x, y, t, z
+            torch.cuda.empty_cache()
+            from deepx_b200 import tensorfunc as TF
+            line["ops"] = per_op_table(torch, TF, N, peak)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-op table of the other configs")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

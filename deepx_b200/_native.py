@@ -37,6 +37,7 @@ SIGNATURES = {
     "dx_last_error": (C.c_char_p, []),
     "dx_dtype_size": (_i, [_i]),
     "dx_sm_count": (_i, []),
+    "dx_launch_count": (C.c_ulonglong, []),
     "dx_ew_binary": (_i, [_i, _i, _vp, _vp, _vp, _i64, _vp]),
     "dx_ew_scalar": (_i, [_i, _i, _vp, _d, _i64, _vp, _i64, _vp]),
     "dx_ew_unary": (_i, [_i, _i, _vp, _vp, _i64, _vp]),

@@ -1,4 +1,5 @@
 // Error reporting, dtype table, device properties.
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -7,6 +8,7 @@
 namespace dx {
 
 static thread_local char g_err[512] = "";
+static std::atomic<unsigned long long> g_launches{0};
 
 void set_error(const char *fmt, ...) {
     va_list ap;
@@ -24,6 +26,7 @@ int fail(int code, const char *fmt, ...) {
 }
 
 int check_launch(const char *what) {
+    g_launches.fetch_add(1, std::memory_order_relaxed);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(DX_E_CUDA, "%s: %s", what, cudaGetErrorString(e));
     return DX_OK;
@@ -58,3 +61,5 @@ extern "C" int dx_dtype_size(int dtype) {
 }
 
 extern "C" int dx_sm_count(void) { return dx::sm_count(); }
+
+extern "C" unsigned long long dx_launch_count(void) { return dx::g_launches.load(std::memory_order_relaxed); }

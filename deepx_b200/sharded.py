@@ -1,0 +1,88 @@
+"""Axis-0 sharding of deepxIR elementwise and reduce ops across the GPUs of one node.
+
+One process per GPU (``torch.distributed``, NCCL over NVLink/NVSwitch).  A tensor is
+partitioned into contiguous row blocks of its leading axis; every rank owns one block in
+its own device pool.  Elementwise ops and reductions that do not touch axis 0 run on the
+local block with no communication; a reduction that includes axis 0 reduces the local
+block first and then combines the per-rank partials with ONE all-reduce (sum / product /
+max / min) — 4 bytes for a global sum, one row for an axis-0 reduce.  Ops that do not
+shard this way (matmul, general transposes) stay single-GPU.
+
+The reference has no multi-GPU code at all (no cudaSetDevice, streams or NCCL anywhere
+under executor/); this module is the multi-GPU extension of its tensorfunc interface.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Sequence
+
+import torch
+import torch.distributed as dist
+
+REDUCE_OPS = {"sum": dist.ReduceOp.SUM, "prod": dist.ReduceOp.PRODUCT, "reducemax": dist.ReduceOp.MAX,
+              "reducemin": dist.ReduceOp.MIN}
+
+
+@dataclass(frozen=True)
+class RowPartition:
+    """Contiguous split of ``rows`` leading-axis indices over ``world`` ranks: the first
+    ``rows % world`` ranks get one extra row."""
+    rows: int
+    world: int
+
+    def count(self, rank: int) -> int:
+        base, extra = divmod(self.rows, self.world)
+        return base + (1 if rank < extra else 0)
+
+    def start(self, rank: int) -> int:
+        base, extra = divmod(self.rows, self.world)
+        return rank * base + min(rank, extra)
+
+    def slice(self, rank: int) -> slice:
+        s = self.start(rank)
+        return slice(s, s + self.count(rank))
+
+
+def shards_axis0(dims: Sequence[int], ndim: int) -> bool:
+    """True when a reduction over ``dims`` (checked, non-negative) crosses the sharded axis."""
+    return ndim > 0 and 0 in set(int(d) for d in dims)
+
+
+def combine_partials(partial: torch.Tensor, op: str, group=None) -> torch.Tensor:
+    """All-reduce per-rank partial results in place.  Works on any backend: NCCL on the
+    GPUs, gloo on CPU tensors in the host-logic tests."""
+    if op not in REDUCE_OPS:
+        raise ValueError(f"unknown reduce op {op!r}")
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(partial, op=REDUCE_OPS[op], group=group)
+    return partial
+
+
+class ShardedOps:
+    """The tensorfunc interface on this rank's row block.
+
+    Elementwise calls forward to :mod:`deepx_b200.tensorfunc` unchanged.  ``sum`` / ``prod`` /
+    ``reducemax`` / ``reducemin`` take the LOCAL block and the output tensor; when axis 0 is
+    reduced the output holds the global result on every rank after the call.
+    """
+
+    def __init__(self, group=None):
+        from . import tensorfunc  # needs the CUDA library; imported here so the partition logic is usable without it
+        self.tf = tensorfunc
+        self.group = group
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+
+    def __getattr__(self, name):
+        return getattr(self.tf, name)
+
+    def _reduce(self, op: str, A: torch.Tensor, dims, keepdims: bool, B: torch.Tensor) -> None:
+        getattr(self.tf, op)(A, dims, keepdims, B)
+        cd = self.tf.checked_dims(A.shape, dims)
+        if shards_axis0(cd, A.dim()):
+            combine_partials(B, op, self.group)
+
+    def sum(self, A, dims, keepdims, B): self._reduce("sum", A, dims, keepdims, B)  # noqa: A003
+    def prod(self, A, dims, keepdims, B): self._reduce("prod", A, dims, keepdims, B)
+    def reducemax(self, A, dims, keepdims, B): self._reduce("reducemax", A, dims, keepdims, B)
+    def reducemin(self, A, dims, keepdims, B): self._reduce("reducemin", A, dims, keepdims, B)

@@ -57,6 +57,8 @@ const char *dx_last_error(void);
 int dx_dtype_size(int dtype);
 /* Number of SMs of the current device (cached per device). */
 int dx_sm_count(void);
+/* Kernels this library has launched in this process so far (all threads, all devices). */
+unsigned long long dx_launch_count(void);
 
 /* ---- elementwise: tensor ∘ tensor ---------------------------------------
  * Replaces launch_add/sub/mul/div/max/min/pow
