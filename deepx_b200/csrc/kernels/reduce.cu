@@ -23,6 +23,7 @@
 // and its max/min are racy read-modify-writes (:230-256, :339-365).
 #include <algorithm>
 #include <limits>
+#include <mutex>
 #include <vector>
 
 #include "common.cuh"
@@ -625,4 +626,55 @@ extern "C" int dx_reduce(int op, int dtype, const void *a, const int64_t *shape,
         case DX_I8: return run_op<int8_t>(op, pl, a, out, workspace, workspace_bytes, st);
         default: return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
     }
+}
+
+// ---- reduce without any device allocation ---------------------------------------------------------
+// Some hosts that embed this library cannot obtain device memory at the moment they need a
+// reduction: an executor whose whole memory budget was handed to a pre-sized pool, a plugin
+// running inside another framework's allocator callback, a service that forbids cudaMalloc
+// after start-up because it synchronises the device.  dx_reduce() leaves the cross-block scratch
+// to the caller; this variant brings its own, a fixed array that lives in the module image.
+//
+// The array costs DX_REDUCE_STATIC_SCRATCH bytes on every GPU that loads the library, until the
+// process exits.  Every call on a device uses the same array, so two calls that may run at the
+// same time on that device (different streams, different threads) would overwrite each other's
+// partials: keep such calls on one stream.  Nothing in the array has to start at zero — each
+// partial slot is written by exactly one block before the combining kernel reads it — so what
+// the previous call left behind is harmless and is not cleared.
+constexpr size_t DX_REDUCE_STATIC_SCRATCH = size_t(1) << 20;  // 1 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[DX_REDUCE_STATIC_SCRATCH];
+
+namespace {
+std::mutex g_static_mu;
+void *g_static_ptr[64] = {};  // per device: the array's DEVICE address (the symbol name is only a host-side handle)
+}
+
+extern "C" int dx_reduce_noalloc(int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
+                                 int ndims, void *out, void *stream) {
+    if (dx_dtype_size(dtype) == 0 || dtype == DX_BOOL)
+        return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
+    Plan pl;
+    if (int e = make_plan(dtype, shape, ndim, dims, ndims, sm_count(), &pl)) return e;
+    if (pl.workspace > DX_REDUCE_STATIC_SCRATCH)
+        return fail(DX_E_WORKSPACE,
+                    "reduce (no-alloc): this shape needs %zu bytes of scratch, the built-in scratch holds %zu; "
+                    "use dx_reduce with a caller-provided workspace",
+                    pl.workspace, (size_t)DX_REDUCE_STATIC_SCRATCH);
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+        return fail(DX_E_CUDA, "reduce (no-alloc): cannot identify the current device");
+    void *scratch;
+    {
+        // First call on a device: resolve where the array lives on THAT device (it must be current).
+        std::lock_guard<std::mutex> lk(g_static_mu);
+        if (!g_static_ptr[dev]) {
+            void *p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+            if (e != cudaSuccess || !p)
+                return fail(DX_E_CUDA, "reduce (no-alloc): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_static_ptr[dev] = p;
+        }
+        scratch = g_static_ptr[dev];
+    }
+    return dx_reduce(op, dtype, a, shape, ndim, dims, ndims, out, scratch, DX_REDUCE_STATIC_SCRATCH, stream);
 }

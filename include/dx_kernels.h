@@ -162,6 +162,22 @@ size_t dx_reduce_workspace_bytes(int op, int dtype, const int64_t *shape, int nd
 int dx_reduce(int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims, int ndims,
               void *out, void *workspace, size_t workspace_bytes, void *stream);
 
+/* Reduce for callers that cannot allocate device memory.  No counterpart in the reference.
+ * Same arguments and results as dx_reduce, minus the workspace: the cross-block scratch is a
+ * 1 MiB array built into the library image (present on every GPU that loads the library, for
+ * the life of the process).  Meant for hosts that have given their whole memory budget to a
+ * pre-sized pool, that run inside another allocator's callback, or that ban cudaMalloc after
+ * start-up because it stalls the device.  The call itself allocates and frees no device memory.
+ *  - A shape whose scratch need exceeds 1 MiB is refused with DX_E_WORKSPACE (the message gives
+ *    both sizes); use dx_reduce with your own workspace for those.
+ *  - The first call on each device looks up the array's device address (that device must be
+ *    current); make that first call before starting any stream capture.
+ *  - All calls on a device share the one array: calls that can overlap on the GPU (different
+ *    streams or threads) race on it.  Issue them on one stream.  The array is not cleared
+ *    between calls and does not need to be. */
+int dx_reduce_noalloc(int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
+                      int ndims, void *out, void *stream);
+
 /* ---- changeshape -----------------------------------------------------------
  * Replace launch_transpose/concat/broadcastTo/indexselect/repeat
  * (changeshape_miaobyte.cuh:16-88).  Pure data movement, bit-exact for every
