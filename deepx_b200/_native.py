@@ -46,6 +46,10 @@ SIGNATURES = {
     "dx_switch": (_i, [_i, _pvp, _i, _i, _vp, _vp, _i64, _vp]),
     "dx_cast": (_i, [_i, _vp, _i, _vp, _i64, _vp]),
     "dx_fill": (_i, [_i, _vp, _d, _i64, _i64, _vp]),
+    "dx_arange": (_i, [_i, _vp, _d, _d, _i64, _vp]),
+    "dx_uniform": (_i, [_i, _vp, _d, _d, C.c_uint64, _i64, _vp]),
+    "dx_normal": (_i, [_i, _vp, _d, _d, C.c_uint64, _i64, _vp]),
+    "dx_dropout": (_i, [_i, _vp, _d, C.c_uint64, _i64, _vp]),
     "dx_reduce_workspace_bytes": (_sz, [_i, _i, _pi64, _i, _pi32, _i]),
     "dx_reduce": (_i, [_i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp, _sz, _vp]),
     "dx_reduce_noalloc": (_i, [_i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp]),

@@ -1,0 +1,158 @@
+// C ABI of the executor (include/dx_executor.h).
+#include <cuda_runtime.h>
+
+#include <cstring>
+
+#include "core.hpp"
+#include "dx_executor.h"
+
+using namespace dxh;
+
+struct dx_exec {
+    Executor ex;
+    dx_exec(int device, size_t limit) : ex(device, limit) {}
+};
+
+namespace {
+thread_local std::string g_err;
+int put(const std::string &s, char *out, size_t cap) {
+    if (!out || s.size() + 1 > cap) return -1;
+    std::memcpy(out, s.c_str(), s.size() + 1);
+    return int(s.size());
+}
+struct ProbeTF : TF {
+    int index = -1;
+    std::shared_ptr<TF> clone() const override { return std::make_shared<ProbeTF>(*this); }
+};
+struct Registry {
+    TfFactory f;
+    int n = 0;
+};
+}  // namespace
+
+extern "C" {
+
+dx_exec *dx_exec_create(int device, size_t pool_limit_bytes) {
+    try {
+        return new dx_exec(device, pool_limit_bytes);
+    } catch (const std::exception &e) {
+        g_err = e.what();
+        return nullptr;
+    }
+}
+void dx_exec_destroy(dx_exec *e) { delete e; }
+const char *dx_exec_last_error(void) { return g_err.c_str(); }
+
+int dx_exec_run(dx_exec *e, const char *ir_line, char *reply, size_t cap) {
+    if (!e || !ir_line) { g_err = "null executor or IR line"; return -1; }
+    const OpResp r = e->ex.run_line(ir_line);
+    if (put(r.to_string(), reply, cap) < 0) { g_err = "reply buffer too small"; return -1; }
+    return r.result == "ok" ? 0 : 1;
+}
+
+int dx_exec_tensor_info(dx_exec *e, const char *name, int *dtype, int64_t *shape, int cap) {
+    if (!e || !name || !e->ex.mem().exists_tensor(name)) return -1;
+    auto t = e->ex.mem().get_tensor(name);
+    if (dtype) *dtype = t->dx();
+    for (int i = 0; i < t->shape.dim() && i < cap; ++i) shape[i] = t->shape.shape[i];
+    return t->shape.dim();
+}
+
+void *dx_exec_tensor_ptr(dx_exec *e, const char *name) {
+    if (!e || !name || !e->ex.mem().exists_tensor(name)) return nullptr;
+    return e->ex.mem().get_tensor(name)->data;
+}
+
+static int copy(dx_exec *e, const char *name, void *host, size_t bytes, bool up) {
+    if (!e || !name || !e->ex.mem().exists_tensor(name)) { g_err = std::string("tensor not found: ") + (name ? name : ""); return -1; }
+    auto t = e->ex.mem().get_tensor(name);
+    if (size_t(t->shape.bytes()) != bytes) {
+        g_err = "size mismatch: tensor holds " + std::to_string(t->shape.bytes()) + " bytes, caller gave " + std::to_string(bytes);
+        return -2;
+    }
+    if (bytes == 0) return 0;
+    cudaSetDevice(e->ex.mem().device());
+    cudaStream_t st = static_cast<cudaStream_t>(e->ex.mem().stream());
+    cudaError_t err = up ? cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, st)
+                         : cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, st);
+    if (err == cudaSuccess) err = cudaStreamSynchronize(st);
+    if (err != cudaSuccess) { g_err = cudaGetErrorString(err); return -4; }
+    return 0;
+}
+int dx_exec_upload(dx_exec *e, const char *name, const void *host, size_t bytes) { return copy(e, name, const_cast<void *>(host), bytes, true); }
+int dx_exec_download(dx_exec *e, const char *name, void *host, size_t bytes) { return copy(e, name, host, bytes, false); }
+
+int dx_exec_sync(dx_exec *e) {
+    if (!e) return -1;
+    cudaSetDevice(e->ex.mem().device());
+    cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(e->ex.mem().stream()));
+    if (err != cudaSuccess) { g_err = cudaGetErrorString(err); return -4; }
+    return 0;
+}
+void *dx_exec_stream(dx_exec *e) { return e ? e->ex.mem().stream() : nullptr; }
+
+size_t dx_exec_op_table(dx_exec *e, char *out, size_t cap) {
+    if (!e) return 0;
+    const std::string s = e->ex.factory().print_markdown("op-b200");
+    if (out && cap > 0) {
+        const size_t n = std::min(cap - 1, s.size());
+        std::memcpy(out, s.data(), n);
+        out[n] = 0;
+    }
+    return s.size() + 1;
+}
+
+void dx_exec_stats(dx_exec *e, size_t stats[5]) {
+    if (!e || !stats) return;
+    dx_pool_stats(e->ex.mem().pool(), stats);
+    stats[4] = size_t(e->ex.ops_run());
+}
+
+int dx_ir_parse(const char *ir_line, char *out, size_t cap) {
+    try {
+        TF t;
+        t.parse(ir_line ? ir_line : "");
+        std::string s = t.name + "|";
+        for (size_t i = 0; i < t.args.size(); ++i) s += (i ? "," : "") + t.args[i].to_string();
+        s += "|";
+        for (size_t i = 0; i < t.returns.size(); ++i) s += (i ? "," : "") + t.returns[i].to_string();
+        s += "|author=" + t.metadata.author + " id=" + std::to_string(t.metadata.id) + " repeat=" + std::to_string(t.metadata.benchmark_repeat);
+        return put(s, out, cap);
+    } catch (const std::exception &e) {
+        return put(std::string("!") + e.what(), out, cap);
+    }
+}
+int dx_ir_dtype_roundtrip(const char *text, char *out, size_t cap) { return put(typedef_str(typedef_of(text ? text : "")), out, cap); }
+
+void *dx_registry_new(int with_builtin_ops) {
+    auto *r = new Registry();
+    if (with_builtin_ops) {
+        register_all(r->f);
+        r->n = int(r->f.size());
+    }
+    return r;
+}
+void dx_registry_free(void *r) { delete static_cast<Registry *>(r); }
+int dx_registry_add(void *rv, const char *signature_ir) {
+    auto *r = static_cast<Registry *>(rv);
+    try {
+        auto t = std::make_shared<ProbeTF>();
+        t->parse(signature_ir);
+        t->index = r->n++;
+        r->f.add_tf(t);
+        return t->index;
+    } catch (...) { return -1; }
+}
+int dx_registry_get(void *rv, const char *call_ir) {
+    auto *r = static_cast<Registry *>(rv);
+    try {
+        TF q;
+        q.parse(call_ir);
+        auto got = r->f.get_tf(q);
+        if (!got) return -1;
+        if (auto p = dynamic_cast<ProbeTF *>(got.get())) return p->index;
+        return -2;  // a built-in op matched
+    } catch (...) { return -1; }
+}
+int dx_registry_size(void *rv) { return int(static_cast<Registry *>(rv)->f.size()); }
+}

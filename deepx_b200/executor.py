@@ -1,0 +1,175 @@
+"""ctypes front of ``libdeepx_exec.so`` (C ABI in ``include/dx_executor.h``): the deepxIR text
+boundary.  ``Executor.run(ir_line)`` is what the reference's executor process does with one UDP
+datagram line — parse, resolve in the op registry, run on the GPU, reply — in process.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libdeepx_exec.so"
+BIN_PATH = _PKG / "deepx-op-b200"
+
+_vp, _i, _sz, _cp = C.c_void_p, C.c_int, C.c_size_t, C.c_char_p
+SIGNATURES = {
+    "dx_exec_create": (_vp, [_i, _sz]),
+    "dx_exec_destroy": (None, [_vp]),
+    "dx_exec_last_error": (_cp, []),
+    "dx_exec_run": (_i, [_vp, _cp, C.c_char_p, _sz]),
+    "dx_exec_tensor_info": (_i, [_vp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int64), _i]),
+    "dx_exec_tensor_ptr": (_vp, [_vp, _cp]),
+    "dx_exec_upload": (_i, [_vp, _cp, _vp, _sz]),
+    "dx_exec_download": (_i, [_vp, _cp, _vp, _sz]),
+    "dx_exec_sync": (_i, [_vp]),
+    "dx_exec_stream": (_vp, [_vp]),
+    "dx_exec_op_table": (_sz, [_vp, C.c_char_p, _sz]),
+    "dx_exec_stats": (None, [_vp, C.POINTER(C.c_size_t)]),
+    "dx_ir_parse": (_i, [_cp, C.c_char_p, _sz]),
+    "dx_ir_dtype_roundtrip": (_i, [_cp, C.c_char_p, _sz]),
+    "dx_registry_new": (_vp, [_i]),
+    "dx_registry_free": (None, [_vp]),
+    "dx_registry_add": (_i, [_vp, _cp]),
+    "dx_registry_get": (_i, [_vp, _cp]),
+    "dx_registry_size": (_i, [_vp]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python -m deepx_b200.build`. There is no CPU fallback.")
+        _lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(_lib, name)
+            fn.restype = res
+            fn.argtypes = args
+    return _lib
+
+
+_DX2NP = {0: np.float64, 1: np.float32, 2: np.float16, 3: None, 4: np.int64, 5: np.int32, 6: np.int16, 7: np.int8, 8: np.bool_}
+
+
+def _bf16():
+    import ml_dtypes
+    return ml_dtypes.bfloat16
+
+
+def parse_ir(line: str) -> str:
+    """What the parser understood, as one canonical line ("!…" for a parse error)."""
+    buf = C.create_string_buffer(1 << 16)
+    lib().dx_ir_parse(line.encode(), buf, len(buf))
+    return buf.value.decode()
+
+
+def dtype_roundtrip(text: str) -> str:
+    buf = C.create_string_buffer(4096)
+    lib().dx_ir_dtype_roundtrip(text.encode(), buf, len(buf))
+    return buf.value.decode()
+
+
+class Registry:
+    """An op registry on its own (no GPU): add signature lines, resolve calls."""
+
+    def __init__(self, builtin: bool = False):
+        self._h = lib().dx_registry_new(1 if builtin else 0)
+
+    def add(self, signature_ir: str) -> int:
+        return lib().dx_registry_add(self._h, signature_ir.encode())
+
+    def get(self, call_ir: str) -> int:
+        return lib().dx_registry_get(self._h, call_ir.encode())
+
+    def __len__(self) -> int:
+        return lib().dx_registry_size(self._h)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib().dx_registry_free(self._h)
+            self._h = None
+
+
+class IRError(RuntimeError):
+    pass
+
+
+class Executor:
+    def __init__(self, device: int = 0, pool_limit_bytes: int = 0):
+        self._h = lib().dx_exec_create(device, pool_limit_bytes)
+        if not self._h:
+            raise RuntimeError("cannot create executor: " + lib().dx_exec_last_error().decode())
+        self._buf = C.create_string_buffer(1 << 16)
+
+    def close(self):
+        if self._h:
+            lib().dx_exec_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def reply(self, ir_line: str) -> tuple[int, str]:
+        rc = lib().dx_exec_run(self._h, ir_line.encode(), self._buf, len(self._buf))
+        return rc, self._buf.value.decode()
+
+    def run(self, ir_line: str) -> str:
+        """Runs one IR line; raises IRError with the reply text when the executor answers `error`."""
+        rc, text = self.reply(ir_line)
+        if rc != 0:
+            raise IRError(text)
+        return text
+
+    def info(self, name: str):
+        dt = C.c_int()
+        shape = (C.c_int64 * 12)()
+        nd = lib().dx_exec_tensor_info(self._h, name.encode(), C.byref(dt), shape, 12)
+        if nd < 0:
+            raise KeyError(name)
+        return dt.value, [int(shape[i]) for i in range(nd)]
+
+    def ptr(self, name: str) -> int:
+        return int(lib().dx_exec_tensor_ptr(self._h, name.encode()) or 0)
+
+    def new(self, name: str, dtype: str, shape) -> None:
+        self.run(f"newtensor(vector<int32>:[{' '.join(str(int(s)) for s in shape)}])->(tensor<{dtype}>:{name})")
+
+    def upload(self, name: str, array: np.ndarray) -> None:
+        a = np.ascontiguousarray(array)
+        rc = lib().dx_exec_upload(self._h, name.encode(), a.ctypes.data, a.nbytes)
+        if rc != 0:
+            raise RuntimeError(lib().dx_exec_last_error().decode())
+
+    def put(self, name: str, array: np.ndarray, dtype: str | None = None) -> None:
+        """newtensor + upload."""
+        a = np.ascontiguousarray(array)
+        dtype = dtype or ("bfloat16" if a.dtype == np.dtype(_bf16()) else str(a.dtype))
+        self.new(name, dtype, a.shape)
+        self.upload(name, a)
+
+    def download(self, name: str) -> np.ndarray:
+        code, shape = self.info(name)
+        npdt = _bf16() if code == 3 else _DX2NP[code]
+        out = np.empty(shape, dtype=npdt)
+        rc = lib().dx_exec_download(self._h, name.encode(), out.ctypes.data, out.nbytes)
+        if rc != 0:
+            raise RuntimeError(lib().dx_exec_last_error().decode())
+        return out
+
+    def sync(self) -> None:
+        lib().dx_exec_sync(self._h)
+
+    def op_table(self) -> str:
+        n = lib().dx_exec_op_table(self._h, None, 0)
+        buf = C.create_string_buffer(n)
+        lib().dx_exec_op_table(self._h, buf, n)
+        return buf.value.decode()
+
+    def stats(self) -> dict:
+        st = (C.c_size_t * 5)()
+        lib().dx_exec_stats(self._h, st)
+        return {"in_use": st[0], "reserved": st[1], "high_water": st[2], "driver_allocs": st[3], "ops_run": st[4]}

@@ -1,0 +1,67 @@
+/*
+ * dx_executor.h — C ABI of the deepxIR executor (libdeepx_exec.so).
+ *
+ * One handle = what one reference executor process holds: the tensor store (`Mem`,
+ * executor/deepxcore/src/deepx/mem/mem.hpp), the op registry filled by register_all
+ * (executor/op-cuda/src/client/tfs.cpp:636-646) and a device pool + stream.  dx_exec_run takes
+ * one deepxIR text line and produces the reply line the reference's main loop would send over
+ * UDP (executor/op-cuda/src/client/main.cpp:47-102, reply format tf.hpp:198-213); the
+ * `deepx-op-b200` binary is exactly this behind a UDP socket.  The upload/download calls are the
+ * in-process stand-in for the on-disk tensor exchange (save/load IR ops work too).
+ * All functions return 0 on success and a negative value on failure unless stated otherwise.
+ */
+#ifndef DX_EXECUTOR_H
+#define DX_EXECUTOR_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct dx_exec dx_exec;
+
+/* pool_limit_bytes = 0: no limit.  NULL on failure (dx_exec_last_error has the reason). */
+dx_exec *dx_exec_create(int device, size_t pool_limit_bytes);
+void dx_exec_destroy(dx_exec *e);
+const char *dx_exec_last_error(void);
+
+/* Runs one IR line.  Writes the NUL-terminated reply ("<id> ok// recv_at=… start_at=… finish_at=…"
+ * or "<id> error// … <message>") into reply[cap].  Returns 0 when the op succeeded, 1 when the
+ * reply is an error reply, -1 when reply does not fit. */
+int dx_exec_run(dx_exec *e, const char *ir_line, char *reply, size_t cap);
+
+/* Tensor metadata: dtype is a dx_dtype code; shape receives up to cap extents; returns the rank,
+ * or -1 if there is no such tensor. */
+int dx_exec_tensor_info(dx_exec *e, const char *name, int *dtype, int64_t *shape, int cap);
+/* Device pointer of a tensor's storage (NULL if absent). */
+void *dx_exec_tensor_ptr(dx_exec *e, const char *name);
+/* Copies host bytes into / out of an existing tensor (exactly its size in bytes). Synchronous. */
+int dx_exec_upload(dx_exec *e, const char *name, const void *host, size_t bytes);
+int dx_exec_download(dx_exec *e, const char *name, void *host, size_t bytes);
+/* Waits for everything submitted so far. */
+int dx_exec_sync(dx_exec *e);
+/* The executor's CUDA stream (cudaStream_t as void*). */
+void *dx_exec_stream(dx_exec *e);
+/* Markdown op table (TfFactory::print_markdown, tffactory.cpp:85-119); returns bytes needed. */
+size_t dx_exec_op_table(dx_exec *e, char *out, size_t cap);
+/* Pool statistics as dx_pool_stats, plus [4] = ops run. */
+void dx_exec_stats(dx_exec *e, size_t stats[5]);
+
+/* Parser / registry probes that need no GPU (used by the differential tests):
+ * canonical one-line rendering of what the parser understood:
+ * "<name>|<arg dtype>:<arg text>,…|<ret dtype>:<ret text>,…|author=<a> id=<n> repeat=<n>", or "!<error>". */
+int dx_ir_parse(const char *ir_line, char *out, size_t cap);
+int dx_ir_dtype_roundtrip(const char *text, char *out, size_t cap);
+/* A registry without an executor: add signature lines, ask which registration a call resolves to. */
+void *dx_registry_new(int with_builtin_ops);
+void dx_registry_free(void *r);
+int dx_registry_add(void *r, const char *signature_ir);
+int dx_registry_get(void *r, const char *call_ir); /* index in registration order, -1 = no match */
+int dx_registry_size(void *r);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -146,6 +146,16 @@ int dx_cast(int src_dtype, const void *a, int dst_dtype, void *c, int64_t n, voi
  * Replaces launch_constant (init_miaobyte.cuh:11). */
 int dx_fill(int dtype, void *c, double fscalar, int64_t iscalar, int64_t n, void *stream);
 
+/* ---- initialisers ----------------------------------------------------------
+ * Replace launch_arange/uniform/normal/dropout (init_miaobyte.cuh:19-47).
+ * arange: out[i] = T(float(start) + float(step) * float(i)), the reference's fp32 form.
+ * uniform [low, high), normal(mean, stddev), dropout (zero with probability p, in place):
+ * element i depends on (seed, i) only. */
+int dx_arange(int dtype, void *out, double start, double step, int64_t n, void *stream);
+int dx_uniform(int dtype, void *out, double low, double high, uint64_t seed, int64_t n, void *stream);
+int dx_normal(int dtype, void *out, double mean, double stddev, uint64_t seed, int64_t n, void *stream);
+int dx_dropout(int dtype, void *inout, double p, uint64_t seed, int64_t n, void *stream);
+
 /* ---- reduce ----------------------------------------------------------------
  * Replaces launch_sum/prod/reducemax/reducemin (reduce_miaobyte.cuh:16-56).
  * Reduces `a` (row-major `shape[ndim]`) over the axes in `dims[ndims]`
