@@ -33,6 +33,8 @@ sys.path.insert(0, str(ROOT))
 
 ROWS, COLS = 2048, 1 << 20
 BLOCK_ROWS = 256            # data is generated per 256-row block, seed = block index
+# dram__bytes_read.sum + dram__bytes_write.sum of ew2_kernel<mul,f32> on a 256-row slab, per row
+MUL_TRAFFIC_PER_ROW = 3.180764e9 / 256
 METRIC = "achieved HBM GB/s per op (chain: exp, mul, add, global sum, row max)"
 UNIT = "GB/s"
 
@@ -178,71 +180,151 @@ def cpu_baseline_leg() -> dict:
 
 
 # ------------------------------------------------------------------------------------------------
+def op_cases(torch, TF, dev):
+    """name -> builder returning (list of launch closures over rotating buffers, algorithmic bytes, flops or None).
+    The ops of BASELINE configs 0-3 at their stated shapes, plus the chain ops on a 1 GiB slab."""
+    g = torch.Generator(device=dev).manual_seed(0)
+    R = 3
+
+    def rnd(*shape, n=1, dtype=torch.float32):
+        return [(torch.rand(*shape, device=dev, generator=g) * 2 - 1).to(dtype) for _ in range(n)]
+
+    def nrm(*shape, n=1, dtype=torch.float32, scale=1.0):
+        return [(torch.randn(*shape, device=dev, generator=g) * scale).to(dtype) for _ in range(n)]
+
+    def add_f32():
+        a, b = rnd(4096, 4096, n=R), rnd(4096, 4096, n=R)
+        c = [torch.empty(4096, 4096, device=dev) for _ in range(R)]
+        return [lambda i=i: TF.add(a[i], b[i], c[i]) for i in range(R)], 3 * 4096 * 4096 * 4, None
+
+    def reduce_f32(op, dims):
+        def build():
+            x = nrm(8192, 8192, n=2)
+            o = torch.empty(8192, device=dev)
+            return [lambda i=i: getattr(TF, op)(x[i], dims, False, o) for i in range(2)], 8192 * 8192 * 4 + 8192 * 4, None
+        return build
+
+    def sum_i32():
+        k = [torch.randint(-100, 101, (64, 1024, 1024), dtype=torch.int32, device=dev, generator=g) for _ in range(2)]
+        o = torch.empty(64, dtype=torch.int32, device=dev)
+        return [lambda i=i: TF.sum(k[i], [1, 2], False, o) for i in range(2)], 64 * 1024 * 1024 * 4 + 256, None
+
+    def transpose_bf16():
+        t = nrm(32, 2048, 32, 128, n=2, dtype=torch.bfloat16)
+        o = torch.empty(32, 32, 2048, 128, dtype=torch.bfloat16, device=dev)
+        return [lambda i=i: TF.transpose(t[i], [0, 2, 1, 3], o) for i in range(2)], 2 * o.numel() * 2, None
+
+    def concat_f32():
+        parts = nrm(8, 1024, 4096, n=4)
+        o = torch.empty(8, 4096, 4096, device=dev)
+        return [lambda: TF.concat(parts, 1, o)], 2 * o.numel() * 4, None
+
+    def broadcast_f32():
+        r = nrm(1, 4096)[0]
+        o = [torch.empty(8192, 4096, device=dev) for _ in range(R)]
+        return [lambda i=i: TF.broadcastTo(r, [8192, 4096], o[i]) for i in range(R)], 8192 * 4096 * 4 + 4096 * 4, None
+
+    def indexselect_f32():
+        table = nrm(151936, 896, scale=0.02)[0]
+        idx = [torch.randint(0, 151936, (8, 2048), dtype=torch.int32, device=dev, generator=g) for _ in range(R)]
+        o = [torch.empty(8, 2048, 896, device=dev) for _ in range(R)]
+        return [lambda i=i: TF.indexselect(table, idx[i], 0, o[i]) for i in range(R)], 2 * 8 * 2048 * 896 * 4 + 8 * 2048 * 4, None
+
+    def matmul_bf16():
+        A = nrm(8192, 4096, dtype=torch.bfloat16, scale=0.02)[0]
+        B = nrm(4096, 4096, dtype=torch.bfloat16, scale=0.02)[0]
+        Cm = torch.empty(8192, 4096, dtype=torch.bfloat16, device=dev)
+        return [lambda: TF.matmul(A, B, Cm)], 0, 2 * 8192 * 4096 * 4096
+
+    def rms(opname):
+        def build():
+            x = nrm(16, 2048, 896, n=R)
+            y = [torch.empty(16, 2048, 896, device=dev) for _ in range(R)]
+            v = torch.empty(16, 2048, 1, device=dev)
+            n = 16 * 2048 * 896 * 4
+            if opname == "mul":
+                return [lambda i=i: TF.mul(x[i], x[i], y[i]) for i in range(R)], 2 * n, None
+            if opname == "sum":
+                return [lambda i=i: TF.sum(x[i], [2], True, v) for i in range(R)], n + 16 * 2048 * 4, None
+            if opname == "broadcast":
+                return [lambda i=i: TF.broadcastTo(v, [16, 2048, 896], y[i]) for i in range(R)], n + 16 * 2048 * 4, None
+            return [lambda i=i: TF.mul(x[i], y[(i + 1) % R], y[i]) for i in range(R)], 3 * n, None
+        return build
+
+    def chain(opname):
+        def build():  # the bench chain on 256 of the 2048 rows (1 GiB per tensor): the size used for profiler captures
+            x, y = rnd(256, 1 << 20)[0], rnd(256, 1 << 20)[0]
+            t, z = torch.empty_like(x), torch.empty_like(x)
+            s1, m = torch.empty(1, device=dev), torch.empty(256, device=dev)
+            n = x.numel() * 4
+            return {"exp": ([lambda: TF.exp(x, t)], 2 * n, None), "mul": ([lambda: TF.mul(x, y, t)], 3 * n, None),
+                    "add": ([lambda: TF.add(x, y, z)], 3 * n, None), "sum": ([lambda: TF.sum(x, [0, 1], False, s1)], n + 4, None),
+                    "rowmax": ([lambda: TF.reducemax(x, [1], False, m)], n + 1024, None)}[opname]
+        return build
+
+    return {
+        "add_f32_4096x4096": add_f32,
+        "sum_f32_8192x8192_last": reduce_f32("sum", [1]), "sum_f32_8192x8192_axis0": reduce_f32("sum", [0]),
+        "max_f32_8192x8192_last": reduce_f32("reducemax", [1]), "max_f32_8192x8192_axis0": reduce_f32("reducemax", [0]),
+        "sum_i32_64x1024x1024_axes12": sum_i32,
+        "transpose_bf16_32x2048x32x128_0213": transpose_bf16, "concat_4x_f32_8x1024x4096_axis1": concat_f32,
+        "broadcastTo_f32_1x4096_to_8192x4096": broadcast_f32, "indexselect_f32_151936x896_by_8x2048": indexselect_f32,
+        "matmul_bf16_8192x4096x4096": matmul_bf16,
+        "rmsnorm_mul_xx_f32_16x2048x896": rms("mul"), "rmsnorm_sum_last_f32_16x2048x896": rms("sum"),
+        "rmsnorm_broadcast_f32_16x2048x1": rms("broadcast"), "rmsnorm_mul_xy_f32_16x2048x896": rms("mul3"),
+        "chain_exp_f32_256x1048576": chain("exp"), "chain_mul_f32_256x1048576": chain("mul"), "chain_add_f32_256x1048576": chain("add"),
+        "chain_sum_f32_256x1048576": chain("sum"), "chain_rowmax_f32_256x1048576": chain("rowmax"),
+    }
+
+
+def time_case(torch, fns, nbytes, flops, peak, iters, warmup=1):
+    for _ in range(max(warmup, 1)):
+        for f in fns:
+            f()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(iters):
+        fns[i % len(fns)]()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / iters
+    if flops is None:
+        gbs = nbytes / ms / 1e6
+        return {"us": round(ms * 1e3, 1), "gbs": round(gbs, 1), "frac_hbm": round(gbs / peak, 3)}
+    return {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1)}
+
+
 def per_op_table(torch, TF, N, peak: float) -> dict:
     """Single-GPU GB/s of each op of the other configs (rotating buffers so L2 cannot help)."""
     dev = torch.device("cuda", torch.cuda.current_device())
     out: dict[str, dict] = {}
-
-    def timed(name, fns, nbytes, flops=None, iters=12):
-        for f in fns:
-            f()
-        torch.cuda.synchronize()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for i in range(iters):
-            fns[i % len(fns)]()
-        e.record()
-        torch.cuda.synchronize()
-        ms = s.elapsed_time(e) / iters
-        if flops is None:
-            g = nbytes / ms / 1e6
-            out[name] = {"us": round(ms * 1e3, 1), "gbs": round(g, 1), "frac_hbm": round(g / peak, 3)}
-        else:
-            out[name] = {"us": round(ms * 1e3, 1), "tflops": round(flops / ms / 1e9, 1)}
-
-    R = 3  # rotating copies
-    g = torch.Generator(device=dev).manual_seed(0)
-    a = [torch.rand(4096, 4096, device=dev, generator=g) * 2 - 1 for _ in range(R)]
-    b = [torch.rand(4096, 4096, device=dev, generator=g) * 2 - 1 for _ in range(R)]
-    c = [torch.empty(4096, 4096, device=dev) for _ in range(R)]
-    timed("add_f32_4096x4096", [lambda i=i: TF.add(a[i], b[i], c[i]) for i in range(R)], 3 * 4096 * 4096 * 4)
-    del a, b, c
-    x = [torch.randn(8192, 8192, device=dev, generator=g) for _ in range(2)]
-    o = torch.empty(8192, device=dev)
-    nb = 8192 * 8192 * 4 + 8192 * 4
-    timed("sum_f32_8192x8192_last", [lambda i=i: TF.sum(x[i], [1], False, o) for i in range(2)], nb)
-    timed("sum_f32_8192x8192_axis0", [lambda i=i: TF.sum(x[i], [0], False, o) for i in range(2)], nb)
-    timed("max_f32_8192x8192_last", [lambda i=i: TF.reducemax(x[i], [1], False, o) for i in range(2)], nb)
-    timed("max_f32_8192x8192_axis0", [lambda i=i: TF.reducemax(x[i], [0], False, o) for i in range(2)], nb)
-    del x
-    k = [torch.randint(-100, 101, (64, 1024, 1024), dtype=torch.int32, device=dev, generator=g) for _ in range(2)]
-    o2 = torch.empty(64, dtype=torch.int32, device=dev)
-    timed("sum_i32_64x1024x1024_axes12", [lambda i=i: TF.sum(k[i], [1, 2], False, o2) for i in range(2)], 64 * 1024 * 1024 * 4 + 256)
-    del k
-    t = [torch.randn(32, 2048, 32, 128, device=dev, generator=g).to(torch.bfloat16) for _ in range(2)]
-    to = torch.empty(32, 32, 2048, 128, dtype=torch.bfloat16, device=dev)
-    timed("transpose_bf16_32x2048x32x128_0213", [lambda i=i: TF.transpose(t[i], [0, 2, 1, 3], to) for i in range(2)], 2 * to.numel() * 2)
-    del t, to
-    parts = [torch.randn(8, 1024, 4096, device=dev, generator=g) for _ in range(4)]
-    co = torch.empty(8, 4096, 4096, device=dev)
-    timed("concat_4x_f32_8x1024x4096_axis1", [lambda: TF.concat(parts, 1, co)], 2 * co.numel() * 4)
-    del parts, co
-    r = torch.randn(1, 4096, device=dev, generator=g)
-    bo = [torch.empty(8192, 4096, device=dev) for _ in range(R)]
-    timed("broadcastTo_f32_1x4096_to_8192x4096", [lambda i=i: TF.broadcastTo(r, [8192, 4096], bo[i]) for i in range(R)], 8192 * 4096 * 4 + 4096 * 4)
-    del bo
-    table = torch.randn(151936, 896, device=dev, generator=g) * 0.02
-    idx = [torch.randint(0, 151936, (8, 2048), dtype=torch.int32, device=dev, generator=g) for _ in range(R)]
-    go = [torch.empty(8, 2048, 896, device=dev) for _ in range(R)]
-    timed("indexselect_f32_151936x896_by_8x2048", [lambda i=i: TF.indexselect(table, idx[i], 0, go[i]) for i in range(R)],
-          2 * 8 * 2048 * 896 * 4 + 8 * 2048 * 4)
-    del table, idx, go
-    A = (torch.randn(8192, 4096, device=dev, generator=g) * 0.02).to(torch.bfloat16)
-    B = (torch.randn(4096, 4096, device=dev, generator=g) * 0.02).to(torch.bfloat16)
-    Cm = torch.empty(8192, 4096, dtype=torch.bfloat16, device=dev)
-    timed("matmul_bf16_8192x4096x4096", [lambda: TF.matmul(A, B, Cm)], 0, flops=2 * 8192 * 4096 * 4096, iters=20)
+    for name, build in op_cases(torch, TF, dev).items():
+        if name.startswith("chain_"):
+            continue
+        fns, nbytes, flops = build()
+        out[name] = time_case(torch, fns, nbytes, flops, peak, iters=20 if flops else 12)
+        del fns
+        torch.cuda.empty_cache()
     N.check(N.lib.dx_matmul_status(None))
     return out
+
+
+def run_one_op(args) -> None:
+    """`--op NAME`: one op of the table on its own (what the profiler captures are taken on)."""
+    import torch
+    from deepx_b200 import _native as N
+    from deepx_b200 import tensorfunc as TF
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    cases = op_cases(torch, TF, dev)
+    if args.op not in cases:
+        raise SystemExit("unknown --op; choose from: " + ", ".join(cases))
+    fns, nbytes, flops = cases[args.op]()
+    peak, kind = measured_peaks()
+    res = time_case(torch, fns, nbytes, flops, peak, iters=args.steps, warmup=args.warmup)
+    res.update({"op": args.op, "steps": args.steps, "algorithmic_bytes": nbytes, "peak_source": kind})
+    print(json.dumps(res), flush=True)
 
 
 def run_ours(args) -> None:
@@ -386,7 +468,9 @@ def run_ours(args) -> None:
                    "l2": "inputs larger than L2 (8 GiB per tensor)", "algorithmic_bytes_per_step": total_bytes},
         "roofline": {"bound": "hbm", "kernel": "ew2_kernel<mul,f32> (t=t*y)", "achieved": round(achieved, 1), "peak": peak,
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": round(achieved / peak, 4),
-                     "traffic": None, "bytes_per_launch": mul_bytes, "us_per_launch": round(mul_ms * 1e3, 2)},
+                     "traffic": round(MUL_TRAFFIC_PER_ROW * my_rows), "traffic_source": "ncu dram read+write of the same kernel on 256 rows "
+                     "(profiles/ew2_mul_f32_chain_256x1048576.md), scaled by rows",
+                     "bytes_per_launch": mul_bytes, "us_per_launch": round(mul_ms * 1e3, 2)},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": 2 * my_rows * COLS * 4 * world,
                 "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
         "gpu_launches": int(launches),
@@ -416,8 +500,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table of the other configs")
+    ap.add_argument("--op", default=None, help="time one named op of the per-op table alone (single GPU)")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.op:
+        run_one_op(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
