@@ -34,6 +34,7 @@ namespace {
 constexpr int RB = 256;      // threads per CTA
 constexpr int RUNROLL = 4;   // independent 16-byte loads per thread per step
 constexpr int MAXG = 6;      // ≤ 12 axes → ≤ 6 groups of each class
+constexpr int TEAM_UNROLL = 8;  // vectors a lane of the team kernel keeps in flight
 
 // ---- accumulation types and combine rules ----------------------------------------
 template <typename T> struct acc_of { using type = T; };
@@ -230,20 +231,20 @@ __global__ void __launch_bounds__(RB) rows_team_kernel(const T *__restrict__ in,
         return base + unravel(seg, p.rout) + int64_t(pos) * VEC;
     };
     if (live) {
-        uint32_t u = lane;
-        for (; u + (RUNROLL - 1) * team < p.units; u += RUNROLL * team) {
-            Pack<T, VEC> v[RUNROLL];
+        // Short runs: a lane owns at most a handful of vectors, so issue up to TEAM_UNROLL of them
+        // (predicated) before the first use instead of a 4-wide body plus a serial remainder.
+#pragma unroll 1
+        for (uint32_t u0 = lane; u0 < p.units; u0 += TEAM_UNROLL * team) {
+            Pack<T, VEC> v[TEAM_UNROLL];
 #pragma unroll
-            for (int k = 0; k < RUNROLL; ++k) v[k] = ld_stream<T, VEC>(addr(u + k * team));
+            for (int k = 0; k < TEAM_UNROLL; ++k)
+                if (u0 + k * team < p.units) v[k] = ld_stream<T, VEC>(addr(u0 + k * team));
 #pragma unroll
-            for (int k = 0; k < RUNROLL; ++k)
+            for (int k = 0; k < TEAM_UNROLL; ++k)
+                if (u0 + k * team < p.units) {
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v[k].v[i]));
-        }
-        for (; u < p.units; u += team) {
-            Pack<T, VEC> v = ld_stream<T, VEC>(addr(u));
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v.v[i]));
+                    for (int i = 0; i < VEC; ++i) acc[i] = combine<OP>(acc[i], widen<T>(v[k].v[i]));
+                }
         }
     }
     A r = acc[0];
@@ -427,7 +428,8 @@ int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, in
     int vec = 16 / es;  // full 16-byte vectors when the contiguous run allows it, else scalar
     if (inner % vec != 0) vec = 1;
     pl->vec = vec;
-    const int target_ctas = sms * 8;
+    // resident CTAs per SM: the rows kernels fit 8 (32 registers), the cols kernel 6 (39 registers)
+    const int target_ctas = sms * (g.back().red ? 8 : 6);
 
     if (g.back().red) {
         RowsParams &p = pl->rows;
@@ -451,7 +453,7 @@ int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, in
             pl->kind = PLAN_ROWS_BLOCK;
             int64_t split = 1;
             if (nout < target_ctas) {
-                const int64_t by_target = (target_ctas + nout - 1) / nout;
+                const int64_t by_target = target_ctas / nout;  // floor: one wave, no straggler CTAs
                 const int64_t by_work = std::max<int64_t>(1, units / (RB * RUNROLL * 2));
                 split = std::max<int64_t>(1, std::min(by_target, by_work));
             }
@@ -485,7 +487,7 @@ int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, in
         int64_t split = 1;
         const int64_t ctas = ctiles * nko;
         if (ctas < target_ctas) {
-            const int64_t by_target = (target_ctas + ctas - 1) / ctas;
+            const int64_t by_target = target_ctas / ctas;  // floor: one wave, no straggler CTAs
             const int64_t by_work = std::max<int64_t>(1, rows / (ny * RUNROLL * 2));
             split = std::max<int64_t>(1, std::min(by_target, by_work));
         }
