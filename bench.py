@@ -51,6 +51,20 @@ def gen_block(block: int, which: str):
     return rng.random((BLOCK_ROWS, COLS), dtype=np.float32) * np.float32(2) - np.float32(1)
 
 
+def ctypes_ptr(ex) -> int:
+    """The executor's CUDA stream handle as an integer."""
+    from deepx_b200 import executor as E
+    return int(E.lib().dx_exec_stream(ex._h) or 0)
+
+
+def download_into(ex, name: str, out) -> None:
+    """Device → the caller's (pinned) host array, through the executor's C ABI."""
+    from deepx_b200 import executor as E
+    rc = E.lib().dx_exec_download(ex._h, name.encode(), out.ctypes.data, out.nbytes)
+    if rc != 0:
+        raise RuntimeError(E.lib().dx_exec_last_error().decode())
+
+
 def measured_peaks() -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -465,17 +479,62 @@ def run_ours(args) -> None:
     mul_bytes = 3 * my_rows * COLS * 4
     achieved = mul_bytes / mul_ms / 1e6
 
-    # ---- end-to-end number: host buffers in, results out, every step ---------------------------------
+    # ---- end-to-end number: through the deepxIR executor (the reference-facing boundary), host buffers
+    # in, results out, every step.  The device-resident tensors above are released first.
+    del x, y, t, z
+    torch.cuda.empty_cache()
+    from deepx_b200.executor import Executor
+    ex = Executor(local_rank)
+    f32 = "tensor<float32>"
+    for nm, shp in (("x", (my_rows, COLS)), ("y", (my_rows, COLS)), ("t", (my_rows, COLS)), ("z", (my_rows, COLS)), ("s", (1,)), ("m", (my_rows,))):
+        ex.new(nm, "float32", shp)
+    ir = [f"exp({f32}:x)->({f32}:t) // author=miaobyte",
+          f"mul({f32}:t, {f32}:y)->({f32}:t) // author=miaobyte",
+          f"add({f32}:t, {f32}:x)->({f32}:z) // author=miaobyte",
+          f"sum({f32}:z, vector<int32>:[0 1], var<bool>:false)->({f32}:s) // author=miaobyte",
+          f"reducemax({f32}:z, vector<int32>:[1], var<bool>:false)->({f32}:m) // author=miaobyte"]
+    hx_np, hy_np, hs_np, hm_np = hx.numpy(), hy.numpy(), hs.numpy(), hm.numpy()  # views of the pinned buffers
+    ex_stream = torch.cuda.ExternalStream(ctypes_ptr(ex), device=dev)
+
+    class _DevView:  # the executor's `s` tensor as a torch tensor, for the NCCL combine
+        def __init__(self, ptr, n):
+            self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+    s_view = torch.as_tensor(_DevView(ex.ptr("s"), 1), device=dev) if world > 1 else None
+
     def e2e_step():
-        x.copy_(hx, non_blocking=True)
-        y.copy_(hy, non_blocking=True)
-        chain()
-        hs.copy_(s, non_blocking=True)
-        hm.copy_(m, non_blocking=True)
+        ex.upload("x", hx_np)
+        ex.upload("y", hy_np)
+        for line in ir:
+            ex.run(line)
+        if world > 1:  # partial sums of the row blocks → global sum (the one exchange step of the chain)
+            ex.sync()
+            dist.all_reduce(s_view, op=dist.ReduceOp.SUM)
+            torch.cuda.current_stream().synchronize()
+        download_into(ex, "s", hs_np)
+        download_into(ex, "m", hm_np)
+
+    def timed_ex(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(ex_stream):
+            e0.record()
+        for _ in range(steps):
+            fn()
+        with torch.cuda.stream(ex_stream):
+            e1.record()
+        ex.sync()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
 
     e2e_steps = max(2, min(args.steps, 5))
     e2e_step()
-    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_ms = timed_ex(e2e_step, e2e_steps) / e2e_steps
+    if abs(float(hs_np[0]) - got_sum) > 1e-4 * abs(got_sum) + 1e-3 or not np.array_equal(hm_np[:ref_rows], got_m):
+        raise SystemExit("bench: the executor path and the direct path disagree — refusing to report a number")
+    ex.close()
     e2e_value = total_bytes / e2e_ms / 1e6
 
     line = {
@@ -492,7 +551,8 @@ def run_ours(args) -> None:
                      "(profiles/ew2_mul_f32_chain_256x1048576.md), scaled by rows",
                      "bytes_per_launch": mul_bytes, "us_per_launch": round(mul_ms * 1e3, 2)},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": 2 * my_rows * COLS * 4 * world,
-                "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
+                "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
+                "path": "deepxIR text -> libdeepx_exec.so (dx_exec_upload / dx_exec_run / dx_exec_download), pinned host buffers"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "global_sum": got_sum,
@@ -503,7 +563,6 @@ def run_ours(args) -> None:
         except Exception as ex:  # the CPU leg must never take the GPU number down with it
             line["cpu_baseline"] = {"value": None, "unit": UNIT, "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
         if not args.no_ops:
-            del x, y, t, z
             torch.cuda.empty_cache()
             from deepx_b200 import tensorfunc as TF
             line["ops"] = per_op_table(torch, TF, N, peak)
