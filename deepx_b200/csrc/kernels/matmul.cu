@@ -24,6 +24,7 @@
 // plain TF32 tensor-core math).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -339,6 +340,258 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
 }
 
+// ---- the CTA-pair form: cta_group::2, one 256 × 256 tile per pair of SMs -------------------------
+// Two CTAs of a cluster work on one tile.  CTA r of the pair owns rows r·128..r·128+127 of the
+// tile (its own TMEM holds those accumulators) and loads, per 64-deep K block, its own 128 × 64
+// slice of A and its own 64 × 128 half of the B panel: 32 KiB per stage instead of 48, so six
+// stages fit, and every B element crosses L2 → shared memory once per pair instead of once per CTA.
+// One thread of the leader CTA (rank 0) issues tcgen05.mma.cta_group::2 (M256 N256 K16): the
+// tensor cores of both SMs read A from their own shared memory and the two B halves from both.
+// Barrier protocol: the `full` barriers live in the leader (the peer's TMA loads complete on the
+// leader's barrier through the .cta_group::2 form of the copy); `empty` and `tmem_full` exist in
+// both CTAs and are signalled together by tcgen05.commit with a two-CTA mask; `tmem_empty` lives
+// in the leader and collects the eight epilogue warps of both CTAs.  No multicast loads.
+constexpr int P_STAGES = 6;
+constexpr int P_B_STAGE_BYTES = B_BOX_BYTES * 2;                 // 64 K × 128 N
+constexpr int P_STAGE_BYTES = A_STAGE_BYTES + P_B_STAGE_BYTES;   // 32 KiB
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int PBM = 256;                                         // tile rows per pair
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar_cluster, int c0, int c1, int c2) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1), "r"(c2)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in every CTA of `mask` once all MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask)
+                 : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc_pair(int ab_format) {
+    return (1u << 4) | (uint32_t(ab_format) << 7) | (uint32_t(ab_format) << 10) | (0u << 15) | (1u << 16) |
+           (uint32_t(BN >> 3) << 17) | (uint32_t(PBM >> 4) << 24);
+}
+
+struct PairParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, num_tiles, k_blocks;  // tiles of 256 × 256
+    int *status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                             T *__restrict__ C, PairParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bars = smem_base + P_STAGES * P_STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (P_STAGES + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * P_STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * P_STAGES + ACC_STAGES + a); };
+    constexpr int SLOT_OFF = 8 * (2 * P_STAGES + 2 * ACC_STAGES);
+    const uint32_t tmem_slot = bars + SLOT_OFF;
+    uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + P_STAGES * P_STAGE_BYTES + SLOT_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + P_STAGES * P_STAGE_BYTES + SLOT_OFF + 8);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();      // 0 = leader of the pair
+    const int pair = blockIdx.x >> 1;             // cluster index (clusters are consecutive CTA pairs)
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);   // used in the leader only: its producer's arrive.expect_tx
+            mbar_init(empty_bar(s), 1);  // one tcgen05.commit per use
+        }
+        for (int a = 0; a < ACC_STAGES; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 8);  // used in the leader only: 4 epilogue warps × 2 CTAs
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    auto tile_coords = [&](int tile, int &b, int &tm, int &tn) {
+        const int per_batch = p.tiles_m * p.tiles_n;
+        b = tile / per_batch;
+        const int t = tile - b * per_batch;
+        tn = t / p.tiles_m;
+        tm = t - tn * p.tiles_m;
+    };
+
+    if (warp == 0) {
+        // ===== TMA producer (one per CTA; both complete on the LEADER's full barrier) =====
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+                int b, tm, tn;
+                tile_coords(tile, b, tm, tn);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_EMPTY); }
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+                    const uint32_t leader_full = mapa_u32(full_bar(stage), 0);
+                    if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);  // both CTAs' bytes
+                    tma_load_3d_pair(sa, &tmap_a, leader_full, kb * BK, tm * PBM + int(rank) * BM, b);
+#pragma unroll
+                    for (int j = 0; j < 2; ++j)
+                        tma_load_3d_pair(sb + j * B_BOX_BYTES, &tmap_b, leader_full, tn * BN + int(rank) * 128 + j * B_BOX_N, kb * BK, b);
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000ll) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer: one thread of the leader CTA drives the tensor cores of both SMs =====
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_pair(std::is_same<T, bf16>::value ? 1 : 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_TMEM_EMPTY); }
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_FULL); }
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+                    const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t adesc = make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+                        const uint64_t bdesc = make_smem_desc(sb + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
+                        umma_f16_pair(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
+                    }
+                    umma_commit_pair(empty_bar(stage), 0x3);  // frees this stage in both CTAs
+                    if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull_bar(acc), 0x3);  // accumulators of both CTAs complete
+                if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else {
+        // ===== epilogue: warps 2..5 of BOTH CTAs, each CTA drains its own 128 rows from its own TMEM =====
+        const int q = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool vec_ok = (p.N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+        for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
+            int b, tm, tn;
+            tile_coords(tile, b, tm, tn);
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+                if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL); }
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * PBM + int(rank) * BM + q * 32 + lane;
+            T *crow = C + (size_t(b) * p.M + row) * p.N;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c0, r);
+                tmem_ld_wait();
+                const int col = tn * BN + c0;
+                if (row < p.M) {
+                    if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            uint4 o;
+                            o.x = pack2<T>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                            o.y = pack2<T>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                            o.z = pack2<T>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                            o.w = pack2<T>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                            *reinterpret_cast<uint4 *>(crow + col + 8 * v) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < p.N) crow[col + j] = from_compute<T>(__uint_as_float(r[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));  // the leader's barrier collects all eight warps
+            if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    // Teardown: neither CTA may leave (or free TMEM) while the other can still signal its barriers
+    // or read its shared memory, so the whole pair meets first.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 // ---- SIMT FMA kernel for f32 / f64 (and shapes the TMA path cannot take) -----------------------
 template <typename T, typename A, int TS, int RT>
 __global__ void __launch_bounds__((TS / RT) * (TS / RT))
@@ -440,6 +693,40 @@ std::mutex g_setup_mu;
 bool g_attr_set[64][2] = {};
 int *g_status_ptr[64] = {};
 
+// How many CTA pairs can be resident at once on `dev` (0 = the pair kernel cannot run there).
+// Looked up once per device and element type; also raises the kernel's shared-memory limit.
+int g_pair_slots[64][2] = {};
+bool g_pair_known[64][2] = {};
+template <typename T> int pair_slots(int dev) {
+    const int ti = std::is_same<T, bf16>::value ? 0 : 1;
+    std::lock_guard<std::mutex> lk(g_setup_mu);
+    if (g_pair_known[dev][ti]) return g_pair_slots[dev][ti];
+    g_pair_known[dev][ti] = true;
+    g_pair_slots[dev][ti] = 0;
+    if (cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2u * (unsigned)sm_count(), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = P_SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_kernel<T>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    g_pair_slots[dev][ti] = n;
+    return n;
+}
+
 template <typename T>
 int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
     int dev = 0;
@@ -466,6 +753,39 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
     CUtensorMap ma, mb;
     if (int e = make_map(&ma, dt, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, BK, BM)) return e;
     if (int e = make_map(&mb, dt, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, B_BOX_N, BK)) return e;
+
+    // ---- CTA-pair form: worth it once there is at least one 256 × 256 tile per pair of SMs ----
+    const int64_t ptiles_m = (M + PBM - 1) / PBM, ptiles_n = (N + BN - 1) / BN;
+    const int64_t ptiles = ptiles_m * ptiles_n * batch;
+    const int pairs = pair_slots<T>(dev);
+    int mode = -1;  // auto
+    if (const char *env = std::getenv("DX_GEMM_CTA_PAIR")) mode = (env[0] == '1') ? 1 : (env[0] == '0' ? 0 : -1);
+    const bool use_pair = pairs > 0 && ptiles < (1ll << 31) && (mode == 1 || (mode == -1 && ptiles >= pairs));
+    if (use_pair) {
+        PairParams pp;
+        pp.M = (int)M; pp.N = (int)N; pp.K = (int)K; pp.batch = (int)batch;
+        pp.tiles_m = (int)ptiles_m;
+        pp.tiles_n = (int)ptiles_n;
+        pp.num_tiles = (int)ptiles;
+        pp.k_blocks = (int)((K + BK - 1) / BK);
+        pp.status = status;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ptiles, pairs), 1, 1);
+        cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = P_SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<T>, ma, mb, C, pp);
+        if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 pair): %s", cudaGetErrorString(e));
+        return check_launch("matmul(tcgen05 pair)");
+    }
+
     GemmParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.tiles_m = (int)((M + BM - 1) / BM);

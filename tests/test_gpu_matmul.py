@@ -60,6 +60,60 @@ def test_matmul_16bit(mods, shape, dtype):
         assert np.abs(got - want).max() <= 2 * TOL[dtype] * max(1.0, np.abs(want).max())
 
 
+@pytest.fixture()
+def force_pair(monkeypatch):
+    """Forces the CTA-pair (cta_group::2) kernel regardless of problem size."""
+    monkeypatch.setenv("DX_GEMM_CTA_PAIR", "1")
+    yield
+    monkeypatch.delenv("DX_GEMM_CTA_PAIR", raising=False)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("shape", [
+    (256, 256, 64), (256, 256, 512), (512, 768, 128), (1024, 1024, 1024),   # whole 256×256 tiles
+    (100, 200, 72), (130, 264, 40), (257, 1000, 520), (384, 520, 200), (1, 8, 8),  # ragged; second CTA partly or wholly past M
+])
+def test_matmul_16bit_cta_pair(mods, force_pair, shape, dtype):
+    TF, O, N = mods
+    M, Nn, K = shape
+    rng = np.random.default_rng(seed_of("mm2", shape, dtype))
+    a = make(rng, dtype, (M, K), -1.0, 1.0)
+    b = make(rng, dtype, (K, Nn), -1.0, 1.0)
+    check(TF, N, a, b, dtype, f"matmul pair<{dtype}> {shape}")
+
+
+def test_matmul_cta_pair_identity_and_batched(mods, force_pair):
+    TF, O, N = mods
+    rng = np.random.default_rng(4)
+    a = make(rng, "bfloat16", (512, 512), -2.0, 2.0)
+    eye = np.eye(512, dtype=np.float32).astype(NP_DTYPES["bfloat16"])
+    Cc = torch.empty((512, 512), dtype=torch.bfloat16, device="cuda:0")
+    TF.matmul(to_gpu(a), to_gpu(eye), Cc)
+    N.check(N.lib.dx_matmul_status(None))
+    assert np.array_equal(to_np(Cc).view(np.uint16), a.view(np.uint16))
+    a3 = make(rng, "bfloat16", (3, 300, 136), -1.0, 1.0)
+    b3 = make(rng, "bfloat16", (3, 136, 264), -1.0, 1.0)
+    check(TF, N, a3, b3, "bfloat16", "matmul pair batched [3,300,136]x[3,136,264]")
+
+
+def test_matmul_both_forms_agree_bit_for_bit(mods, monkeypatch):
+    """Same K order, same fp32 accumulation: the one-CTA and the CTA-pair kernels give identical bits."""
+    TF, O, N = mods
+    rng = np.random.default_rng(6)
+    a = make(rng, "bfloat16", (1000, 520), -1.0, 1.0)
+    b = make(rng, "bfloat16", (520, 776), -1.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    outs = []
+    for mode in ("0", "1"):
+        monkeypatch.setenv("DX_GEMM_CTA_PAIR", mode)
+        Cc = torch.empty((1000, 776), dtype=torch.bfloat16, device="cuda:0")
+        TF.matmul(A, B, Cc)
+        N.check(N.lib.dx_matmul_status(None))
+        outs.append(to_np(Cc).view(np.uint16))
+    monkeypatch.delenv("DX_GEMM_CTA_PAIR", raising=False)
+    assert np.array_equal(outs[0], outs[1])
+
+
 def test_matmul_identity_exact(mods):
     """A · I reproduces A bit for bit: exercises every (row, k) → (row, n) path of the tile."""
     TF, O, N = mods
