@@ -228,6 +228,13 @@ def op_cases(torch, TF, dev):
         o = torch.empty(32, 32, 2048, 128, dtype=torch.bfloat16, device=dev)
         return [lambda i=i: TF.transpose(t[i], [0, 2, 1, 3], o) for i in range(2)], 2 * o.numel() * 2, None
 
+    def transpose_inner(dtype):
+        def build():  # innermost axis moves: the shared-memory tile path
+            t = nrm(8192, 8192, n=2, dtype=dtype)
+            o = torch.empty(8192, 8192, dtype=dtype, device=dev)
+            return [lambda i=i: TF.transpose(t[i], [1, 0], o) for i in range(2)], 2 * o.numel() * o.element_size(), None
+        return build
+
     def concat_f32():
         parts = nrm(8, 1024, 4096, n=4)
         o = torch.empty(8, 4096, 4096, device=dev)
@@ -281,7 +288,8 @@ def op_cases(torch, TF, dev):
         "sum_f32_8192x8192_last": reduce_f32("sum", [1]), "sum_f32_8192x8192_axis0": reduce_f32("sum", [0]),
         "max_f32_8192x8192_last": reduce_f32("reducemax", [1]), "max_f32_8192x8192_axis0": reduce_f32("reducemax", [0]),
         "sum_i32_64x1024x1024_axes12": sum_i32,
-        "transpose_bf16_32x2048x32x128_0213": transpose_bf16, "concat_4x_f32_8x1024x4096_axis1": concat_f32,
+        "transpose_bf16_32x2048x32x128_0213": transpose_bf16,
+        "transpose_f32_8192x8192_10": transpose_inner(torch.float32), "transpose_bf16_8192x8192_10": transpose_inner(torch.bfloat16), "concat_4x_f32_8x1024x4096_axis1": concat_f32,
         "broadcastTo_f32_1x4096_to_8192x4096": broadcast_f32, "indexselect_f32_151936x896_by_8x2048": indexselect_f32,
         "matmul_bf16_8192x4096x4096": matmul_bf16,
         "rmsnorm_mul_xx_f32_16x2048x896": rms("mul"), "rmsnorm_sum_last_f32_16x2048x896": rms("sum"),

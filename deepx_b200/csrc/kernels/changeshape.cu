@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(CB) run_gather_kernel(const char *__restrict__
 
 // ---- tiled transpose (innermost axis moves) ------------------------------------------------
 // Source axis B is contiguous in the input, destination axis A is contiguous in the
-// output.  A CTA moves a TILE×TILE patch of the (A, B) plane through shared memory so
+// output.  A CTA moves a 64×64 patch of the (A, B) plane through shared memory so
 // both sides see coalesced rows; the remaining axes are a batch index.
 struct TileParams {
     Dims batch;            // strides: source bytes
@@ -133,27 +133,73 @@ __global__ void __launch_bounds__(CB) tile_transpose_kernel(const char *__restri
     const uint32_t ta = q - bt * p.tiles_a.d;
     const char *src = in + unravel_bytes(bt, p.batch);
     char *dst = out + unravel_bytes(bt, p.batch_out);
-    constexpr int NY = CB / TILE;
+    constexpr int NY = CB / TILE;    // tile rows covered by one pass of the CTA
+    constexpr int PER = TILE / NY;   // elements per thread
     const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
-    // load: x walks B (contiguous in the source), y walks A
+    // load: x walks B (contiguous in the source), y walks A.  All of a thread's loads are issued
+    // before the first shared-memory store, so PER independent requests per thread are in flight.
     {
         const uint32_t ib = tb * TILE + tx;
+        E v[PER];
 #pragma unroll
-        for (int y = ty; y < TILE; y += NY) {
-            const uint32_t ia = ta * TILE + y;
-            if (ia < p.na && ib < p.nb)
-                tile[y][tx] = *reinterpret_cast<const E *>(src + int64_t(ia) * p.a_src_stride + int64_t(ib) * sizeof(E));
+        for (int i = 0; i < PER; ++i) {
+            const uint32_t ia = ta * TILE + ty + i * NY;
+            v[i] = (ia < p.na && ib < p.nb)
+                       ? __ldcs(reinterpret_cast<const E *>(src + int64_t(ia) * p.a_src_stride + int64_t(ib) * sizeof(E)))
+                       : E(0);
         }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) tile[ty + i * NY][tx] = v[i];
     }
     __syncthreads();
     // store: x walks A (contiguous in the destination), y walks B
     {
         const uint32_t ia = ta * TILE + tx;
 #pragma unroll
-        for (int y = ty; y < TILE; y += NY) {
-            const uint32_t ib = tb * TILE + y;
+        for (int i = 0; i < PER; ++i) {
+            const uint32_t ib = tb * TILE + ty + i * NY;
             if (ia < p.na && ib < p.nb)
-                *reinterpret_cast<E *>(dst + int64_t(ib) * p.b_dst_stride + int64_t(ia) * sizeof(E)) = tile[tx][y];
+                __stcs(reinterpret_cast<E *>(dst + int64_t(ib) * p.b_dst_stride + int64_t(ia) * sizeof(E)), tile[tx][ty + i * NY]);
+        }
+    }
+}
+
+// 2-byte elements, both moving extents even: global accesses are 4-byte words (two elements), so a
+// thread has 16 × 4 bytes in flight instead of 16 × 2.  Patch = 64 (A) × 128 (B) elements.
+__global__ void __launch_bounds__(CB) tile_transpose_pairs16_kernel(const char *__restrict__ in, char *__restrict__ out, TileParams p) {
+    constexpr int TA = 64, TB = 128, PITCH = TB + 2;  // pitch in elements; rows stay 4-byte aligned
+    __shared__ __align__(4) uint16_t tile[TA][PITCH];
+    uint32_t b = blockIdx.x;
+    uint32_t q = fd_div(b, p.tiles_b);
+    const uint32_t tb = b - q * p.tiles_b.d;
+    const uint32_t bt = fd_div(q, p.tiles_a);
+    const uint32_t ta = q - bt * p.tiles_a.d;
+    const char *src = in + unravel_bytes(bt, p.batch);
+    char *dst = out + unravel_bytes(bt, p.batch_out);
+    {   // load: 64 words across B per row, 4 rows of A per pass, 16 passes
+        const int wx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+        const uint32_t ib = tb * TB + 2 * wx;
+        uint32_t v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t ia = ta * TA + ty + 4 * i;
+            v[i] = (ia < p.na && ib < p.nb) ? __ldcs(reinterpret_cast<const uint32_t *>(src + int64_t(ia) * p.a_src_stride + int64_t(ib) * 2)) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) *reinterpret_cast<uint32_t *>(&tile[ty + 4 * i][2 * wx]) = v[i];
+    }
+    __syncthreads();
+    {   // store: 32 words across A per output row, 8 rows of B per pass, 16 passes
+        const int wx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+        const uint32_t ia = ta * TA + 2 * wx;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int lb = ty + 8 * i;
+            const uint32_t ib = tb * TB + lb;
+            if (ia < p.na && ib < p.nb) {
+                const uint32_t w = uint32_t(tile[2 * wx][lb]) | (uint32_t(tile[2 * wx + 1][lb]) << 16);
+                __stcs(reinterpret_cast<uint32_t *>(dst + int64_t(ib) * p.b_dst_stride + int64_t(ia) * 2), w);
+            }
         }
     }
 }
@@ -394,15 +440,21 @@ extern "C" int dx_transpose(int dtype, const void *a, const int64_t *shape, int 
         ++p.batch_out.n;
         nbatch *= ax[i].size;
     }
-    const int tile = (es >= 4) ? 32 : 64;
-    const int64_t ta = (p.na + tile - 1) / tile, tb = (p.nb + tile - 1) / tile;
+    // 2-byte elements with even moving extents and 4-byte aligned bases: the paired-word kernel
+    const bool pairs16 = es == 2 && (p.na % 2 == 0) && (p.nb % 2 == 0) && aligned_to(a, 4) && aligned_to(out, 4);
+    const int tile_a = 64, tile_b = pairs16 ? 128 : 64;
+    const int64_t ta = (p.na + tile_a - 1) / tile_a, tb = (p.nb + tile_b - 1) / tile_b;
     p.tiles_a = make_fastdiv((uint32_t)ta);
     p.tiles_b = make_fastdiv((uint32_t)tb);
     const int64_t ctas = ta * tb * nbatch;
     if (ctas >= (1ll << 31)) return fail(DX_E_SHAPE, "transpose: grid too large");
+    if (pairs16) {
+        tile_transpose_pairs16_kernel<<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p);
+        return check_launch("transpose(tiles/pairs)");
+    }
     switch (es) {
-        case 8: tile_transpose_kernel<uint64_t, 32><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
-        case 4: tile_transpose_kernel<uint32_t, 32><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
+        case 8: tile_transpose_kernel<uint64_t, 64><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
+        case 4: tile_transpose_kernel<uint32_t, 64><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
         case 2: tile_transpose_kernel<uint16_t, 64><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
         default: tile_transpose_kernel<uint8_t, 64><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;
     }

@@ -56,6 +56,10 @@ def test_transpose_swap_last_two_large(mods):
     _transpose(TF, O, a, [0, 2, 1], "transpose swap last two")
     v = make(rng, "float32", (1000,))
     _transpose(TF, O, v, [0], "transpose 1d")
+    # 2-byte elements, even moving extents: the paired-word tile kernel, with ragged tiles
+    for shape, perm in [((3, 1000, 778), [0, 2, 1]), ((130, 258), [1, 0]), ((2, 66, 5, 130), [3, 2, 1, 0]), ((4, 64, 128), [2, 0, 1])]:
+        for dt in ("bfloat16", "int16"):
+            _transpose(TF, O, make(rng, dt, shape), perm, f"transpose<{dt}> {shape} {perm}")
 
 
 def test_transpose_errors(mods):
