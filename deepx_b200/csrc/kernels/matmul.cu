@@ -592,6 +592,252 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
 }
 
+// ---- float32 on the tensor cores: three TF32 products per fp32 product ------------------------------
+// kind::tf32 reads 32-bit words and keeps 10 mantissa bits, which alone misses the 1e-5 bound.  Each
+// operand is therefore split IN SHARED MEMORY into hi = round-to-tf32(x) and lo = x − hi (exact in
+// fp32, |lo| ≤ 2^-11 |x|), and the kernel accumulates  Ahi·Bhi + Alo·Bhi + Ahi·Blo  in fp32 TMEM.
+// What is dropped (Alo·Blo, and the tf32 truncation of lo) is ~2^-21 relative to |a||b|.
+//   warp 0      TMA producer: raw fp32 tiles (A 128×32, B 32×128 as four 32-column panels)
+//   warps 6-9   splitters: rewrite the raw tile as hi in place, write lo beside it, fence to the
+//               async proxy, signal the MMA warp
+//   warp 1      MMA issuer: 4 K-steps × 3 products of tcgen05.mma.kind::tf32 (M128 N128 K8) per stage
+//   warps 2-5   epilogue: TMEM → fp32 → 16-byte stores
+// The caller passes no workspace: nothing is pre-split in global memory.
+constexpr int F_BN = 128, F_BK = 32, F_UMMA_K = 8;
+constexpr int F_STAGES = 3;
+constexpr int F_A_BYTES = BM * F_BK * 4;                 // 16 KiB
+constexpr int F_B_BOX_N = 32;                            // 32 fp32 = one 128-byte swizzle row
+constexpr int F_B_BOX_BYTES = F_BK * F_B_BOX_N * 4;      // 4 KiB
+constexpr int F_B_BYTES = F_B_BOX_BYTES * (F_BN / F_B_BOX_N);  // 16 KiB
+constexpr int F_RAW_BYTES = F_A_BYTES + F_B_BYTES;       // what TMA delivers per stage
+constexpr int F_STAGE_BYTES = 2 * F_RAW_BYTES;           // hi + lo of both operands: 64 KiB
+constexpr int F_SMEM_BYTES = F_STAGES * F_STAGE_BYTES + 1024 + 256;
+constexpr int F_TMEM_COLS = ACC_STAGES * F_BN;           // 256
+constexpr int F_THREADS = 320;
+enum { GEMM_TIMEOUT_RAW = 5, GEMM_TIMEOUT_SPLIT = 6 };
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ float round_tf32(float x) {
+    uint32_t u;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+    return __uint_as_float(u);
+}
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// D f32 (1<<4), A and B tf32 (format 2), A K-major, B MN-major, N = 128, M = 128
+__host__ __device__ constexpr uint32_t make_idesc_tf32() {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) | (uint32_t(F_BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(F_THREADS, 1)
+    gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, float *__restrict__ C,
+                       GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + F_STAGES * F_STAGE_BYTES;
+    auto raw_bar = [&](int s) { return bars + 8u * s; };                       // TMA → splitters
+    auto split_bar = [&](int s) { return bars + 8u * (F_STAGES + s); };        // splitters → MMA
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * F_STAGES + s); };    // MMA → TMA
+    auto tfull_bar = [&](int a) { return bars + 8u * (3 * F_STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (3 * F_STAGES + ACC_STAGES + a); };
+    constexpr int SLOT_OFF = 8 * (3 * F_STAGES + 2 * ACC_STAGES);
+    const uint32_t tmem_slot = bars + SLOT_OFF;
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + F_STAGES * F_STAGE_BYTES + SLOT_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + F_STAGES * F_STAGE_BYTES + SLOT_OFF + 8);
+    // stage layout: [A hi | B hi | A lo | B lo]; TMA fills the first two, which the splitters round in place
+    auto a_hi = [&](int s) { return smem_base + s * F_STAGE_BYTES; };
+    auto b_hi = [&](int s) { return smem_base + s * F_STAGE_BYTES + F_A_BYTES; };
+    auto a_lo = [&](int s) { return smem_base + s * F_STAGE_BYTES + F_RAW_BYTES; };
+    auto b_lo = [&](int s) { return smem_base + s * F_STAGE_BYTES + F_RAW_BYTES + F_A_BYTES; };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < F_STAGES; ++s) {
+            mbar_init(raw_bar(s), 1);
+            mbar_init(split_bar(s), 4);  // one arrival per splitter warp
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < ACC_STAGES; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 4);
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, F_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    auto tile_coords = [&](int tile, int &b, int &tm, int &tn) {
+        const int per_batch = p.tiles_m * p.tiles_n;
+        b = tile / per_batch;
+        const int t = tile - b * per_batch;
+        tn = t / p.tiles_m;
+        tm = t - tn * p.tiles_m;
+    };
+    if (warp == 0) {
+        // ===== TMA producer =====
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                int b, tm, tn;
+                tile_coords(tile, b, tm, tn);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_EMPTY); }
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(raw_bar(stage), F_RAW_BYTES);
+                    tma_load_3d(a_hi(stage), &tmap_a, raw_bar(stage), kb * F_BK, tm * BM, b);
+#pragma unroll
+                    for (int j = 0; j < F_BN / F_B_BOX_N; ++j)
+                        tma_load_3d(b_hi(stage) + j * F_B_BOX_BYTES, &tmap_b, raw_bar(stage), tn * F_BN + j * F_B_BOX_N, kb * F_BK, b);
+                    if (++stage == F_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000ll) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer =====
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32();
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_TMEM_EMPTY); }
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * F_BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(split_bar(stage), phase, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_SPLIT); }
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < F_BK / F_UMMA_K; ++k) {
+                        // A: K-major; 8 fp32 = 32 bytes per K step inside the 128-byte swizzle row
+                        const uint64_t ah = make_smem_desc(a_hi(stage) + k * 32, 16, 1024);
+                        const uint64_t al = make_smem_desc(a_lo(stage) + k * 32, 16, 1024);
+                        // B: N-major; 32-column panels 4096 bytes apart, one 8-row K group (1024 bytes) per step
+                        const uint64_t bh = make_smem_desc(b_hi(stage) + k * 1024, F_B_BOX_BYTES, 1024);
+                        const uint64_t bl = make_smem_desc(b_lo(stage) + k * 1024, F_B_BOX_BYTES, 1024);
+                        umma_tf32(tmem_d, al, bh, idesc, (kb | k) != 0);  // small terms first
+                        umma_tf32(tmem_d, ah, bl, idesc, 1);
+                        umma_tf32(tmem_d, ah, bh, idesc, 1);
+                    }
+                    umma_commit(empty_bar(stage));
+                    if (++stage == F_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(tfull_bar(acc));
+                if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else if (warp < 6) {
+        // ===== epilogue: warps 2..5 → TMEM lane quarter warp % 4 =====
+        const int q = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool vec_ok = (p.N % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+            int b, tm, tn;
+            tile_coords(tile, b, tm, tn);
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+                if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL); }
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * BM + q * 32 + lane;
+            float *crow = C + (size_t(b) * p.M + row) * p.N;
+#pragma unroll 1
+            for (int c0 = 0; c0 < F_BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * F_BN + c0, r);
+                tmem_ld_wait();
+                const int col = tn * F_BN + c0;
+                if (row < p.M) {
+                    if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            *reinterpret_cast<uint4 *>(crow + col + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < p.N) crow[col + j] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+            if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        }
+    } else {
+        // ===== splitters: warps 6..9, 128 threads; 2048 float4 per stage (A and B raw tiles) =====
+        const int t = threadIdx.x - 6 * 32;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                if (!mbar_wait(raw_bar(stage), phase, abort_flag)) {
+                    if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_RAW); }
+                    ok = false;
+                    break;
+                }
+                float4 *hi = reinterpret_cast<float4 *>(gen_base + stage * F_STAGE_BYTES);
+                float4 *lo = reinterpret_cast<float4 *>(gen_base + stage * F_STAGE_BYTES + F_RAW_BYTES);
+#pragma unroll 4
+                for (int i = t; i < F_RAW_BYTES / 16; i += 128) {
+                    const float4 x = hi[i];
+                    float4 h, l;
+                    h.x = round_tf32(x.x); l.x = x.x - h.x;
+                    h.y = round_tf32(x.y); l.y = x.y - h.y;
+                    h.z = round_tf32(x.z); l.z = x.z - h.z;
+                    h.w = round_tf32(x.w); l.w = x.w - h.w;
+                    hi[i] = h;
+                    lo[i] = l;
+                }
+                fence_proxy_async_smem();  // these generic-proxy writes are read next by the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(split_bar(stage));
+                if (++stage == F_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, F_TMEM_COLS);
+    }
+}
+
 // ---- SIMT FMA kernel for f32 / f64 (and shapes the TMA path cannot take) -----------------------
 template <typename T, typename A, int TS, int RT>
 __global__ void __launch_bounds__((TS / RT) * (TS / RT))
@@ -674,11 +920,11 @@ EncodeTiledFn encode_tiled() {
 }
 
 int make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t rows, uint64_t batch,
-             uint32_t box_inner, uint32_t box_rows) {
+             uint32_t box_inner, uint32_t box_rows, uint32_t esize = 2) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return fail(DX_E_CUDA, "matmul: cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[3] = {inner, rows, batch};
-    const cuuint64_t strides[2] = {inner * 2, inner * rows * 2};  // bytes, for dims 1 and 2
+    const cuuint64_t strides[2] = {inner * esize, inner * rows * esize};  // bytes, for dims 1 and 2
     const cuuint32_t box[3] = {box_inner, box_rows, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -800,6 +1046,45 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
     return check_launch("matmul(tcgen05)");
 }
 
+// float32 through the tensor cores (three TF32 products per product).
+bool g_tf32_attr[64] = {};
+int launch_tf32x3(const float *A, const float *B, float *C, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return fail(DX_E_CUDA, "matmul: device index %d out of range", dev);
+    int *status;
+    {
+        std::lock_guard<std::mutex> lk(g_setup_mu);
+        if (!g_status_ptr[dev]) {
+            void *sym = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&sym, g_gemm_status);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_status_ptr[dev] = static_cast<int *>(sym);
+        }
+        status = g_status_ptr[dev];
+        if (!g_tf32_attr[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM_BYTES);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            g_tf32_attr[dev] = true;
+        }
+    }
+    CUtensorMap ma, mb;
+    if (int e = make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, F_BK, BM, 4)) return e;
+    if (int e = make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, F_B_BOX_N, F_BK, 4)) return e;
+    GemmParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.tiles_m = (int)((M + BM - 1) / BM);
+    p.tiles_n = (int)((N + F_BN - 1) / F_BN);
+    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n * batch;
+    if (tiles >= (1ll << 31)) return fail(DX_E_SHAPE, "matmul: too many tiles");
+    p.num_tiles = (int)tiles;
+    p.k_blocks = (int)((K + F_BK - 1) / F_BK);
+    p.status = status;
+    const int grid = (int)std::min<int64_t>(tiles, sm_count());
+    gemm_tf32x3_kernel<<<grid, F_THREADS, F_SMEM_BYTES, st>>>(ma, mb, C, p);
+    return check_launch("matmul(tf32x3)");
+}
+
 }  // namespace
 }  // namespace dx
 
@@ -845,7 +1130,13 @@ extern "C" int dx_matmul(int dtype, const void *A, const void *B, void *C, int64
             return dtype == DX_BF16 ? launch_simt<bf16, float>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, st)
                                     : launch_simt<f16, float>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);
         }
-        case DX_F32: return launch_simt<float, float>((const float *)A, (const float *)B, (float *)C, batch, M, N, K, st);
+        case DX_F32: {
+            // tensor-core path needs 16-byte aligned bases and row pitches; DX_GEMM_F32_SIMT=1 forces the FMA kernel
+            const char *env = std::getenv("DX_GEMM_F32_SIMT");
+            const bool tma_ok = (K % 4 == 0) && (N % 4 == 0) && aligned_to(A, 16) && aligned_to(B, 16) && !(env && env[0] == '1');
+            if (tma_ok) return launch_tf32x3((const float *)A, (const float *)B, (float *)C, batch, M, N, K, st);
+            return launch_simt<float, float>((const float *)A, (const float *)B, (float *)C, batch, M, N, K, st);
+        }
         case DX_F64: return launch_simt<double, double>((const double *)A, (const double *)B, (double *)C, batch, M, N, K, st);
         default: return fail(DX_E_DTYPE, "matmul: unsupported dtype code %d (float dtypes only)", dtype);
     }

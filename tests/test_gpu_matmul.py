@@ -33,7 +33,10 @@ def check(TF, N, a, b, dtype, what):
     scale = np.abs(a64) @ np.abs(b64)
     err = np.abs(got - ref)
     # one rounding of the result (relative to |ref|) + accumulation error (relative to Σ|a||b|)
-    bound = TOL[dtype] * np.abs(ref) + (1e-6 if dtype != "float64" else 1e-14) * scale + 1e-300
+    # float32 runs as three TF32 tensor-core products per product: the dropped lo·lo term and the tf32
+    # truncation of the lo parts are each ~2^-21 of |a||b|, hence 2e-6 on the accumulation term
+    acc_tol = {"float64": 1e-14, "float32": 2e-6}.get(dtype, 1e-6)
+    bound = TOL[dtype] * np.abs(ref) + acc_tol * scale + 1e-300
     bad = err > bound
     assert not bad.any(), (f"{what}: {bad.sum()} of {bad.size} outside tolerance; max err {err.max():.3e}; "
                            f"first bad index {np.argwhere(bad)[0].tolist()} got {got[tuple(np.argwhere(bad)[0])]} "
@@ -147,6 +150,39 @@ def test_matmul_fp32_fp64(mods, dtype):
     a = make(rng, dtype, (2, 3, 4, 5), -1.0, 1.0)
     b = make(rng, dtype, (2, 3, 5, 6), -1.0, 1.0)
     check(TF, N, a, b, dtype, "batched [2,3,4,5]x[2,3,5,6]")  # shapes of executor/op-cuda/test/tensorfunc/1_cublas_matmul.cpp:36-62
+
+
+@pytest.mark.parametrize("shape", [(128, 128, 32), (256, 384, 96), (1000, 520, 264), (130, 36, 8), (2048, 1024, 512)])
+def test_matmul_fp32_tensor_core_path(mods, shape):
+    """float32 with K and N multiples of 4 takes the TF32x3 tcgen05 kernel; result within 1e-5."""
+    TF, O, N = mods
+    M, Nn, K = shape
+    rng = np.random.default_rng(seed_of("mm32", shape))
+    a = make(rng, "float32", (M, K), -1.0, 1.0)
+    b = make(rng, "float32", (K, Nn), -1.0, 1.0)
+    got = check(TF, N, a, b, "float32", f"matmul<float32 tf32x3> {shape}")
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    rel = np.abs(got - ref).max() / np.abs(ref).max()
+    assert rel <= 1e-5, rel
+    a3 = make(rng, "float32", (3, 200, 64), -1.0, 1.0)
+    b3 = make(rng, "float32", (3, 64, 132), -1.0, 1.0)
+    check(TF, N, a3, b3, "float32", "matmul<float32 tf32x3> batched")
+
+
+def test_matmul_fp32_simt_path_is_tighter(mods, monkeypatch):
+    """The FMA kernel (shapes TMA cannot take, or DX_GEMM_F32_SIMT=1) accumulates in plain fp32."""
+    TF, O, N = mods
+    monkeypatch.setenv("DX_GEMM_F32_SIMT", "1")
+    rng = np.random.default_rng(8)
+    a = make(rng, "float32", (300, 256), -1.0, 1.0)
+    b = make(rng, "float32", (256, 200), -1.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    Cc = torch.empty((300, 200), dtype=torch.float32, device="cuda:0")
+    TF.matmul(A, B, Cc)
+    monkeypatch.delenv("DX_GEMM_F32_SIMT", raising=False)
+    got = to_np(Cc).astype(np.float64)
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    assert (np.abs(got - a64 @ b64) <= 3e-7 * (np.abs(a64) @ np.abs(b64))).all()
 
 
 def test_matmul_golden_arange(mods):
