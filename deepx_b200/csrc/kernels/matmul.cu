@@ -134,14 +134,15 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // ---- descriptors ----------------------------------------------------------------------------
 // Shared-memory matrix descriptor (64-bit): start address >>4 in [0,14), leading byte offset >>4
 // in [16,30), stride byte offset >>4 in [32,46), descriptor version 1 in [46,48), swizzle mode in
-// [61,64) (2 = 128-byte swizzle).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// [61,64) (2 = 128-byte swizzle of 16-byte chunks, 1 = 128-byte swizzle of 32-byte chunks).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t swizzle_mode = 2) {
     uint64_t d = 0;
     d |= uint64_t((saddr >> 4) & 0x3FFF);
     d |= uint64_t((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= uint64_t(1) << 46;
-    d |= uint64_t(2) << 61;
+    d |= uint64_t(swizzle_mode) << 61;
     return d;
 }
 // Instruction descriptor (32-bit) for kind::f16: D format [4,6) 1 = f32; A format [7,10), B format
@@ -743,9 +744,11 @@ __global__ void __launch_bounds__(F_THREADS, 1)
                         // A: K-major; 8 fp32 = 32 bytes per K step inside the 128-byte swizzle row
                         const uint64_t ah = make_smem_desc(a_hi(stage) + k * 32, 16, 1024);
                         const uint64_t al = make_smem_desc(a_lo(stage) + k * 32, 16, 1024);
-                        // B: N-major; 32-column panels 4096 bytes apart, one 8-row K group (1024 bytes) per step
-                        const uint64_t bh = make_smem_desc(b_hi(stage) + k * 1024, F_B_BOX_BYTES, 1024);
-                        const uint64_t bl = make_smem_desc(b_lo(stage) + k * 1024, F_B_BOX_BYTES, 1024);
+                        // B: N-major. 32-bit N-major operands exist only in the 128-byte swizzle of
+                        // 32-byte chunks (mode 1): its atom is 32 columns x 4 K rows = 512 bytes, so one
+                        // K = 8 step spans two atoms 512 bytes apart; 32-column panels are 4096 bytes apart.
+                        const uint64_t bh = make_smem_desc(b_hi(stage) + k * 1024, F_B_BOX_BYTES, 512, 1);
+                        const uint64_t bl = make_smem_desc(b_lo(stage) + k * 1024, F_B_BOX_BYTES, 512, 1);
                         umma_tf32(tmem_d, al, bh, idesc, (kb | k) != 0);  // small terms first
                         umma_tf32(tmem_d, ah, bl, idesc, 1);
                         umma_tf32(tmem_d, ah, bh, idesc, 1);
@@ -920,7 +923,8 @@ EncodeTiledFn encode_tiled() {
 }
 
 int make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_t inner, uint64_t rows, uint64_t batch,
-             uint32_t box_inner, uint32_t box_rows, uint32_t esize = 2) {
+             uint32_t box_inner, uint32_t box_rows, uint32_t esize = 2,
+             CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return fail(DX_E_CUDA, "matmul: cuTensorMapEncodeTiled is not available from this driver");
     const cuuint64_t dims[3] = {inner, rows, batch};
@@ -928,7 +932,7 @@ int make_map(CUtensorMap *map, CUtensorMapDataType dt, const void *base, uint64_
     const cuuint32_t box[3] = {box_inner, box_rows, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = enc(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                     swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(DX_E_CUDA, "matmul: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return DX_OK;
 }
@@ -1070,7 +1074,8 @@ int launch_tf32x3(const float *A, const float *B, float *C, int64_t batch, int64
     }
     CUtensorMap ma, mb;
     if (int e = make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, F_BK, BM, 4)) return e;
-    if (int e = make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, F_B_BOX_N, F_BK, 4)) return e;
+    if (int e = make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, F_B_BOX_N, F_BK, 4,
+                         CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return e;
     GemmParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.tiles_m = (int)((M + BM - 1) / BM);

@@ -182,7 +182,8 @@ def test_matmul_fp32_simt_path_is_tighter(mods, monkeypatch):
     monkeypatch.delenv("DX_GEMM_F32_SIMT", raising=False)
     got = to_np(Cc).astype(np.float64)
     a64, b64 = a.astype(np.float64), b.astype(np.float64)
-    assert (np.abs(got - a64 @ b64) <= 3e-7 * (np.abs(a64) @ np.abs(b64))).all()
+    # sequential fp32 accumulation over K = 256: well inside K * 2^-24 of sum |a||b|
+    assert (np.abs(got - a64 @ b64) <= 4e-6 * (np.abs(a64) @ np.abs(b64))).all()
 
 
 def test_matmul_golden_arange(mods):
