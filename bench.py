@@ -257,6 +257,46 @@ def op_cases(torch, TF, dev):
         Cm = torch.empty(8192, 4096, dtype=torch.bfloat16, device=dev)
         return [lambda: TF.matmul(A, B, Cm)], 0, 2 * 8192 * 4096 * 4096
 
+    def matmul_f32():
+        A = nrm(8192, 4096, scale=0.02)[0]
+        B = nrm(4096, 4096, scale=0.02)[0]
+        Cm = torch.empty(8192, 4096, device=dev)
+        return [lambda: TF.matmul(A, B, Cm)], 0, 2 * 8192 * 4096 * 4096
+
+    def rms_fused():
+        x = nrm(16, 2048, 896, n=R)
+        w = nrm(896)[0]
+        y = [torch.empty(16, 2048, 896, device=dev) for _ in range(R)]
+        n = 16 * 2048 * 896 * 4
+        return [lambda i=i: TF.rmsnorm(x[i], w, 896.0, 1e-6, y[i]) for i in range(R)], 2 * n + 896 * 4, None
+
+    def rms_single_ops():
+        """The ten IR ops of the RMSNorm chain, one launch each: what the fused kernel replaces."""
+        x = nrm(16, 2048, 896, n=R)
+        w = nrm(1, 1, 896)[0]
+        sq, vb, y, wb, out = (torch.empty(16, 2048, 896, device=dev) for _ in range(5))
+        v = torch.empty(16, 2048, 1, device=dev)
+        n, nv, shp = 16 * 2048 * 896 * 4, 16 * 2048 * 4, [16, 2048, 896]
+
+        def chain(i):
+            TF.mul(x[i], x[i], sq)
+            TF.sum(sq, [2], True, v)
+            TF.divscalar(v, 896.0, v)
+            TF.addscalar(v, 1e-6, v)
+            TF.sqrt(v, v)
+            TF.rdivscalar(1.0, v, v)
+            TF.broadcastTo(v, shp, vb)
+            TF.mul(x[i], vb, y)
+            TF.broadcastTo(w, shp, wb)
+            TF.mul(y, wb, out)
+        total = 2 * n + (n + nv) + 4 * 2 * nv + (nv + n) + 3 * n + (896 * 4 + n) + 3 * n
+        return [lambda i=i: chain(i) for i in range(R)], total, None
+
+    def softmax_fused():
+        x = nrm(32768, 2048, n=R)
+        y = [torch.empty(32768, 2048, device=dev) for _ in range(R)]
+        return [lambda i=i: TF.softmax(x[i], y[i]) for i in range(R)], 2 * 32768 * 2048 * 4, None
+
     def rms(opname):
         def build():
             x = nrm(16, 2048, 896, n=R)
@@ -291,7 +331,9 @@ def op_cases(torch, TF, dev):
         "transpose_bf16_32x2048x32x128_0213": transpose_bf16,
         "transpose_f32_8192x8192_10": transpose_inner(torch.float32), "transpose_bf16_8192x8192_10": transpose_inner(torch.bfloat16), "concat_4x_f32_8x1024x4096_axis1": concat_f32,
         "broadcastTo_f32_1x4096_to_8192x4096": broadcast_f32, "indexselect_f32_151936x896_by_8x2048": indexselect_f32,
-        "matmul_bf16_8192x4096x4096": matmul_bf16,
+        "matmul_bf16_8192x4096x4096": matmul_bf16, "matmul_f32_8192x4096x4096": matmul_f32,
+        "rmsnorm_fused_f32_16x2048x896": rms_fused, "softmax_fused_f32_32768x2048": softmax_fused,
+        "rmsnorm_ten_single_ops_f32_16x2048x896": rms_single_ops,
         "rmsnorm_mul_xx_f32_16x2048x896": rms("mul"), "rmsnorm_sum_last_f32_16x2048x896": rms("sum"),
         "rmsnorm_broadcast_f32_16x2048x1": rms("broadcast"), "rmsnorm_mul_xy_f32_16x2048x896": rms("mul3"),
         "chain_exp_f32_256x1048576": chain("exp"), "chain_mul_f32_256x1048576": chain("mul"), "chain_add_f32_256x1048576": chain("add"),

@@ -53,6 +53,8 @@ SIGNATURES = {
     "dx_reduce_workspace_bytes": (_sz, [_i, _i, _pi64, _i, _pi32, _i]),
     "dx_reduce": (_i, [_i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp, _sz, _vp]),
     "dx_reduce_noalloc": (_i, [_i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp]),
+    "dx_rmsnorm": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _d, _d, _vp]),
+    "dx_softmax": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "dx_transpose": (_i, [_i, _vp, _pi64, _i, _pi32, _vp, _vp]),
     "dx_concat": (_i, [_i, _pvp, _pi64, _i, _pi64, _i, _i, _vp, _vp]),
     "dx_broadcast_to": (_i, [_i, _vp, _pi64, _i, _pi64, _i, _vp, _vp]),

@@ -2,8 +2,11 @@
 #include <cuda_runtime.h>
 
 #include <cstring>
+#include <sstream>
+#include <unordered_map>
 
 #include "core.hpp"
+#include "fusion.hpp"
 #include "dx_executor.h"
 
 using namespace dxh;
@@ -48,6 +51,26 @@ int dx_exec_run(dx_exec *e, const char *ir_line, char *reply, size_t cap) {
     const OpResp r = e->ex.run_line(ir_line);
     if (put(r.to_string(), reply, cap) < 0) { g_err = "reply buffer too small"; return -1; }
     return r.result == "ok" ? 0 : 1;
+}
+
+int dx_exec_run_program(dx_exec *e, const char *program, char *replies, size_t cap) {
+    if (!e || !program) { g_err = "null executor or program"; return -1; }
+    const std::vector<OpResp> rs = e->ex.run_program(program);
+    std::string all;
+    int errors = 0;
+    for (size_t i = 0; i < rs.size(); ++i) {
+        if (i) all += "\n";
+        all += rs[i].to_string();
+        errors += rs[i].result == "ok" ? 0 : 1;
+    }
+    if (put(all, replies, cap) < 0) { g_err = "reply buffer too small"; return -1; }
+    return errors;
+}
+void dx_exec_set_fusion(dx_exec *e, int on) { if (e) e->ex.fuse = on != 0; }
+void dx_exec_fusion_stats(dx_exec *e, uint64_t stats[4]) {
+    if (!e || !stats) return;
+    const FusionStats &f = e->ex.fusion_stats();
+    stats[0] = f.programs; stats[1] = f.rmsnorm_groups; stats[2] = f.softmax_groups; stats[3] = f.lines_absorbed;
 }
 
 int dx_exec_tensor_info(dx_exec *e, const char *name, int *dtype, int64_t *shape, int cap) {
@@ -123,6 +146,46 @@ int dx_ir_parse(const char *ir_line, char *out, size_t cap) {
     }
 }
 int dx_ir_dtype_roundtrip(const char *text, char *out, size_t cap) { return put(typedef_str(typedef_of(text ? text : "")), out, cap); }
+
+int dx_ir_plan_fusion(const char *program, const char *existing, char *out, size_t cap) {
+    try {
+        std::vector<TF> prog;
+        std::istringstream ps(program ? program : "");
+        std::string line;
+        while (std::getline(ps, line))
+            if (line.find_first_not_of(" \t\r") != std::string::npos) prog.emplace_back(line);
+        std::unordered_map<std::string, std::pair<uint16_t, std::vector<int64_t>>> known;
+        std::istringstream es(existing ? existing : "");
+        while (std::getline(es, line)) {
+            std::istringstream ls(line);
+            std::string name, dtype;
+            if (!(ls >> name >> dtype)) continue;
+            std::vector<int64_t> shape;
+            int64_t d;
+            while (ls >> d) shape.push_back(d);
+            known[name] = {precision_of(dtype), shape};
+        }
+        FusionStats st;
+        const auto plan = plan_fusion(prog, [&](const std::string &n, uint16_t &p, std::vector<int64_t> &s) {
+            auto it = known.find(n);
+            if (it == known.end()) return false;
+            p = it->second.first;
+            s = it->second.second;
+            return true;
+        }, &st);
+        std::string text;
+        for (size_t i = 0; i < plan.size(); ++i) {
+            if (plan[i].kind == PlanItem::RUN) text += "run\n";
+            else if (plan[i].kind == PlanItem::ABSORBED) text += "absorbed " + std::to_string(plan[i].group) + "\n";
+            else text += "fused " + std::to_string(plan[i].group) + " " + plan[i].fused.to_string() + "\n";
+        }
+        if (put(text, out, cap) < 0) return -1;
+        return int(st.rmsnorm_groups + st.softmax_groups);
+    } catch (const std::exception &ex) {
+        g_err = ex.what();
+        return -1;
+    }
+}
 
 void *dx_registry_new(int with_builtin_ops) {
     auto *r = new Registry();

@@ -1,5 +1,6 @@
 // deepxIR host core — see core.hpp.
 #include "core.hpp"
+#include "fusion.hpp"
 
 #include <cuda_runtime.h>
 
@@ -642,7 +643,10 @@ std::string TfFactory::print_markdown(const std::string &executor_name) const {
 // ============================================================================================
 // executor
 // ============================================================================================
-Executor::Executor(int device, size_t pool_limit_bytes) : mem_(device, pool_limit_bytes) { register_all(factory_); }
+Executor::Executor(int device, size_t pool_limit_bytes) : mem_(device, pool_limit_bytes) {
+    register_all(factory_);
+    register_fused(factory_);
+}
 
 OpResp Executor::run(const TF &call) {
     OpResp resp;
@@ -696,6 +700,49 @@ OpResp Executor::run_line(const std::string &ir) {
         return resp;
     }
     return run(call);
+}
+
+std::vector<OpResp> Executor::run_program(const std::string &text) {
+    std::vector<std::string> lines;
+    {
+        std::istringstream ss(text);
+        std::string line;
+        while (std::getline(ss, line)) {
+            if (!line.empty() && line.back() == '\r') line.pop_back();
+            if (line.find_first_not_of(" \t") != std::string::npos) lines.push_back(line);
+        }
+    }
+    std::vector<OpResp> replies;
+    replies.reserve(lines.size());
+    const auto now = std::chrono::system_clock::now();
+    std::vector<TF> program(lines.size());
+    bool parsed = fuse && lines.size() > 1;
+    for (size_t i = 0; parsed && i < lines.size(); ++i) {
+        try {
+            program[i].metadata.recv_at = now;
+            program[i].parse(lines[i]);
+        } catch (const std::exception &) {
+            parsed = false;  // the line-by-line path reports the error where it belongs
+        }
+    }
+    if (!parsed) {
+        for (const auto &l : lines) replies.push_back(run_line(l));
+        return replies;
+    }
+    const std::vector<PlanItem> plan = plan_fusion(program, mem_, &fusion_);
+    for (size_t i = 0; i < program.size(); ++i) {
+        if (plan[i].kind == PlanItem::ABSORBED) {
+            OpResp r;
+            r.id = program[i].metadata.id;
+            r.recv_at = now;
+            r.start_at = std::chrono::system_clock::now();
+            r.finish("");
+            replies.push_back(r);
+        } else {
+            replies.push_back(run(plan[i].kind == PlanItem::FUSED ? plan[i].fused : program[i]));
+        }
+    }
+    return replies;
 }
 
 }  // namespace dxh

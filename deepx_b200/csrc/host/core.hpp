@@ -215,6 +215,15 @@ class TfFactory {
 };
 
 int register_all(TfFactory &factory);   // the op table of executor/op-cuda/src/client/tfs.cpp
+int register_fused(TfFactory &factory); // rmsnorm / softmax: the single-kernel forms of the front end's op chains
+
+// What the fusion pass (fusion.hpp) has done so far.
+struct FusionStats {
+    uint64_t programs = 0;        // programs seen by the pass
+    uint64_t rmsnorm_groups = 0;  // chains rewritten
+    uint64_t softmax_groups = 0;
+    uint64_t lines_absorbed = 0;  // IR lines that no longer run (chain steps, temp newtensor/deltensor)
+};
 
 // ---- executor: one IR line in, one reply out (executor/op-cuda/src/client/main.cpp:47-102) --------------------
 class Executor {
@@ -222,6 +231,12 @@ class Executor {
     Executor(int device, size_t pool_limit_bytes);
     OpResp run(const TF &call);              // never throws: every failure becomes an "error" reply
     OpResp run_line(const std::string &ir);  // parse + run
+    // Several IR lines handed over together (one per text line): one reply per non-empty line, in
+    // order.  With `fuse` on, RMSNorm / softmax op chains whose temporaries live and die inside the
+    // program run as one kernel; the replies of the lines that no longer run say "ok".
+    std::vector<OpResp> run_program(const std::string &text);
+    const FusionStats &fusion_stats() const { return fusion_; }
+    bool fuse = true;
     Mem &mem() { return mem_; }
     const TfFactory &factory() const { return factory_; }
     uint64_t ops_run() const { return ops_run_; }
@@ -232,6 +247,7 @@ class Executor {
     TfFactory factory_;
     std::mutex mu_;
     uint64_t ops_run_ = 0;
+    FusionStats fusion_;
 };
 
 }  // namespace dxh

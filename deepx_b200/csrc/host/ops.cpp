@@ -678,6 +678,56 @@ struct LoadTensorDataTF : TF {
     }
 };
 
+// ---- fused row chains (no reference counterpart: what the fusion pass rewrites an op chain into) ---------------------
+// rmsnorm(x, weight, divisor, eps)->(out) and rmsnorm(x, divisor, eps)->(out) stand for the chain
+// powscalar(x,2)|mul(x,x), sum(last,keepdims), divscalar, addscalar, sqrt, rdivscalar(1), broadcastTo, mul
+// [, broadcastTo(weight), mul] of front/py/deepx/nn/modules/norm/t5layernorm.py:19-23; softmax(x)->(out)
+// for reducemax, broadcastTo, sub, exp, sum, broadcastTo, div over the last axis of
+// front/py/deepx/nn/functional/normalization.py:4-18.  Scalars take the same text → stof → dtype path.
+struct RmsNormTF : TF {
+    bool has_weight;
+    std::string formula;
+    RmsNormTF(bool weight, std::vector<Param> a, std::vector<Param> r)
+        : has_weight(weight), formula(weight ? "T3=W*(T1/sqrt(sum(T1^2,-1)/divisor+eps))" : "T3=T1/sqrt(sum(T1^2,-1)/divisor+eps)") {
+        name = "rmsnorm"; metadata.author = "b200"; tftype = "fused"; args = std::move(a); returns = std::move(r);
+    }
+    DX_TF_BOILERPLATE(RmsNormTF)
+    int run(Mem &mem, std::string &error) override {
+        const int di = has_weight ? 2 : 1;
+        std::vector<std::string> names{args[0].textvalue, returns[0].textvalue};
+        if (has_weight) names.push_back(args[1].textvalue);
+        if (!check_tensors(names, mem, error)) return 1;
+        auto X = mem.get_tensor(args[0].textvalue), O = mem.get_tensor(returns[0].textvalue);
+        TensorPtr W = has_weight ? mem.get_tensor(args[1].textvalue) : nullptr;
+        if (X->shape.dtype != O->shape.dtype || (W && W->shape.dtype != X->shape.dtype)) {
+            error = W ? type_mismatch({X->shape.dtype, W->shape.dtype, O->shape.dtype}) : type_mismatch({X->shape.dtype, O->shape.dtype});
+            return 1;
+        }
+        if (X->shape.dim() < 1 || X->shape.shape != O->shape.shape) throw std::invalid_argument("shape mismatch");
+        const int64_t cols = X->shape.shape.back();
+        if (W && (W->shape.size != cols || W->shape.dim() < 1 || W->shape.shape.back() != cols))
+            throw TensorShapeError("rmsnorm: weight must hold one row of " + std::to_string(cols) + " elements");
+        const Scalar d = scalar_for(*this, di, mem), e = scalar_for(*this, di + 1, mem);
+        dx_check(dx_rmsnorm(X->dx(), X->data, W ? W->data : nullptr, O->data, cols ? X->shape.size / cols : 0, cols, d.f, e.f, mem.stream()));
+        return 0;
+    }
+};
+
+struct SoftmaxTF : TF {
+    std::string formula = "T3=softmax(T1, axis=-1)";
+    SoftmaxTF(std::vector<Param> a, std::vector<Param> r) { name = "softmax"; metadata.author = "b200"; tftype = "fused"; args = std::move(a); returns = std::move(r); }
+    DX_TF_BOILERPLATE(SoftmaxTF)
+    int run(Mem &mem, std::string &error) override {
+        if (!check_tensors({args[0].textvalue, returns[0].textvalue}, mem, error)) return 1;
+        auto X = mem.get_tensor(args[0].textvalue), O = mem.get_tensor(returns[0].textvalue);
+        if (X->shape.dtype != O->shape.dtype) { error = type_mismatch({X->shape.dtype, O->shape.dtype}); return 1; }
+        if (X->shape.dim() < 1 || X->shape.shape != O->shape.shape) throw std::invalid_argument("shape mismatch");
+        const int64_t cols = X->shape.shape.back();
+        dx_check(dx_softmax(X->dx(), X->data, O->data, cols ? X->shape.size / cols : 0, cols, mem.stream()));
+        return 0;
+    }
+};
+
 // ---- registration helpers ---------------------------------------------------------------------------------------------------
 Param T(const char *n, uint16_t p = P_ANY) { return Param(n, CAT_TENSOR, p); }
 Param V(const char *n, uint16_t p = P_ANY) { return Param(n, CAT_VAR, p); }
@@ -761,6 +811,15 @@ int register_all(TfFactory &f) {
     f.add_tf(std::make_shared<ReduceTF>("prod", DX_PROD, "B = prod(A, axis=[1 2], keepdims=false)", PV{T("A"), Vec("dims", P_I32), V("keepdims", P_BOOL)}, PV{T("B")}));
     f.add_tf(std::make_shared<ReduceTF>("reducemax", DX_RMAX, "B = reducemax(A, axis=[1 2], keepdims=false)", PV{T("A"), Vec("dims", P_I32), V("keepdims", P_BOOL)}, PV{T("B")}));
     f.add_tf(std::make_shared<ReduceTF>("reducemin", DX_RMIN, "B = reducemin(A, axis=[1 2], keepdims=false)", PV{T("A"), Vec("dims", P_I32), V("keepdims", P_BOOL)}, PV{T("B")}));
+    return 0;
+}
+
+// Ops beyond the reference's table: the single-kernel forms of the RMSNorm and softmax chains.
+int register_fused(TfFactory &f) {
+    const uint16_t F4 = P_F64 | P_F32 | P_F16 | P_BF16;
+    f.add_tf(std::make_shared<RmsNormTF>(true, PV{T("x", F4), T("weight", F4), V("divisor"), V("eps")}, PV{T("out", F4)}));
+    f.add_tf(std::make_shared<RmsNormTF>(false, PV{T("x", F4), V("divisor"), V("eps")}, PV{T("out", F4)}));
+    f.add_tf(std::make_shared<SoftmaxTF>(PV{T("x", F4)}, PV{T("out", F4)}));
     return 0;
 }
 

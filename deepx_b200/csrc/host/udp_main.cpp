@@ -7,7 +7,8 @@
 // exception becomes an error reply instead of ending the process.
 //
 // Environment: DEEPX_PORT (9090), DEEPX_DEVICE (0), DEEPX_POOL_BYTES (0 = unlimited),
-// DEEPX_IR_LOG (1|true echoes each op), DEEPX_OP_TABLE (path to write the markdown op table).
+// DEEPX_IR_LOG (1|true echoes each op), DEEPX_OP_TABLE (path to write the markdown op table),
+// DEEPX_FUSE (0 turns the chain-fusion pass over multi-line datagrams off).
 #include <arpa/inet.h>
 #include <sys/socket.h>
 #include <unistd.h>
@@ -39,6 +40,7 @@ int main() {
     }
     env = std::getenv("DEEPX_IR_LOG");
     ex->ir_log = env && (std::strcmp(env, "1") == 0 || strcasecmp(env, "true") == 0);
+    if ((env = std::getenv("DEEPX_FUSE"))) ex->fuse = std::strcmp(env, "0") != 0;
     if ((env = std::getenv("DEEPX_OP_TABLE"))) {
         std::ofstream md(env);
         if (md.is_open()) md << ex->factory().print_markdown("op-b200");
@@ -64,11 +66,10 @@ int main() {
         const ssize_t n = recvfrom(fd, buf.data(), buf.size() - 1, 0, reinterpret_cast<sockaddr *>(&cli), &len);
         if (n <= 0) continue;
         buf[size_t(n)] = 0;
-        std::istringstream lines(std::string(buf.data(), size_t(n)));
-        std::string line;
-        while (std::getline(lines, line)) {
-            if (line.empty()) continue;
-            const std::string reply = ex->run_line(line).to_string();
+        // one reply datagram per IR line, in order; a datagram of several lines is a program
+        // (chains of single ops inside it may run fused)
+        for (const OpResp &r : ex->run_program(std::string(buf.data(), size_t(n)))) {
+            const std::string reply = r.to_string();
             sendto(fd, reply.data(), reply.size(), 0, reinterpret_cast<sockaddr *>(&cli), len);
         }
     }

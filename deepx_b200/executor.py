@@ -19,6 +19,9 @@ SIGNATURES = {
     "dx_exec_destroy": (None, [_vp]),
     "dx_exec_last_error": (_cp, []),
     "dx_exec_run": (_i, [_vp, _cp, C.c_char_p, _sz]),
+    "dx_exec_run_program": (_i, [_vp, _cp, C.c_char_p, _sz]),
+    "dx_exec_set_fusion": (None, [_vp, _i]),
+    "dx_exec_fusion_stats": (None, [_vp, C.POINTER(C.c_uint64)]),
     "dx_exec_tensor_info": (_i, [_vp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int64), _i]),
     "dx_exec_tensor_ptr": (_vp, [_vp, _cp]),
     "dx_exec_upload": (_i, [_vp, _cp, _vp, _sz]),
@@ -29,6 +32,7 @@ SIGNATURES = {
     "dx_exec_stats": (None, [_vp, C.POINTER(C.c_size_t)]),
     "dx_ir_parse": (_i, [_cp, C.c_char_p, _sz]),
     "dx_ir_dtype_roundtrip": (_i, [_cp, C.c_char_p, _sz]),
+    "dx_ir_plan_fusion": (_i, [_cp, _cp, C.c_char_p, _sz]),
     "dx_registry_new": (_vp, [_i]),
     "dx_registry_free": (None, [_vp]),
     "dx_registry_add": (_i, [_vp, _cp]),
@@ -71,6 +75,16 @@ def dtype_roundtrip(text: str) -> str:
     buf = C.create_string_buffer(4096)
     lib().dx_ir_dtype_roundtrip(text.encode(), buf, len(buf))
     return buf.value.decode()
+
+
+def plan_fusion(program: str, existing: str = "") -> tuple[int, list[str]]:
+    """The fusion pass alone (no GPU): (number of fused groups, one verdict per program line —
+    "run", "absorbed <group>" or "fused <group> <op>").  `existing`: "<name> <dtype> <d0> <d1> …" lines."""
+    buf = C.create_string_buffer(max(1 << 16, 4 * len(program) + 4096))
+    n = lib().dx_ir_plan_fusion(program.encode(), existing.encode(), buf, len(buf))
+    if n < 0:
+        raise ValueError("plan_fusion: " + lib().dx_exec_last_error().decode())
+    return n, buf.value.decode().splitlines()
 
 
 class Registry:
@@ -123,6 +137,26 @@ class Executor:
         if rc != 0:
             raise IRError(text)
         return text
+
+    def run_program(self, program: str, check: bool = True) -> list[str]:
+        """Runs several IR lines handed over together (chains of single ops in it may run fused);
+        returns one reply per non-empty line.  With `check`, an error reply raises IRError."""
+        buf = C.create_string_buffer(max(1 << 16, 256 * (program.count("\n") + 2)))
+        rc = lib().dx_exec_run_program(self._h, program.encode(), buf, len(buf))
+        if rc < 0:
+            raise RuntimeError(lib().dx_exec_last_error().decode())
+        replies = buf.value.decode().split("\n") if buf.value else []
+        if check and rc != 0:
+            raise IRError("\n".join(r for r in replies if " ok" not in r.split("//")[0]))
+        return replies
+
+    def set_fusion(self, on: bool) -> None:
+        lib().dx_exec_set_fusion(self._h, 1 if on else 0)
+
+    def fusion_stats(self) -> dict:
+        st = (C.c_uint64 * 4)()
+        lib().dx_exec_fusion_stats(self._h, st)
+        return {"programs": st[0], "rmsnorm_groups": st[1], "softmax_groups": st[2], "lines_absorbed": st[3]}
 
     def info(self, name: str):
         dt = C.c_int()

@@ -266,6 +266,34 @@ def reducemax(A, dims, keepdims, B): _reduce(N.RMAX, A, dims, keepdims, B)
 def reducemin(A, dims, keepdims, B): _reduce(N.RMIN, A, dims, keepdims, B)
 
 
+# ---- fused row chains (no single reference function: the front end's RMSNorm / softmax op chains) --------
+def rmsnorm(X: torch.Tensor, weight, divisor: float, eps: float, Out: torch.Tensor) -> None:
+    """Out = weight * (X * 1/sqrt(sum(X^2, last axis)/divisor + eps)); `weight` [cols] or None."""
+    _dev(X, Out) if weight is None else _dev(X, Out, weight)
+    _same_dtype(X, Out) if weight is None else _same_dtype(X, Out, weight)
+    if X.shape != Out.shape or X.dim() < 1:
+        raise ValueError("shape mismatch")
+    cols = X.shape[-1]
+    if weight is not None and weight.numel() != cols:
+        raise ValueError("weight does not match the last axis")
+    rows = X.numel() // cols if cols else 0
+    with torch.cuda.device(X.device):
+        N.check(N.lib.dx_rmsnorm(dtype_code(X), X.data_ptr(), None if weight is None else weight.data_ptr(), Out.data_ptr(),
+                                 rows, cols, float(divisor), float(eps), _stream(X)))
+
+
+def softmax(X: torch.Tensor, Out: torch.Tensor) -> None:
+    """Out = softmax(X) over the last axis, as the chain reducemax, sub, exp, sum, div computes it."""
+    _dev(X, Out)
+    _same_dtype(X, Out)
+    if X.shape != Out.shape or X.dim() < 1:
+        raise ValueError("shape mismatch")
+    cols = X.shape[-1]
+    rows = X.numel() // cols if cols else 0
+    with torch.cuda.device(X.device):
+        N.check(N.lib.dx_softmax(dtype_code(X), X.data_ptr(), Out.data_ptr(), rows, cols, _stream(X)))
+
+
 # ---- changeshape -----------------------------------------------------------------------------------------
 def transpose(A: torch.Tensor, dim_order: Sequence[int], Cc: torch.Tensor) -> None:
     _dev(A, Cc)

@@ -32,6 +32,22 @@ const char *dx_exec_last_error(void);
  * reply is an error reply, -1 when reply does not fit. */
 int dx_exec_run(dx_exec *e, const char *ir_line, char *reply, size_t cap);
 
+/* Runs a program: several IR lines in one text, one per line (what one UDP datagram may carry,
+ * executor/deepxcore/src/client/udpserver.cpp:49-58).  The replies, one per non-empty line and in
+ * order, are written into replies[cap] separated by '\n'.  Before running, the fusion pass looks
+ * for the op chains the front end emits for RMSNorm
+ * (front/py/deepx/nn/modules/norm/t5layernorm.py:19-23) and softmax
+ * (front/py/deepx/nn/functional/normalization.py:4-18); a chain whose intermediate tensors are
+ * created and deleted inside the program and used by nothing else runs as ONE kernel
+ * (dx_rmsnorm / dx_softmax), and the lines it absorbed are answered "ok" without running.  The
+ * reference has no such pass (one launch per line).  Returns the number of error replies, or -1
+ * when the replies do not fit. */
+int dx_exec_run_program(dx_exec *e, const char *program, char *replies, size_t cap);
+/* Fusion on (default) / off for dx_exec_run_program. */
+void dx_exec_set_fusion(dx_exec *e, int on);
+/* [0] programs seen, [1] RMSNorm chains rewritten, [2] softmax chains rewritten, [3] IR lines absorbed. */
+void dx_exec_fusion_stats(dx_exec *e, uint64_t stats[4]);
+
 /* Tensor metadata: dtype is a dx_dtype code; shape receives up to cap extents; returns the rank,
  * or -1 if there is no such tensor. */
 int dx_exec_tensor_info(dx_exec *e, const char *name, int *dtype, int64_t *shape, int cap);
@@ -54,6 +70,11 @@ void dx_exec_stats(dx_exec *e, size_t stats[5]);
  * "<name>|<arg dtype>:<arg text>,…|<ret dtype>:<ret text>,…|author=<a> id=<n> repeat=<n>", or "!<error>". */
 int dx_ir_parse(const char *ir_line, char *out, size_t cap);
 int dx_ir_dtype_roundtrip(const char *text, char *out, size_t cap);
+/* The fusion pass alone, no GPU needed.  `existing` lists tensors that exist before the program,
+ * one per line as "<name> <dtype name> <d0> <d1> …" (may be NULL or empty).  Writes one line per
+ * program line: "run", "absorbed <group>" or "fused <group> <the op that runs instead>".
+ * Returns the number of fused groups, or -1 (parse error, or the text does not fit). */
+int dx_ir_plan_fusion(const char *program, const char *existing, char *out, size_t cap);
 /* A registry without an executor: add signature lines, ask which registration a call resolves to. */
 void *dx_registry_new(int with_builtin_ops);
 void dx_registry_free(void *r);

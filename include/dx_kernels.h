@@ -188,6 +188,26 @@ int dx_reduce(int op, int dtype, const void *a, const int64_t *shape, int ndim, 
 int dx_reduce_noalloc(int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
                       int ndims, void *out, void *stream);
 
+/* ---- fused row chains --------------------------------------------------------
+ * The reference has no single function for these: its front end builds RMSNorm
+ * (front/py/deepx/nn/modules/norm/t5layernorm.py:19-23) and softmax
+ * (front/py/deepx/nn/functional/normalization.py:4-18) out of single ops, one
+ * kernel launch and one pass over HBM each.  These two calls run such a chain
+ * over contiguous rows in one pass (the row stays in registers).  Each step uses
+ * the arithmetic of the single op it stands for, rounding to `dtype` included,
+ * so the result differs from the op-by-op chain only by the order of the
+ * additions inside the row sum.  Float dtypes only.  `out` may alias `x`.
+ *
+ * dx_rmsnorm: out[r,i] = weight[i] * (x[r,i] * (1 / sqrt(sum_i(x[r,i]^2) / divisor + eps)))
+ *             — powscalar(x,2)|mul(x,x), sum(last,keepdims), divscalar(divisor),
+ *             addscalar(eps), sqrt, rdivscalar(1), broadcastTo, mul, [broadcastTo(weight), mul].
+ *             `weight` (cols elements) may be NULL: the last multiply is then left out.
+ * dx_softmax: m = max_i x[r,i]; e_i = exp(x[r,i] - m); out[r,i] = e_i / sum_i e_i
+ *             — reducemax(last,keepdims), broadcastTo, sub, exp, sum(last,keepdims), broadcastTo, div. */
+int dx_rmsnorm(int dtype, const void *x, const void *weight, void *out, int64_t rows, int64_t cols, double divisor,
+               double eps, void *stream);
+int dx_softmax(int dtype, const void *x, void *out, int64_t rows, int64_t cols, void *stream);
+
 /* ---- changeshape -----------------------------------------------------------
  * Replace launch_transpose/concat/broadcastTo/indexselect/repeat
  * (changeshape_miaobyte.cuh:16-88).  Pure data movement, bit-exact for every

@@ -75,6 +75,36 @@ def main():
             (OUT / name).write_text("\n".join(lines) + "\n")
         print(f"{ex}: {len(lines)} IR lines")
 
+    record_chains(srv)
+
+
+def record_chains(srv):
+    """The op chains of the two normalisation layers, as the front end's own functions emit them.
+
+    softmax: deepx.nn.functional.softmax as it is (normalization.py:4-18).  RMSNorm: the three
+    statements of T5LayerNorm.forward (t5layernorm.py:19-23) run one by one, because the module as
+    written stops on its own asserts (mean(-1) wants a tuple, and weight * x wants equal ranks):
+    the tuple and a reshape of the weight are supplied here, the ops sent are the front end's."""
+    from deepx import arange, constant_, rsqrt, softmax
+    from deepx.nn.modules.norm import RMSNorm
+    start = len(srv.lines)
+    x = arange(0, 48, 1, dtype="float32").reshape_((2, 3, 8))
+    x.div_(10.0)
+    x.sub_(2.0)
+    norm = RMSNorm(8, eps=1e-6)
+    constant_(norm.weight, 0.5)  # as examples/4_transformer/llama/1_llama_rmsnorm.py does
+    setup = srv.lines[start:]
+    start = len(srv.lines)
+    variance = x.float().pow(2).mean((-1,), keepdim=True)
+    xn = x * rsqrt(variance + norm.variance_epsilon)
+    out = norm.weight.reshape((1, 1, 8)) * xn
+    (OUT / "chains__rmsnorm_forward.ir").write_text("\n".join(setup + srv.lines[start:]) + "\n")
+    print(f"chains/rmsnorm_forward: {len(setup)} setup + {len(srv.lines) - start} IR lines "
+          f"(input tensor {x.name}, weight {norm.weight.name}, output {out.name})")
+    start = len(srv.lines)
+    sm = softmax(x, [-1])
+    (OUT / "chains__softmax.ir").write_text("\n".join(setup + srv.lines[start:]) + "\n")
+    print(f"chains/softmax: {len(setup)} setup + {len(srv.lines) - start} IR lines (input tensor {x.name}, output {sm.name})")
 
 if __name__ == "__main__":
     main()
