@@ -33,6 +33,23 @@ def test_executor_library_exports_every_declared_symbol():
     assert names == set(E.SIGNATURES)
 
 
+def test_heapmem_symbols_are_exported():
+    from deepx_b200 import heapmem as H
+    names = declared("dx_heapmem.h")
+    lib = H.lib()
+    for n in sorted(names):
+        assert hasattr(lib, n), f"{n} is declared in dx_heapmem.h but not exported"
+    assert names == set(H.SIGNATURES)
+
+
+def test_fused_calls_validate_on_the_host():
+    from deepx_b200 import _native as N
+    assert N.lib.dx_rmsnorm(N.I32, 8, None, 8, 4, 4, 4.0, 1e-6, None) == N.E_DTYPE
+    assert N.lib.dx_softmax(N.F32, 8, 8, 4, 0, None) == N.E_SHAPE
+    assert N.lib.dx_softmax(N.F32, 8, 8, 0, 16, None) == N.OK            # no rows: nothing to do
+    assert N.lib.dx_rmsnorm(N.F32, None, None, None, 4, 4, 4.0, 1e-6, None) == N.E_ARG
+
+
 def test_argument_validation_needs_no_gpu():
     """Bad arguments are rejected on the host before anything touches a device."""
     from deepx_b200 import _native as N
