@@ -841,6 +841,260 @@ __global__ void __launch_bounds__(F_THREADS, 1)
     }
 }
 
+// ---- float32, CTA-pair form: a 256 × 256 tile per pair of SMs ---------------------------------------
+// The one-CTA kernel above is bound by shared-memory bandwidth, not by the tensor pipe: per
+// 128 × 128 × 32 block the splitters move 96 KiB and the three MMAs read 96 KiB of operands.  With
+// cta_group::2 each CTA still loads and splits a 128 × 32 slice of A and a 32 × 128 half of B
+// (same 64 KiB stage, same splitter work) but the pair computes 256 × 256, so every operand byte
+// read from shared memory feeds twice the flops.  Protocol as in the bf16 pair kernel, plus the
+// split step: each CTA's TMA completes on its OWN `raw` barrier (its own splitters wait there);
+// all eight splitter warps of the pair arrive on the LEADER's `split` barrier (release at cluster
+// scope, after the proxy fence), where the one MMA thread waits with a cluster-scope acquire.
+constexpr int FP_BN = 256;
+constexpr int FP_TMEM_COLS = ACC_STAGES * FP_BN;  // 512
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (true) {
+        if (mbar_try_wait_cluster(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D f32, A and B tf32, A K-major, B MN-major, N = 256, M = 256 (128 rows in each CTA's TMEM)
+__host__ __device__ constexpr uint32_t make_idesc_tf32_pair() {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (0u << 15) | (1u << 16) | (uint32_t(FP_BN >> 3) << 17) | (uint32_t(PBM >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(F_THREADS, 1)
+    gemm_tf32x3_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                            float *__restrict__ C, PairParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + F_STAGES * F_STAGE_BYTES;
+    auto raw_bar = [&](int s) { return bars + 8u * s; };                       // this CTA's TMA → this CTA's splitters
+    auto split_bar = [&](int s) { return bars + 8u * (F_STAGES + s); };        // both CTAs' splitters → leader's MMA thread
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * F_STAGES + s); };    // MMA → each CTA's TMA (commit to both)
+    auto tfull_bar = [&](int a) { return bars + 8u * (3 * F_STAGES + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (3 * F_STAGES + ACC_STAGES + a); };  // leader: 8 epilogue warps
+    constexpr int SLOT_OFF = 8 * (3 * F_STAGES + 2 * ACC_STAGES);
+    const uint32_t tmem_slot = bars + SLOT_OFF;
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + F_STAGES * F_STAGE_BYTES + SLOT_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + F_STAGES * F_STAGE_BYTES + SLOT_OFF + 8);
+    auto a_hi = [&](int s) { return smem_base + s * F_STAGE_BYTES; };
+    auto b_hi = [&](int s) { return smem_base + s * F_STAGE_BYTES + F_A_BYTES; };
+    auto a_lo = [&](int s) { return smem_base + s * F_STAGE_BYTES + F_RAW_BYTES; };
+    auto b_lo = [&](int s) { return smem_base + s * F_STAGE_BYTES + F_RAW_BYTES + F_A_BYTES; };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1;
+    const int num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < F_STAGES; ++s) {
+            mbar_init(raw_bar(s), 1);
+            mbar_init(split_bar(s), 8);  // used in the leader only: 4 splitter warps × 2 CTAs
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < ACC_STAGES; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 8);  // used in the leader only
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, FP_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    auto tile_coords = [&](int tile, int &b, int &tm, int &tn) {
+        const int per_batch = p.tiles_m * p.tiles_n;
+        b = tile / per_batch;
+        const int t = tile - b * per_batch;
+        tn = t / p.tiles_m;
+        tm = t - tn * p.tiles_m;
+    };
+
+    if (warp == 0) {
+        // ===== TMA producer: this CTA's A slice and B half, completing on this CTA's raw barrier =====
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+                int b, tm, tn;
+                tile_coords(tile, b, tm, tn);
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_EMPTY); }
+                        ok = false;
+                        break;
+                    }
+                    mbar_expect_tx(raw_bar(stage), F_RAW_BYTES);
+                    tma_load_3d(a_hi(stage), &tmap_a, raw_bar(stage), kb * F_BK, tm * PBM + int(rank) * BM, b);
+#pragma unroll
+                    for (int j = 0; j < F_BN / F_B_BOX_N; ++j)
+                        tma_load_3d(b_hi(stage) + j * F_B_BOX_BYTES, &tmap_b, raw_bar(stage),
+                                    tn * FP_BN + int(rank) * F_BN + j * F_B_BOX_N, kb * F_BK, b);
+                    if (++stage == F_STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000ll) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ===== MMA issuer: one thread of the leader =====
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32_pair();
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+                if (!mbar_wait_cluster(tempty_bar(acc), acc_phase ^ 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_TMEM_EMPTY); }
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * FP_BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait_cluster(split_bar(stage), phase, abort_flag)) {
+                        if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_SPLIT); }
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+#pragma unroll
+                    for (int k = 0; k < F_BK / F_UMMA_K; ++k) {
+                        const uint64_t ah = make_smem_desc(a_hi(stage) + k * 32, 16, 1024);
+                        const uint64_t al = make_smem_desc(a_lo(stage) + k * 32, 16, 1024);
+                        const uint64_t bh = make_smem_desc(b_hi(stage) + k * 1024, F_B_BOX_BYTES, 512, 1);
+                        const uint64_t bl = make_smem_desc(b_lo(stage) + k * 1024, F_B_BOX_BYTES, 512, 1);
+                        umma_tf32_pair(tmem_d, al, bh, idesc, (kb | k) != 0);  // small terms first
+                        umma_tf32_pair(tmem_d, ah, bl, idesc, 1);
+                        umma_tf32_pair(tmem_d, ah, bh, idesc, 1);
+                    }
+                    umma_commit_pair(empty_bar(stage), 0x3);
+                    if (++stage == F_STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit_pair(tfull_bar(acc), 0x3);
+                if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+            }
+        }
+    } else if (warp < 6) {
+        // ===== epilogue: each CTA drains its own 128 rows × 256 columns =====
+        const int q = warp & 3;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        const bool vec_ok = (p.N % 4) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+        for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
+            int b, tm, tn;
+            tile_coords(tile, b, tm, tn);
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) {
+                if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL); }
+                break;
+            }
+            tc_fence_after();
+            const int row = tm * PBM + int(rank) * BM + q * 32 + lane;
+            float *crow = C + (size_t(b) * p.M + row) * p.N;
+#pragma unroll 1
+            for (int c0 = 0; c0 < FP_BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * FP_BN + c0, r);
+                tmem_ld_wait();
+                const int col = tn * FP_BN + c0;
+                if (row < p.M) {
+                    if (vec_ok && col + 32 <= p.N) {
+#pragma unroll
+                        for (int v = 0; v < 8; ++v)
+                            *reinterpret_cast<uint4 *>(crow + col + 4 * v) = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (col + j < p.N) crow[col + j] = __uint_as_float(r[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
+            if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+        }
+    } else {
+        // ===== splitters: warps 6..9 of BOTH CTAs; each CTA splits what its own TMA delivered =====
+        const int t = threadIdx.x - 6 * 32;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+            for (int kb = 0; kb < p.k_blocks; ++kb) {
+                if (!mbar_wait(raw_bar(stage), phase, abort_flag)) {
+                    if (lane == 0 && !*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_RAW); }
+                    ok = false;
+                    break;
+                }
+                float4 *hi = reinterpret_cast<float4 *>(gen_base + stage * F_STAGE_BYTES);
+                float4 *lo = reinterpret_cast<float4 *>(gen_base + stage * F_STAGE_BYTES + F_RAW_BYTES);
+#pragma unroll 4
+                for (int i = t; i < F_RAW_BYTES / 16; i += 128) {
+                    const float4 x = hi[i];
+                    float4 h, l;
+                    h.x = round_tf32(x.x); l.x = x.x - h.x;
+                    h.y = round_tf32(x.y); l.y = x.y - h.y;
+                    h.z = round_tf32(x.z); l.z = x.z - h.z;
+                    h.w = round_tf32(x.w); l.w = x.w - h.w;
+                    hi[i] = h;
+                    lo[i] = l;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(mapa_u32(split_bar(stage), 0));
+                if (++stage == F_STAGES) { stage = 0; phase ^= 1; }
+            }
+        }
+    }
+    // Teardown: the pair meets before either CTA leaves or frees TMEM.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, FP_TMEM_COLS);
+    }
+}
+
 // ---- SIMT FMA kernel for f32 / f64 (and shapes the TMA path cannot take) -----------------------
 template <typename T, typename A, int TS, int RT>
 __global__ void __launch_bounds__((TS / RT) * (TS / RT))
@@ -1052,6 +1306,37 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
 
 // float32 through the tensor cores (three TF32 products per product).
 bool g_tf32_attr[64] = {};
+int g_tf32_pair_slots[64] = {};
+bool g_tf32_pair_known[64] = {};
+// Resident CTA pairs of the float32 pair kernel on `dev` (0 = it cannot run there).
+int tf32_pair_slots(int dev) {
+    std::lock_guard<std::mutex> lk(g_setup_mu);
+    if (g_tf32_pair_known[dev]) return g_tf32_pair_slots[dev];
+    g_tf32_pair_known[dev] = true;
+    g_tf32_pair_slots[dev] = 0;
+    if (cudaFuncSetAttribute(gemm_tf32x3_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, F_SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2u * (unsigned)sm_count(), 1, 1);
+    cfg.blockDim = dim3(F_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = F_SMEM_BYTES;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tf32x3_pair_kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    g_tf32_pair_slots[dev] = n;
+    return n;
+}
 int launch_tf32x3(const float *A, const float *B, float *C, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1076,6 +1361,37 @@ int launch_tf32x3(const float *A, const float *B, float *C, int64_t batch, int64
     if (int e = make_map(&ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, F_BK, BM, 4)) return e;
     if (int e = make_map(&mb, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, F_B_BOX_N, F_BK, 4,
                          CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B)) return e;
+    // ---- CTA-pair form: once there is at least one 256 × 256 tile per resident pair ----
+    const int64_t ptiles_m = (M + PBM - 1) / PBM, ptiles_n = (N + FP_BN - 1) / FP_BN;
+    const int64_t ptiles = ptiles_m * ptiles_n * batch;
+    const int pairs = tf32_pair_slots(dev);
+    int mode = -1;
+    if (const char *env = std::getenv("DX_GEMM_CTA_PAIR")) mode = (env[0] == '1') ? 1 : (env[0] == '0' ? 0 : -1);
+    if (pairs > 0 && ptiles < (1ll << 31) && (mode == 1 || (mode == -1 && ptiles >= pairs))) {
+        PairParams pp;
+        pp.M = (int)M; pp.N = (int)N; pp.K = (int)K; pp.batch = (int)batch;
+        pp.tiles_m = (int)ptiles_m;
+        pp.tiles_n = (int)ptiles_n;
+        pp.num_tiles = (int)ptiles;
+        pp.k_blocks = (int)((K + F_BK - 1) / F_BK);
+        pp.status = status;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ptiles, pairs), 1, 1);
+        cfg.blockDim = dim3(F_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = F_SMEM_BYTES;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tf32x3_pair_kernel, ma, mb, C, pp);
+        if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tf32x3 pair): %s", cudaGetErrorString(e));
+        return check_launch("matmul(tf32x3 pair)");
+    }
+
     GemmParams p;
     p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
     p.tiles_m = (int)((M + BM - 1) / BM);

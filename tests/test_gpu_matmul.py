@@ -169,6 +169,41 @@ def test_matmul_fp32_tensor_core_path(mods, shape):
     check(TF, N, a3, b3, "float32", "matmul<float32 tf32x3> batched")
 
 
+@pytest.mark.parametrize("shape", [(256, 256, 32), (512, 768, 128), (1024, 1024, 1024), (100, 200, 72), (130, 264, 40),
+                                   (257, 1000, 520), (384, 516, 200), (1, 8, 8)])
+def test_matmul_fp32_cta_pair(mods, force_pair, shape):
+    """The float32 CTA-pair kernel (256 x 256 tile per SM pair), forced on shapes of every raggedness."""
+    TF, O, N = mods
+    M, Nn, K = shape
+    rng = np.random.default_rng(seed_of("mm32pair", shape))
+    a = make(rng, "float32", (M, K), -1.0, 1.0)
+    b = make(rng, "float32", (K, Nn), -1.0, 1.0)
+    got = check(TF, N, a, b, "float32", f"matmul pair<float32 tf32x3> {shape}")
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.abs(got - ref).max() / np.abs(ref).max() <= 1e-5
+    a3 = make(rng, "float32", (3, 300, 136), -1.0, 1.0)
+    b3 = make(rng, "float32", (3, 136, 264), -1.0, 1.0)
+    check(TF, N, a3, b3, "float32", "matmul pair<float32 tf32x3> batched")
+
+
+def test_matmul_fp32_both_forms_agree_bit_for_bit(mods, monkeypatch):
+    """Same products in the same K order into fp32 accumulators: one-CTA and pair kernels give identical bits."""
+    TF, O, N = mods
+    rng = np.random.default_rng(9)
+    a = make(rng, "float32", (1000, 520), -1.0, 1.0)
+    b = make(rng, "float32", (520, 776), -1.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    outs = []
+    for mode in ("0", "1"):
+        monkeypatch.setenv("DX_GEMM_CTA_PAIR", mode)
+        Cc = torch.empty((1000, 776), dtype=torch.float32, device="cuda:0")
+        TF.matmul(A, B, Cc)
+        N.check(N.lib.dx_matmul_status(None))
+        outs.append(to_np(Cc).view(np.uint32))
+    monkeypatch.delenv("DX_GEMM_CTA_PAIR", raising=False)
+    assert np.array_equal(outs[0], outs[1])
+
+
 def test_matmul_fp32_simt_path_is_tighter(mods, monkeypatch):
     """The FMA kernel (shapes TMA cannot take, or DX_GEMM_F32_SIMT=1) accumulates in plain fp32."""
     TF, O, N = mods
