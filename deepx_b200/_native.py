@@ -53,6 +53,16 @@ SIGNATURES = {
     "dx_reduce_workspace_bytes": (_sz, [_i, _i, _pi64, _i, _pi32, _i]),
     "dx_reduce": (_i, [_i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp, _sz, _vp]),
     "dx_reduce_noalloc": (_i, [_i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp]),
+    "dx_comm_max_bytes": (_sz, []),
+    "dx_comm_create": (_vp, [_i, _i, _i]),
+    "dx_comm_handle": (_i, [_vp, C.c_char_p]),
+    "dx_comm_connect": (_i, [_vp, C.c_char_p]),
+    "dx_comm_set_timeout_ms": (_i, [_vp, _i]),
+    "dx_comm_allreduce": (_i, [_vp, _i, _i, _vp, _i64, _vp]),
+    "dx_comm_status": (_i, [_vp, _vp]),
+    "dx_comm_destroy": (None, [_vp]),
+    "dx_comm_emulate": (_vp, [_i, _i]),
+    "dx_comm_emulated_allreduce": (_i, [_vp, _i, _i, _pvp, _i, _i64, _vp]),
     "dx_rmsnorm": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _d, _d, _vp]),
     "dx_softmax": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "dx_transpose": (_i, [_i, _vp, _pi64, _i, _pi32, _vp, _vp]),

@@ -1,0 +1,375 @@
+// dx_comm: the exchange step of a reduction that crosses the sharded axis, done by the GPUs
+// themselves over NVLink peer memory instead of by a library collective.
+//
+// Each rank (one process per GPU) owns a MAILBOX in its own device memory, exported with CUDA IPC
+// and mapped by every peer.  An all-reduce of a small buffer (the per-rank partials of a global
+// sum, a few KB at most for an axis-0 reduce of a narrow tensor) is ONE kernel per rank:
+//   1. every CTA takes one 4 KiB chunk, reads it from the local buffer and stores it into slot
+//      [parity][my rank] of EVERY rank's mailbox (plain 16-byte st.global to peer memory; no TMA,
+//      no multicast, no library call on peer pointers);
+//   2. fence, then one thread per peer publishes flag[parity][my rank][chunk] = epoch there
+//      (st.release.sys);
+//   3. one thread per peer waits (ld.acquire.sys, clock-bounded) until its own mailbox shows this
+//      epoch from that peer;
+//   4. the CTA combines the W slots in rank order 0..W-1 (so every rank computes the same bits)
+//      and writes the result back over the local buffer.
+// Slots and flags are double-buffered by epoch parity: a rank can start epoch e+1 while a peer
+// still reads epoch e, and cannot reach e+2 before every peer has published e+1, i.e. finished
+// reading e.  The epoch of a chunk lives in the mailbox and is advanced by the kernel itself, so a
+// captured launch can be replayed.
+//
+// Every wait is bounded (default 2 s, dx_comm_set_timeout_ms); when one expires the kernel records
+// which (chunk, peer) it gave up on, skips the combine and returns, and dx_comm_status reports it.
+// The reference has no multi-GPU code at all; the alternative here is an NCCL all-reduce of the
+// same partial, which deepx_b200/sharded.py uses for buffers larger than a mailbox slot.
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+#include "reduce_ops.cuh"
+
+namespace dx {
+namespace {
+
+constexpr int COMM_MAX_WORLD = 16;
+constexpr int COMM_CHUNK = 4096;                  // bytes per CTA
+constexpr int COMM_CHUNKS = 16;                   // chunks per slot
+constexpr int COMM_SLOT = COMM_CHUNK * COMM_CHUNKS;  // 64 KiB per (parity, rank)
+constexpr int COMM_THREADS = 256;
+
+struct Mailbox {
+    unsigned int flag[2][COMM_MAX_WORLD][COMM_CHUNKS];  // epoch last published by (rank, chunk)
+    unsigned int epoch[COMM_CHUNKS];                    // epochs this rank has completed per chunk
+    int status;                                         // 0, or 1 + chunk * 64 + peer of the wait that expired
+    int pad[15];
+    alignas(256) unsigned char slot[2][COMM_MAX_WORLD][COMM_SLOT];
+};
+
+struct Peers {
+    Mailbox *box[COMM_MAX_WORLD];
+    int world;
+};
+
+__device__ __forceinline__ void st_release_sys(unsigned int *p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// 16-bit __ldcg overloads do not exist for the float wrappers: go through the bit pattern.
+template <typename T> __device__ __forceinline__ T ldcg_any(const T *p) {
+    if constexpr (sizeof(T) == 2) {
+        const unsigned short u = __ldcg(reinterpret_cast<const unsigned short *>(p));
+        return *reinterpret_cast<const T *>(&u);
+    } else if constexpr (sizeof(T) == 1) {
+        const unsigned char u = __ldcg(reinterpret_cast<const unsigned char *>(p));
+        return *reinterpret_cast<const T *>(&u);
+    } else return __ldcg(p);
+}
+
+// The exchange for one rank and one chunk; `buf` is that rank's local data.
+template <int OP, typename T>
+__device__ void exchange_chunk(const Peers &peers, int rank, int chunk, T *buf, int64_t n, long long wait_cycles) {
+    constexpr int PER = COMM_CHUNK / int(sizeof(T));  // elements per chunk
+    constexpr int VEC = 16 / int(sizeof(T));
+    using A = acc_t<T>;
+    __shared__ int gave_up;
+    Mailbox *mine = peers.box[rank];
+    const int W = peers.world;
+    const int64_t first = int64_t(chunk) * PER;
+    const int count = int(n - first < PER ? n - first : PER);  // elements of this chunk
+    if (threadIdx.x == 0) gave_up = 0;
+    const unsigned int e = mine->epoch[chunk] + 1;  // only this CTA ever touches this chunk's epoch
+    const int par = int(e & 1u);
+
+    // 1. my chunk → slot [par][rank] of every mailbox (16-byte vectors; the tail of the last one is padding)
+    T *src = buf + first;
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+    for (int v = threadIdx.x; v * VEC < count; v += COMM_THREADS) {
+        Pack<T, VEC> pk;
+        if (vec_ok && (v + 1) * VEC <= count) pk = ld_cached<T, VEC>(src + v * VEC);
+        else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) pk.v[k] = (v * VEC + k < count) ? src[v * VEC + k] : narrow<T>(identity<OP, T>());
+        }
+        for (int p = 0; p < W; ++p) {
+            T *dst = reinterpret_cast<T *>(peers.box[p]->slot[par][rank] + size_t(chunk) * COMM_CHUNK);
+            *reinterpret_cast<Pack<T, VEC> *>(dst + v * VEC) = pk;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    // 2. publish, 3. wait: thread p talks to peer p
+    if (threadIdx.x < W) {
+        const int p = threadIdx.x;
+        st_release_sys(&peers.box[p]->flag[par][rank][chunk], e);
+        const long long t0 = clock64();
+        while (ld_acquire_sys(&mine->flag[par][p][chunk]) != e) {
+            if (clock64() - t0 > wait_cycles) {
+                atomicCAS(&mine->status, 0, 1 + chunk * 64 + p);
+                gave_up = 1;
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    // 4. combine in rank order; on a timeout leave the local data as it was
+    if (!gave_up) {
+        for (int i = threadIdx.x; i < count; i += COMM_THREADS) {
+            A acc = widen<T>(ldcg_any(reinterpret_cast<const T *>(mine->slot[par][0] + size_t(chunk) * COMM_CHUNK) + i));
+            for (int r = 1; r < W; ++r)
+                acc = combine<OP, A>(acc, widen<T>(ldcg_any(reinterpret_cast<const T *>(mine->slot[par][r] + size_t(chunk) * COMM_CHUNK) + i)));
+            src[i] = narrow<T>(acc);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mine->epoch[chunk] = e;  // advanced even after a timeout: the ranks stay in step
+}
+
+// One launch per rank: blockIdx.x = chunk.
+template <int OP, typename T>
+__global__ void __launch_bounds__(COMM_THREADS) peer_allreduce_kernel(Peers peers, int rank, T *buf, int64_t n, long long wait_cycles) {
+    exchange_chunk<OP, T>(peers, rank, blockIdx.x, buf, n, wait_cycles);
+}
+
+// All ranks in ONE launch on one GPU (blockIdx.y = rank), every mailbox local: the same protocol
+// where there are fewer GPUs than ranks.  Ranks >= `active` are left out, so that the others'
+// waits run into their limit (the failure path, without a second process that misbehaves).
+struct Bufs {
+    void *buf[COMM_MAX_WORLD];
+};
+template <int OP, typename T>
+__global__ void __launch_bounds__(COMM_THREADS) emulated_allreduce_kernel(Peers peers, Bufs bufs, int active, int64_t n, long long wait_cycles) {
+    if (int(blockIdx.y) >= active) return;
+    exchange_chunk<OP, T>(peers, blockIdx.y, blockIdx.x, static_cast<T *>(bufs.buf[blockIdx.y]), n, wait_cycles);
+}
+
+}  // namespace
+}  // namespace dx
+
+struct dx_comm {
+    int rank = 0, world = 1, device = 0;
+    dx::Mailbox *mine = nullptr;
+    dx::Peers peers{};
+    bool opened[dx::COMM_MAX_WORLD] = {};
+    bool connected = false;
+    long long wait_cycles = 4000000000ll;
+    std::vector<dx::Mailbox *> emulated;  // dx_comm_emulate: all mailboxes local
+};
+
+namespace dx {
+namespace {
+
+template <int OP, typename T> int launch_real(dx_comm *c, void *buf, int64_t n, cudaStream_t st) {
+    constexpr int PER = COMM_CHUNK / int(sizeof(T));
+    const int chunks = int((n + PER - 1) / PER);
+    peer_allreduce_kernel<OP, T><<<chunks, COMM_THREADS, 0, st>>>(c->peers, c->rank, static_cast<T *>(buf), n, c->wait_cycles);
+    return check_launch("comm allreduce");
+}
+template <int OP, typename T> int launch_emulated(dx_comm *c, void *const *bufs, int active, int64_t n, cudaStream_t st) {
+    constexpr int PER = COMM_CHUNK / int(sizeof(T));
+    const int chunks = int((n + PER - 1) / PER);
+    Bufs b{};
+    for (int r = 0; r < c->world; ++r) b.buf[r] = bufs[r];
+    emulated_allreduce_kernel<OP, T><<<dim3(chunks, c->world), COMM_THREADS, 0, st>>>(c->peers, b, active, n, c->wait_cycles);
+    return check_launch("comm allreduce (emulated ranks)");
+}
+
+#define DX_COMM_BY_OP(FN, T, ...)                                             \
+    switch (op) {                                                             \
+        case DX_SUM: return FN<DX_SUM, T>(__VA_ARGS__);                       \
+        case DX_PROD: return FN<DX_PROD, T>(__VA_ARGS__);                     \
+        case DX_RMAX: return FN<DX_RMAX, T>(__VA_ARGS__);                     \
+        case DX_RMIN: return FN<DX_RMIN, T>(__VA_ARGS__);                     \
+        default: return fail(DX_E_ARG, "comm: unknown reduce op %d", op);     \
+    }
+#define DX_COMM_DISPATCH(FN, ...)                                             \
+    switch (dtype) {                                                          \
+        case DX_F64: DX_COMM_BY_OP(FN, double, __VA_ARGS__)                   \
+        case DX_F32: DX_COMM_BY_OP(FN, float, __VA_ARGS__)                    \
+        case DX_F16: DX_COMM_BY_OP(FN, f16, __VA_ARGS__)                      \
+        case DX_BF16: DX_COMM_BY_OP(FN, bf16, __VA_ARGS__)                    \
+        case DX_I64: DX_COMM_BY_OP(FN, int64_t, __VA_ARGS__)                  \
+        case DX_I32: DX_COMM_BY_OP(FN, int32_t, __VA_ARGS__)                  \
+        case DX_I16: DX_COMM_BY_OP(FN, int16_t, __VA_ARGS__)                  \
+        case DX_I8: DX_COMM_BY_OP(FN, int8_t, __VA_ARGS__)                    \
+        default: return fail(DX_E_DTYPE, "comm: unsupported dtype code %d", dtype); \
+    }
+
+int real_dispatch(dx_comm *c, int op, int dtype, void *buf, int64_t n, cudaStream_t st) { DX_COMM_DISPATCH(launch_real, c, buf, n, st) }
+int emulated_dispatch(dx_comm *c, int op, int dtype, void *const *bufs, int active, int64_t n, cudaStream_t st) {
+    DX_COMM_DISPATCH(launch_emulated, c, bufs, active, n, st)
+}
+
+int check_size(int dtype, int64_t n) {
+    const int es = dx_dtype_size(dtype);
+    if (es == 0 || dtype == DX_BOOL) return fail(DX_E_DTYPE, "comm: unsupported dtype code %d", dtype);
+    if (n < 0) return fail(DX_E_SHAPE, "comm: negative count");
+    if (n * es > COMM_SLOT) return fail(DX_E_WORKSPACE, "comm: %lld bytes exceed the %d-byte mailbox slot (use a library all-reduce)", (long long)(n * es), COMM_SLOT);
+    return DX_OK;
+}
+
+int new_mailbox(Mailbox **out) {
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, sizeof(Mailbox));
+    if (e == cudaSuccess) e = cudaMemset(p, 0, sizeof(Mailbox));
+    if (e != cudaSuccess) return fail(DX_E_CUDA, "comm: mailbox allocation: %s", cudaGetErrorString(e));
+    *out = static_cast<Mailbox *>(p);
+    return DX_OK;
+}
+
+}  // namespace
+}  // namespace dx
+
+using namespace dx;
+
+extern "C" size_t dx_comm_max_bytes(void) { return COMM_SLOT; }
+
+extern "C" dx_comm *dx_comm_create(int rank, int world, int device) {
+    if (world < 1 || world > COMM_MAX_WORLD || rank < 0 || rank >= world) {
+        fail(DX_E_ARG, "comm: rank %d of %d (at most %d ranks)", rank, world, COMM_MAX_WORLD);
+        return nullptr;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) {
+        fail(DX_E_CUDA, "comm: cudaSetDevice(%d): %s", device, cudaGetErrorString(cudaGetLastError()));
+        return nullptr;
+    }
+    dx_comm *c = new (std::nothrow) dx_comm();
+    if (!c) return nullptr;
+    c->rank = rank;
+    c->world = world;
+    c->device = device;
+    if (new_mailbox(&c->mine) != DX_OK) {
+        delete c;
+        return nullptr;
+    }
+    c->peers.world = world;
+    c->peers.box[rank] = c->mine;
+    c->connected = world == 1;
+    return c;
+}
+
+extern "C" int dx_comm_handle(dx_comm *c, unsigned char out[64]) {
+    if (!c || !out) return fail(DX_E_ARG, "comm: null argument");
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    const cudaError_t e = cudaIpcGetMemHandle(&h, c->mine);
+    if (e != cudaSuccess) return fail(DX_E_CUDA, "comm: cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    std::memcpy(out, &h, 64);
+    return DX_OK;
+}
+
+extern "C" int dx_comm_connect(dx_comm *c, const unsigned char *handles) {
+    if (!c || !handles) return fail(DX_E_ARG, "comm: null argument");
+    if (cudaSetDevice(c->device) != cudaSuccess) return fail(DX_E_CUDA, "comm: cudaSetDevice failed");
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank || c->opened[r]) continue;
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, handles + size_t(r) * 64, 64);
+        void *p = nullptr;
+        const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) return fail(DX_E_CUDA, "comm: cannot map the mailbox of rank %d: %s", r, cudaGetErrorString(e));
+        c->peers.box[r] = static_cast<Mailbox *>(p);
+        c->opened[r] = true;
+    }
+    c->connected = true;
+    return DX_OK;
+}
+
+extern "C" int dx_comm_set_timeout_ms(dx_comm *c, int ms) {
+    if (!c || ms <= 0) return fail(DX_E_ARG, "comm: timeout must be positive");
+    int khz = 0;
+    if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device) != cudaSuccess || khz <= 0) khz = 1965000;
+    c->wait_cycles = (long long)ms * khz;
+    return DX_OK;
+}
+
+extern "C" int dx_comm_allreduce(dx_comm *c, int op, int dtype, void *buf, int64_t n, void *stream) {
+    if (!c || !buf) return fail(DX_E_ARG, "comm: null argument");
+    if (!c->connected) return fail(DX_E_ARG, "comm: dx_comm_connect has not been called");
+    if (!c->emulated.empty()) return fail(DX_E_ARG, "comm: this communicator emulates its ranks on one GPU; use dx_comm_emulated_allreduce");
+    if (int e = check_size(dtype, n)) return e;
+    if (n == 0) return DX_OK;
+    return real_dispatch(c, op, dtype, buf, n, as_stream(stream));
+}
+
+extern "C" int dx_comm_status(dx_comm *c, void *stream) {
+    if (!c) return fail(DX_E_ARG, "comm: null argument");
+    cudaStream_t st = as_stream(stream);
+    int worst = 0;
+    auto check = [&](Mailbox *m, int r) -> int {
+        int h = 0;
+        if (cudaMemcpyAsync(&h, &m->status, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess)
+            return fail(DX_E_CUDA, "comm: cannot read the status word: %s", cudaGetErrorString(cudaGetLastError()));
+        if (h != 0) {
+            cudaMemsetAsync(&m->status, 0, sizeof(int), st);
+            cudaStreamSynchronize(st);
+            worst = fail(DX_E_CUDA, "comm: rank %d gave up waiting for rank %d (chunk %d): peer absent or late", r, (h - 1) % 64, (h - 1) / 64);
+        }
+        return DX_OK;
+    };
+    if (c->emulated.empty()) {
+        if (int e = check(c->mine, c->rank)) return e;
+    } else {
+        for (int r = c->world - 1; r >= 0; --r)
+            if (int e = check(c->emulated[r], r)) return e;
+    }
+    return worst;
+}
+
+extern "C" void dx_comm_destroy(dx_comm *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    for (int r = 0; r < c->world; ++r)
+        if (c->opened[r]) cudaIpcCloseMemHandle(c->peers.box[r]);
+    if (c->emulated.empty()) cudaFree(c->mine);
+    for (Mailbox *m : c->emulated) cudaFree(m);
+    delete c;
+}
+
+extern "C" dx_comm *dx_comm_emulate(int world, int device) {
+    if (world < 1 || world > COMM_MAX_WORLD) {
+        fail(DX_E_ARG, "comm: %d ranks (at most %d)", world, COMM_MAX_WORLD);
+        return nullptr;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) {
+        fail(DX_E_CUDA, "comm: cudaSetDevice(%d) failed", device);
+        return nullptr;
+    }
+    dx_comm *c = new (std::nothrow) dx_comm();
+    if (!c) return nullptr;
+    c->world = world;
+    c->device = device;
+    c->peers.world = world;
+    for (int r = 0; r < world; ++r) {
+        Mailbox *m = nullptr;
+        if (new_mailbox(&m) != DX_OK) {
+            for (Mailbox *x : c->emulated) cudaFree(x);
+            delete c;
+            return nullptr;
+        }
+        c->emulated.push_back(m);
+        c->peers.box[r] = m;
+    }
+    c->mine = c->emulated[0];
+    c->connected = true;
+    return c;
+}
+
+extern "C" int dx_comm_emulated_allreduce(dx_comm *c, int op, int dtype, void *const *bufs, int active_ranks, int64_t n, void *stream) {
+    if (!c || !bufs) return fail(DX_E_ARG, "comm: null argument");
+    if (c->emulated.empty()) return fail(DX_E_ARG, "comm: not an emulating communicator (dx_comm_emulate)");
+    if (active_ranks < 1 || active_ranks > c->world) return fail(DX_E_ARG, "comm: %d active ranks of %d", active_ranks, c->world);
+    if (int e = check_size(dtype, n)) return e;
+    if (n == 0) return DX_OK;
+    // every CTA of the launch must be resident at once, since they wait on one another
+    const int es = dx_dtype_size(dtype);
+    const int64_t chunks = (n * es + COMM_CHUNK - 1) / COMM_CHUNK;
+    if (chunks * c->world > sm_count()) return fail(DX_E_UNSUPPORTED, "comm: %lld CTAs would not all be resident", (long long)(chunks * c->world));
+    return emulated_dispatch(c, op, dtype, bufs, active_ranks, n, as_stream(stream));
+}

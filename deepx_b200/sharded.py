@@ -5,8 +5,10 @@ partitioned into contiguous row blocks of its leading axis; every rank owns one 
 its own device pool.  Elementwise ops and reductions that do not touch axis 0 run on the
 local block with no communication; a reduction that includes axis 0 reduces the local
 block first and then combines the per-rank partials with ONE all-reduce (sum / product /
-max / min) — 4 bytes for a global sum, one row for an axis-0 reduce.  Ops that do not
-shard this way (matmul, general transposes) stay single-GPU.
+max / min) — 4 bytes for a global sum, one row for an axis-0 reduce.  Partials that fit a
+mailbox slot (64 KiB) are combined by the GPUs themselves over NVLink peer memory
+(:mod:`deepx_b200.comm`, one kernel per rank, no library collective); larger ones go to NCCL.
+Ops that do not shard this way (matmul, general transposes) stay single-GPU.
 
 The reference has no multi-GPU code at all (no cudaSetDevice, streams or NCCL anywhere
 under executor/); this module is the multi-GPU extension of its tensorfunc interface.
@@ -48,13 +50,17 @@ def shards_axis0(dims: Sequence[int], ndim: int) -> bool:
     return ndim > 0 and 0 in set(int(d) for d in dims)
 
 
-def combine_partials(partial: torch.Tensor, op: str, group=None) -> torch.Tensor:
-    """All-reduce per-rank partial results in place.  Works on any backend: NCCL on the
-    GPUs, gloo on CPU tensors in the host-logic tests."""
+def combine_partials(partial: torch.Tensor, op: str, group=None, peer=None) -> torch.Tensor:
+    """All-reduce per-rank partial results in place.  ``peer`` (a :class:`deepx_b200.comm.PeerComm`)
+    takes the partials that fit its mailbox; everything else goes to the group's backend: NCCL on
+    the GPUs, gloo on CPU tensors in the host-logic tests."""
     if op not in REDUCE_OPS:
         raise ValueError(f"unknown reduce op {op!r}")
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
-        dist.all_reduce(partial, op=REDUCE_OPS[op], group=group)
+        if peer is not None and peer.fits(partial):
+            peer.allreduce(partial, op)
+        else:
+            dist.all_reduce(partial, op=REDUCE_OPS[op], group=group)
     return partial
 
 
@@ -66,12 +72,22 @@ class ShardedOps:
     reduced the output holds the global result on every rank after the call.
     """
 
-    def __init__(self, group=None):
+    def __init__(self, group=None, peer_combine: bool | None = None):
+        """``peer_combine``: combine small partials with the peer-memory kernel instead of NCCL
+        (default: on when there is more than one rank, off with ``DX_PEER_COMBINE=0``).  Building
+        it is collective: every rank of the group constructs its ShardedOps at the same point."""
+        import os
         from . import tensorfunc  # needs the CUDA library; imported here so the partition logic is usable without it
         self.tf = tensorfunc
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if peer_combine is None:
+            peer_combine = os.environ.get("DX_PEER_COMBINE", "1") != "0"
+        self.peer = None
+        if peer_combine and self.world > 1 and torch.cuda.is_available():
+            from .comm import PeerComm
+            self.peer = PeerComm(group)
 
     def __getattr__(self, name):
         return getattr(self.tf, name)
@@ -80,7 +96,7 @@ class ShardedOps:
         getattr(self.tf, op)(A, dims, keepdims, B)
         cd = self.tf.checked_dims(A.shape, dims)
         if shards_axis0(cd, A.dim()):
-            combine_partials(B, op, self.group)
+            combine_partials(B, op, self.group, self.peer)
 
     def sum(self, A, dims, keepdims, B): self._reduce("sum", A, dims, keepdims, B)  # noqa: A003
     def prod(self, A, dims, keepdims, B): self._reduce("prod", A, dims, keepdims, B)

@@ -188,6 +188,33 @@ int dx_reduce(int op, int dtype, const void *a, const int64_t *shape, int ndim, 
 int dx_reduce_noalloc(int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
                       int ndims, void *out, void *stream);
 
+/* ---- cross-GPU combine (no reference counterpart: the reference is single-GPU) ----
+ * One process per GPU.  A reduction over the axis a tensor is sharded along leaves one partial
+ * per rank; dx_comm_allreduce combines them IN PLACE with one kernel per rank that stores its
+ * partial into every peer's mailbox over NVLink peer memory and combines the W partials in rank
+ * order (identical bits on every rank).  Buffers up to dx_comm_max_bytes(); larger ones belong to
+ * a library all-reduce.  Set-up: every rank calls dx_comm_create, exchanges the 64-byte handles
+ * of dx_comm_handle by any host channel, and gives all of them (world x 64 bytes, rank order) to
+ * dx_comm_connect.  All ranks must issue the same sequence of dx_comm_allreduce calls.
+ * Waits on a peer are bounded (2 s unless dx_comm_set_timeout_ms): when one expires the kernel
+ * leaves the local buffer untouched and returns; dx_comm_status (synchronises the stream) then
+ * reports DX_E_CUDA with the peer it gave up on, and the communicator should be discarded. */
+typedef struct dx_comm dx_comm;
+size_t dx_comm_max_bytes(void);
+dx_comm *dx_comm_create(int rank, int world, int device);
+int dx_comm_handle(dx_comm *c, unsigned char out[64]);
+int dx_comm_connect(dx_comm *c, const unsigned char *handles);
+int dx_comm_set_timeout_ms(dx_comm *c, int ms);
+int dx_comm_allreduce(dx_comm *c, int op, int dtype, void *buf, int64_t n, void *stream);
+int dx_comm_status(dx_comm *c, void *stream);
+void dx_comm_destroy(dx_comm *c);
+/* The same protocol with every rank on ONE GPU (all mailboxes local, all ranks' CTAs in one
+ * launch, which is the only safe way to run kernels that wait on each other on one device):
+ * bufs[r] is rank r's buffer.  Ranks >= active_ranks are left out, so the others' waits expire
+ * and dx_comm_status reports it — the failure path without a misbehaving process. */
+dx_comm *dx_comm_emulate(int world, int device);
+int dx_comm_emulated_allreduce(dx_comm *c, int op, int dtype, void *const *bufs, int active_ranks, int64_t n, void *stream);
+
 /* ---- fused row chains --------------------------------------------------------
  * The reference has no single function for these: its front end builds RMSNorm
  * (front/py/deepx/nn/modules/norm/t5layernorm.py:19-23) and softmax
