@@ -8,7 +8,8 @@
 //
 // Environment: DEEPX_PORT (9090), DEEPX_DEVICE (0), DEEPX_POOL_BYTES (0 = unlimited),
 // DEEPX_IR_LOG (1|true echoes each op), DEEPX_OP_TABLE (path to write the markdown op table),
-// DEEPX_FUSE (0 turns the chain-fusion pass over multi-line datagrams off).
+// DEEPX_FUSE (0 turns the chain-fusion pass over multi-line datagrams off).  SIGUSR1 prints a
+// counters line (ops run, tensors, pool bytes, fused chains); the same line is printed at exit.
 #include <arpa/inet.h>
 #include <sys/socket.h>
 #include <unistd.h>
@@ -22,8 +23,18 @@
 
 #include "core.hpp"
 
-static volatile sig_atomic_t g_stop = 0;
+static volatile sig_atomic_t g_stop = 0, g_report = 0;
 static void on_signal(int) { g_stop = 1; }
+static void on_usr1(int) { g_report = 1; }
+
+static void report(dxh::Executor &ex) {
+    size_t st[4];
+    dx_pool_stats(ex.mem().pool(), st);
+    const dxh::FusionStats &f = ex.fusion_stats();
+    std::cout << "deepx-op-b200: " << ex.ops_run() << " ops run, " << ex.mem().tensor_count() << " tensors, pool in use " << st[0]
+              << " bytes, high-water " << st[2] << " bytes, " << st[3] << " driver allocations; fused chains: " << f.rmsnorm_groups
+              << " rmsnorm, " << f.softmax_groups << " softmax, " << f.lines_absorbed << " IR lines absorbed" << std::endl;
+}
 
 int main() {
     using namespace dxh;
@@ -57,6 +68,7 @@ int main() {
     setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
     std::signal(SIGINT, on_signal);
     std::signal(SIGTERM, on_signal);
+    std::signal(SIGUSR1, on_usr1);  // prints the counters line
     std::cout << "deepx-op-b200 listening on udp " << port << ", device " << device << ", " << ex->factory().size() << " ops" << std::endl;
 
     std::vector<char> buf(65536);
@@ -64,6 +76,10 @@ int main() {
         sockaddr_in cli{};
         socklen_t len = sizeof(cli);
         const ssize_t n = recvfrom(fd, buf.data(), buf.size() - 1, 0, reinterpret_cast<sockaddr *>(&cli), &len);
+        if (g_report) {
+            g_report = 0;
+            report(*ex);
+        }
         if (n <= 0) continue;
         buf[size_t(n)] = 0;
         // one reply datagram per IR line, in order; a datagram of several lines is a program
@@ -73,9 +89,7 @@ int main() {
             sendto(fd, reply.data(), reply.size(), 0, reinterpret_cast<sockaddr *>(&cli), len);
         }
     }
-    size_t st[4];
-    dx_pool_stats(ex->mem().pool(), st);
-    std::cout << "deepx-op-b200: " << ex->ops_run() << " ops run, pool high-water " << st[2] << " bytes, " << st[3] << " driver allocations" << std::endl;
+    report(*ex);
     close(fd);
     return 0;
 }
