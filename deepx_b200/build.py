@@ -76,7 +76,7 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> dict[str, Path]:
         hfut = [ex.submit(_compile, s, ["-x", "cu"] + extra, hdr, verbose) for s in hsrcs]
         kobjs = [f.result() for f in kfut]
         hobjs = [f.result() for f in hfut]
-    _link(kobjs, KERNEL_LIB, True, ["-lcuda"] if False else [], verbose)
+    _link(kobjs, KERNEL_LIB, True, [], verbose)
     out = {"kernels": KERNEL_LIB}
     if hobjs:
         lib_objs = [o for o in hobjs if not o.name.endswith("_main.o")]

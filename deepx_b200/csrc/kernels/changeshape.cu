@@ -204,6 +204,59 @@ __global__ void __launch_bounds__(CB) tile_transpose_pairs16_kernel(const char *
     }
 }
 
+// 1-byte elements, both moving extents multiples of 4: global accesses are 4-byte words (four
+// elements).  Patch = 128 (A) × 128 (B) bytes, held as 128 rows of 32 words; the word column is
+// rotated by the row's quad index so that both the row-wise writes (a warp writes one row) and the
+// column-wise reads (lane q reads rows 4q..4q+3 of one word column) are bank-conflict free.  A
+// thread turns four such words into four output words with a 4 × 4 byte transpose in registers.
+__global__ void __launch_bounds__(CB) tile_transpose_quads8_kernel(const char *__restrict__ in, char *__restrict__ out, TileParams p) {
+    constexpr int T = 128, NW = T / 4;
+    __shared__ uint32_t tile[T][NW];
+    uint32_t b = blockIdx.x;
+    uint32_t q = fd_div(b, p.tiles_b);
+    const uint32_t tb = b - q * p.tiles_b.d;
+    const uint32_t bt = fd_div(q, p.tiles_a);
+    const uint32_t ta = q - bt * p.tiles_a.d;
+    const char *src = in + unravel_bytes(bt, p.batch);
+    char *dst = out + unravel_bytes(bt, p.batch_out);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    {   // load: a warp reads one 128-byte row of the source per pass; 8 warps, 16 passes
+        const uint32_t ib = tb * T + 4 * lane;
+        uint32_t v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t ia = ta * T + warp + 8 * i;
+            v[i] = (ia < p.na && ib < p.nb) ? __ldcs(reinterpret_cast<const uint32_t *>(src + int64_t(ia) * p.a_src_stride + ib)) : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int row = warp + 8 * i;
+            tile[row][(lane + (row >> 2)) & (NW - 1)] = v[i];
+        }
+    }
+    __syncthreads();
+    {   // store: lane = quad of A (output bytes 4*lane..4*lane+3), a warp covers a 128-byte output row
+        const uint32_t ia = ta * T + 4 * lane;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int wb = warp + 8 * i;  // word column = four consecutive B
+            const int col = (wb + lane) & (NW - 1);
+            const uint32_t r0 = tile[4 * lane + 0][col], r1 = tile[4 * lane + 1][col];
+            const uint32_t r2 = tile[4 * lane + 2][col], r3 = tile[4 * lane + 3][col];
+            // byte j of row k → byte k of output word j
+            const uint32_t lo01 = __byte_perm(r0, r1, 0x5140), hi01 = __byte_perm(r0, r1, 0x7362);
+            const uint32_t lo23 = __byte_perm(r2, r3, 0x5140), hi23 = __byte_perm(r2, r3, 0x7362);
+            const uint32_t o[4] = {__byte_perm(lo01, lo23, 0x5410), __byte_perm(lo01, lo23, 0x7632),
+                                   __byte_perm(hi01, hi23, 0x5410), __byte_perm(hi01, hi23, 0x7632)};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t ib = tb * T + 4 * wb + j;
+                if (ia < p.na && ib < p.nb) __stcs(reinterpret_cast<uint32_t *>(dst + int64_t(ib) * p.b_dst_stride + ia), o[j]);
+            }
+        }
+    }
+}
+
 // ---- concat -----------------------------------------------------------------------------------
 constexpr int CONCAT_MAX = 16;
 struct ConcatParams {
@@ -442,7 +495,11 @@ extern "C" int dx_transpose(int dtype, const void *a, const int64_t *shape, int 
     }
     // 2-byte elements with even moving extents and 4-byte aligned bases: the paired-word kernel
     const bool pairs16 = es == 2 && (p.na % 2 == 0) && (p.nb % 2 == 0) && aligned_to(a, 4) && aligned_to(out, 4);
-    const int tile_a = 64, tile_b = pairs16 ? 128 : 64;
+    // 1-byte elements, moving extents and every stride a multiple of 4: the quad-word kernel
+    bool quads8 = es == 1 && (p.na % 4 == 0) && (p.nb % 4 == 0) && aligned_to(a, 4) && aligned_to(out, 4) &&
+                  (p.a_src_stride % 4 == 0) && (p.b_dst_stride % 4 == 0);
+    for (int i = 0; i < p.batch.n; ++i) quads8 = quads8 && (p.batch.stride[i] % 4 == 0) && (p.batch_out.stride[i] % 4 == 0);
+    const int tile_a = quads8 ? 128 : 64, tile_b = (pairs16 || quads8) ? 128 : 64;
     const int64_t ta = (p.na + tile_a - 1) / tile_a, tb = (p.nb + tile_b - 1) / tile_b;
     p.tiles_a = make_fastdiv((uint32_t)ta);
     p.tiles_b = make_fastdiv((uint32_t)tb);
@@ -451,6 +508,10 @@ extern "C" int dx_transpose(int dtype, const void *a, const int64_t *shape, int 
     if (pairs16) {
         tile_transpose_pairs16_kernel<<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p);
         return check_launch("transpose(tiles/pairs)");
+    }
+    if (quads8) {
+        tile_transpose_quads8_kernel<<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p);
+        return check_launch("transpose(tiles/quads)");
     }
     switch (es) {
         case 8: tile_transpose_kernel<uint64_t, 64><<<(unsigned)ctas, CB, 0, st>>>((const char *)a, (char *)out, p); break;

@@ -44,7 +44,13 @@ template <typename T> using compute_t = typename compute<T>::type;
 
 template <typename T> __host__ __device__ __forceinline__ compute_t<T> to_compute(T v) { return v; }
 template <> __host__ __device__ __forceinline__ float to_compute<f16>(f16 v) { return __half2float(v); }
-template <> __host__ __device__ __forceinline__ float to_compute<bf16>(bf16 v) { return __bfloat162float(v); }
+template <> __host__ __device__ __forceinline__ float to_compute<bf16>(bf16 v) {
+#ifdef __CUDA_ARCH__
+    return __uint_as_float(static_cast<unsigned int>(__bfloat16_as_ushort(v)) << 16);  // a bf16 is the float's upper half
+#else
+    return __bfloat162float(v);
+#endif
+}
 
 template <typename T> __host__ __device__ __forceinline__ T from_compute(compute_t<T> v) { return v; }
 template <> __host__ __device__ __forceinline__ f16 from_compute<f16>(float v) { return __float2half_rn(v); }

@@ -50,9 +50,20 @@ static int scalar_fp(int dtype, const void *a, double fs, int64_t is, void *c, i
     return DX_OK;
 }
 
+template <int K> static int pow_small(int dtype, const void *a, void *c, int64_t n, cudaStream_t st) {
+    if (dtype == DX_F64) return launch_ew1((const double *)a, (double *)c, n, PowSmallFn<K, double>(), st, "ew_scalar");
+    return launch_ew1((const float *)a, (float *)c, n, PowSmallFn<K, float>(), st, "ew_scalar");
+}
+
 extern "C" int dx_ew_scalar(int op, int dtype, const void *a, double fs, int64_t is, void *c, int64_t n,
                             void *stream) {
     cudaStream_t st = as_stream(stream);
+    if (op == DX_POWS && (dtype == DX_F32 || dtype == DX_F64)) {
+        if (fs == 2.0) return pow_small<2>(dtype, a, c, n, st);
+        if (fs == 1.0) return pow_small<1>(dtype, a, c, n, st);
+        if (fs == 3.0) return pow_small<3>(dtype, a, c, n, st);
+        if (fs == -1.0) return pow_small<-1>(dtype, a, c, n, st);
+    }
     switch (op) {
         case DX_ADDS: return scalar_all<DX_ADDS>(dtype, a, fs, is, c, n, st);
         case DX_SUBS: return scalar_all<DX_SUBS>(dtype, a, fs, is, c, n, st);

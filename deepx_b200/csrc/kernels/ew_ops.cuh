@@ -27,7 +27,12 @@ template <int OP, typename T> struct BinaryFn {
                 r = static_cast<T>(static_cast<U>(static_cast<U>(x) * static_cast<U>(y)));
             } else r = x * y;  // :226
         } else if constexpr (OP == DX_DIV) {
-            r = x / y;  // :267 (integer: truncating; divisor 0 is undefined in the reference)
+            if constexpr (std::is_integral<T>::value && sizeof(T) <= 2) {
+                // 8- and 16-bit integers: the fp32 quotient, correctly rounded, truncates to the exact
+                // integer quotient (|a/b| <= 2^15, a non-integer quotient is at least 1/|b| away from the
+                // next integer, the rounding error is below 2^-9/|b|), and skips the emulated integer divide.
+                r = static_cast<C>(__float2int_rz(__fdiv_rn(static_cast<float>(x), static_cast<float>(y))));
+            } else r = x / y;  // :267 (integer: truncating; divisor 0 is undefined in the reference)
         } else if constexpr (OP == DX_MAX) {
             r = (x < y) ? y : x;  // std::max, :614
         } else if constexpr (OP == DX_MIN) {
@@ -57,6 +62,21 @@ template <int OP, typename T> struct ScalarFn {
         else {
             static_assert(OP == DX_RPOWS, "scalar op");
             return BinaryFn<DX_POW, T>()(s, a);  // :482
+        }
+    }
+};
+
+// pow(a, k) for the exponents models use all the time (x.pow(2) in every norm layer): plain
+// multiplications stream at memory speed where powf's ~40 instructions per element do not, and
+// x*x is the correctly rounded square.  K = 1, 2, 3 or -1 (reciprocal, IEEE division).
+template <int K, typename T> struct PowSmallFn {
+    __device__ __forceinline__ T operator()(T a) const {
+        if constexpr (K == 1) return a;
+        else if constexpr (K == 2) return a * a;
+        else if constexpr (K == 3) return a * a * a;
+        else {
+            static_assert(K == -1, "exponent");
+            return T(1) / a;
         }
     }
 };

@@ -78,7 +78,10 @@ template <typename E> struct SwitchTable {
     const E *t[DX_SWITCH_MAX];
 };
 
-template <int VEC, typename E, typename CT>
+// NT > 0: exactly NT sources, all read as vectors up front (every load of a thread is in flight
+// before the first select); NT == 0: any number of sources, each element fetched from the source
+// its case names.  Both read each source sector once when the cases are mixed.
+template <int VEC, typename E, typename CT, int NT>
 __global__ void __launch_bounds__(EW_BLOCK)
     switch_kernel(SwitchTable<E> tab, int ntensors, const CT *cases, E *c, int64_t n) {
     constexpr int64_t TILE = int64_t(EW_BLOCK) * EW_UNROLL * VEC;
@@ -89,22 +92,41 @@ __global__ void __launch_bounds__(EW_BLOCK)
         return (w >= 0 && w < ntensors) ? tab.t[w][i] : E(0);
     };
     if (base + TILE <= n) {
+        if constexpr (NT > 0) {
+            Pack<CT, VEC> k[EW_UNROLL];
+            Pack<E, VEC> x[EW_UNROLL][NT];
 #pragma unroll
-        for (int u = 0; u < EW_UNROLL; ++u) {
-            const int64_t i0 = base + (int64_t(u) * EW_BLOCK + threadIdx.x) * VEC;
-            Pack<CT, VEC> k = ld_stream<CT, VEC>(cases + i0);
-            Pack<E, VEC> r;
-            if constexpr (sizeof(CT) == 1) {
-                // bool cases: read both sources as vectors, select per lane.
-                Pack<E, VEC> x0 = ld_stream<E, VEC>(tab.t[0] + i0);
-                Pack<E, VEC> x1 = ld_stream<E, VEC>(tab.t[1] + i0);
+            for (int u = 0; u < EW_UNROLL; ++u) {
+                const int64_t i0 = base + (int64_t(u) * EW_BLOCK + threadIdx.x) * VEC;
+                k[u] = ld_stream<CT, VEC>(cases + i0);
 #pragma unroll
-                for (int j = 0; j < VEC; ++j) r.v[j] = k.v[j] ? x1.v[j] : x0.v[j];
-            } else {
+                for (int t = 0; t < NT; ++t) x[u][t] = ld_stream<E, VEC>(tab.t[t] + i0);
+            }
+#pragma unroll
+            for (int u = 0; u < EW_UNROLL; ++u) {
+                const int64_t i0 = base + (int64_t(u) * EW_BLOCK + threadIdx.x) * VEC;
+                Pack<E, VEC> r;
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    int w = static_cast<int>(k[u].v[j]);
+                    if constexpr (sizeof(CT) == 1) w = (k[u].v[j] != 0);
+                    E v = E(0);  // a case outside [0, NT) selects nothing
+#pragma unroll
+                    for (int t = 0; t < NT; ++t) v = (w == t) ? x[u][t].v[j] : v;
+                    r.v[j] = v;
+                }
+                st_stream<E, VEC>(c + i0, r);
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < EW_UNROLL; ++u) {
+                const int64_t i0 = base + (int64_t(u) * EW_BLOCK + threadIdx.x) * VEC;
+                Pack<CT, VEC> k = ld_stream<CT, VEC>(cases + i0);
+                Pack<E, VEC> r;
 #pragma unroll
                 for (int j = 0; j < VEC; ++j) r.v[j] = pick(i0 + j, k.v[j]);
+                st_stream<E, VEC>(c + i0, r);
             }
-            st_stream<E, VEC>(c + i0, r);
         }
     } else {
         for (int64_t i = base + threadIdx.x; i < n; i += EW_BLOCK) c[i] = pick(i, cases[i]);
@@ -128,10 +150,16 @@ static int launch_switch(const void *const *tensors, int ntensors, const void *c
     int64_t grid;
     if (al) {
         if (int e = ew_grid(n, VEC, &grid)) return e;
-        switch_kernel<VEC, E, CT><<<(unsigned)grid, EW_BLOCK, 0, st>>>(tab, ntensors, (const CT *)cases, (E *)c, n);
+        const unsigned g = (unsigned)grid;
+        switch (ntensors) {
+            case 1: switch_kernel<VEC, E, CT, 1><<<g, EW_BLOCK, 0, st>>>(tab, ntensors, (const CT *)cases, (E *)c, n); break;
+            case 2: switch_kernel<VEC, E, CT, 2><<<g, EW_BLOCK, 0, st>>>(tab, ntensors, (const CT *)cases, (E *)c, n); break;
+            case 3: switch_kernel<VEC, E, CT, 3><<<g, EW_BLOCK, 0, st>>>(tab, ntensors, (const CT *)cases, (E *)c, n); break;
+            default: switch_kernel<VEC, E, CT, 0><<<g, EW_BLOCK, 0, st>>>(tab, ntensors, (const CT *)cases, (E *)c, n); break;
+        }
     } else {
         if (int e = ew_grid(n, 1, &grid)) return e;
-        switch_kernel<1, E, CT><<<(unsigned)grid, EW_BLOCK, 0, st>>>(tab, ntensors, (const CT *)cases, (E *)c, n);
+        switch_kernel<1, E, CT, 0><<<(unsigned)grid, EW_BLOCK, 0, st>>>(tab, ntensors, (const CT *)cases, (E *)c, n);
     }
     return check_launch("switch");
 }

@@ -307,13 +307,53 @@ struct Plan {
     unsigned grid;
 };
 
+// CTAs of the split kernels that fit on one SM, per (op, element type): the register count differs
+// (32 for float32 rows, 47 for 16-bit columns, 61 for 8-bit columns), and a grid sized for more
+// CTAs than fit leaves a few stragglers that run alone after the first wave.
+struct Residency {
+    int rows_block, cols;
+};
+template <int OP, typename T> Residency residency_t() {
+    static Residency r{0, 0};
+    static std::once_flag once;
+    std::call_once(once, [] {
+        constexpr int FULL = 16 / sizeof(T);
+        int n = 0;
+        r.rows_block = (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rows_block_kernel<OP, T, FULL>, RB, 0) == cudaSuccess && n > 0) ? n : 8;
+        r.cols = (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, cols_kernel<OP, T, FULL>, RB, 0) == cudaSuccess && n > 0) ? n : 6;
+        cudaGetLastError();  // no device (a host-only build check): the defaults stand
+    });
+    return r;
+}
+template <typename T> Residency residency_op(int op) {
+    switch (op) {
+        case DX_SUM: return residency_t<DX_SUM, T>();
+        case DX_PROD: return residency_t<DX_PROD, T>();
+        case DX_RMAX: return residency_t<DX_RMAX, T>();
+        default: return residency_t<DX_RMIN, T>();
+    }
+}
+Residency residency(int op, int dtype) {
+    switch (dtype) {
+        case DX_F64: return residency_op<double>(op);
+        case DX_F32: return residency_op<float>(op);
+        case DX_F16: return residency_op<f16>(op);
+        case DX_BF16: return residency_op<bf16>(op);
+        case DX_I64: return residency_op<int64_t>(op);
+        case DX_I32: return residency_op<int32_t>(op);
+        case DX_I16: return residency_op<int16_t>(op);
+        case DX_I8: return residency_op<int8_t>(op);
+        default: return Residency{8, 6};
+    }
+}
+
 int pow2_ceil(int v) {
     int p = 1;
     while (p < v) p <<= 1;
     return p;
 }
 
-int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, int ndims, int sms, Plan *pl) {
+int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, int ndims, int sms, Residency res, Plan *pl) {
     if (ndim < 0 || ndim > DX_MAX_DIMS) return fail(DX_E_SHAPE, "reduce: rank %d outside [0, %d]", ndim, DX_MAX_DIMS);
     if ((ndim > 0 && !shape) || (ndims > 0 && !dims)) return fail(DX_E_ARG, "reduce: null shape or dims");
     bool red[DX_MAX_DIMS] = {false};
@@ -365,8 +405,8 @@ int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, in
     int vec = 16 / es;  // full 16-byte vectors when the contiguous run allows it, else scalar
     if (inner % vec != 0) vec = 1;
     pl->vec = vec;
-    // resident CTAs per SM: the rows kernels fit 8 (32 registers), the cols kernel 6 (39 registers)
-    const int target_ctas = sms * (g.back().red ? 8 : 6);
+    // one wave: as many CTAs as can be resident at once for this kernel and element type
+    const int target_ctas = sms * (g.back().red ? res.rows_block : res.cols);
 
     if (g.back().red) {
         RowsParams &p = pl->rows;
@@ -537,10 +577,9 @@ using namespace dx;
 
 extern "C" size_t dx_reduce_workspace_bytes(int op, int dtype, const int64_t *shape, int ndim, const int32_t *dims,
                                             int ndims) {
-    (void)op;
     Plan pl;
     if (dx_dtype_size(dtype) == 0 || dtype == DX_BOOL) return 0;
-    if (make_plan(dtype, shape, ndim, dims, ndims, sm_count(), &pl) != DX_OK) return 0;
+    if (make_plan(dtype, shape, ndim, dims, ndims, sm_count(), residency(op, dtype), &pl) != DX_OK) return 0;
     return (pl.workspace + 255) / 256 * 256;
 }
 
@@ -550,7 +589,7 @@ extern "C" int dx_reduce(int op, int dtype, const void *a, const int64_t *shape,
     if (dx_dtype_size(dtype) == 0 || dtype == DX_BOOL)
         return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
     Plan pl;
-    if (int e = make_plan(dtype, shape, ndim, dims, ndims, sm_count(), &pl)) return e;
+    if (int e = make_plan(dtype, shape, ndim, dims, ndims, sm_count(), residency(op, dtype), &pl)) return e;
     if (pl.nout > 0 && !out) return fail(DX_E_ARG, "reduce: null output");
     if (pl.nin > 0 && !a) return fail(DX_E_ARG, "reduce: null input");
     if (a == out && pl.nin > 0 && pl.kind != PLAN_COPY) return fail(DX_E_ALIAS, "reduce: output aliases input");
@@ -593,7 +632,7 @@ extern "C" int dx_reduce_noalloc(int op, int dtype, const void *a, const int64_t
     if (dx_dtype_size(dtype) == 0 || dtype == DX_BOOL)
         return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
     Plan pl;
-    if (int e = make_plan(dtype, shape, ndim, dims, ndims, sm_count(), &pl)) return e;
+    if (int e = make_plan(dtype, shape, ndim, dims, ndims, sm_count(), residency(op, dtype), &pl)) return e;
     if (pl.workspace > DX_REDUCE_STATIC_SCRATCH)
         return fail(DX_E_WORKSPACE,
                     "reduce (no-alloc): this shape needs %zu bytes of scratch, the built-in scratch holds %zu; "

@@ -62,6 +62,24 @@ def test_transpose_swap_last_two_large(mods):
             _transpose(TF, O, make(rng, dt, shape), perm, f"transpose<{dt}> {shape} {perm}")
 
 
+def test_transpose_one_byte_quad_kernel(mods):
+    """1-byte elements with moving extents that are multiples of 4 take the quad-word tile kernel:
+    whole and ragged 128 x 128 patches, batch axes, and shapes that must fall back to the byte kernel."""
+    TF, O = mods
+    rng = np.random.default_rng(22)
+    for shape, perm in [((128, 128), [1, 0]), ((256, 384), [1, 0]), ((132, 260), [1, 0]), ((4, 8), [1, 0]), ((3, 1000, 776), [0, 2, 1]),
+                        ((2, 68, 4, 132), [3, 2, 1, 0]), ((8, 64, 128), [2, 0, 1]), ((5, 12, 100), [2, 1, 0]),
+                        ((130, 258), [1, 0]), ((7, 64, 66), [0, 2, 1])]:
+        for dt in ("int8", "bool"):
+            _transpose(TF, O, make(rng, dt, shape), perm, f"transpose<{dt}> {shape} {perm}")
+    # an unaligned base pointer must not take the word kernel
+    a = make(rng, "int8", (129, 128))
+    A = to_gpu(a.reshape(-1))[128:].view(128, 128)
+    out = torch.empty((128, 128), dtype=torch.int8, device="cuda:0")
+    TF.transpose(A.contiguous() if False else A, [1, 0], out)
+    assert_bit_exact(to_np(out), O.transpose(a[1:], [1, 0]), "transpose<int8> from an offset view")
+
+
 def test_transpose_errors(mods):
     TF, _ = mods
     a = torch.zeros(2, 3, device="cuda:0")

@@ -92,6 +92,56 @@ def test_pow(mods, dtype):
         TF.pow(X, X, torch.empty_like(X))
 
 
+@pytest.mark.parametrize("dtype", ["float64", "float32"])
+@pytest.mark.parametrize("k", [2, 3, 1, -1])
+def test_powscalar_small_integer_exponents(mods, dtype, k):
+    """powscalar(x, 2|3|1|-1) runs as multiplications / one division (what x.pow(2) of a norm layer sends);
+    against the CPU pow: negative, zero and huge bases included."""
+    TF, O = mods
+    rng = np.random.default_rng(70 + k)
+    a = make(rng, dtype, (50001,), -30.0, 30.0)
+    a[:6] = [0.0, -0.0, 1.0, -1.0, 1e18, -1e-18]
+    A = to_gpu(a)
+    Cc = torch.empty_like(A)
+    TF.powscalar(A, k, Cc)
+    got, want = to_np(Cc), O.powscalar(a, k)
+    assert np.array_equal(np.isinf(got), np.isinf(want)) and np.array_equal(np.signbit(got), np.signbit(want))
+    fin = np.isfinite(want)
+    tol = 1e-12 if dtype == "float64" else 1e-5
+    assert np.allclose(got[fin], want[fin], rtol=tol, atol=0.0)
+    if k in (1, 2):  # x and x*x are correctly rounded: at least as close to the exact power as the CPU pow
+        exact = a.astype(np.longdouble) ** k
+        assert (np.abs(got[fin] - exact[fin]) <= np.abs(want[fin] - exact[fin])).all()
+
+
+def test_small_integer_division_is_exact(mods):
+    """int8 / int16 division goes through fp32: every int8 pair, and int16 numerators against small, large
+    and extreme divisors, must give the truncated integer quotient bit for bit."""
+    TF, O = mods
+    a8, b8 = np.meshgrid(np.arange(-128, 128, dtype=np.int8), np.array([b for b in range(-128, 128) if b != 0], dtype=np.int8))
+    a8, b8 = a8.ravel().copy(), b8.ravel().copy()
+    out = torch.empty(a8.shape, dtype=torch.int8, device="cuda:0")
+    TF.div(to_gpu(a8), to_gpu(b8), out)
+    assert_bit_exact(to_np(out), O.div(a8, b8), "div<int8> all pairs")
+    rng = np.random.default_rng(11)
+    num = np.arange(-32768, 32768, dtype=np.int16)
+    divisors = list(range(-300, 301)) + [-32768, -32767, 32767, 16384, -16385, 255, 257, 4097, 10923, 21845] + list(rng.integers(-32768, 32768, 200))
+    for d in divisors:
+        if d == 0:
+            continue
+        b = np.full(num.shape, d, dtype=np.int16)
+        o16 = torch.empty(num.shape, dtype=torch.int16, device="cuda:0")
+        TF.div(to_gpu(num), to_gpu(b), o16)
+        assert_bit_exact(to_np(o16), O.div(num, b), f"div<int16> by {d}")
+    o16 = torch.empty(num.shape, dtype=torch.int16, device="cuda:0")
+    TF.divscalar(to_gpu(num), 7, o16)
+    assert_bit_exact(to_np(o16), O.divscalar(num, 7), "divscalar<int16>")
+    nz = num[num != 0]
+    o16 = torch.empty(nz.shape, dtype=torch.int16, device="cuda:0")
+    TF.rdivscalar(30000, to_gpu(nz), o16)
+    assert_bit_exact(to_np(o16), O.rdivscalar(30000, nz), "rdivscalar<int16>")
+
+
 @pytest.mark.parametrize("dtype", ALL_NUMERIC)
 @pytest.mark.parametrize("op", ["addscalar", "subscalar", "rsubscalar", "mulscalar", "divscalar", "rdivscalar",
                                 "maxscalar", "minscalar"])
