@@ -703,6 +703,79 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def run_sweep(args) -> None:
+    """`--sweep`: every elementwise / compare / switch / cast / reduce / transpose op in every dtype on
+    256 MiB tensors (CUDA-graph replay, rotating buffers), as a fraction of the measured HBM peak.
+    Prints one JSON object: {"ops": {name: frac}, "below_0.8": {...}}."""
+    import torch
+    from deepx_b200 import tensorfunc as TF
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    peak, peak_kind = measured_peaks()
+    R, BYTES = 3, 256 << 20
+    DT = {"f64": torch.float64, "f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16, "i64": torch.int64,
+          "i32": torch.int32, "i16": torch.int16, "i8": torch.int8}
+    res: dict[str, float] = {}
+
+    def run(name, fns, nbytes):
+        res[name] = time_case(torch, fns, nbytes, None, peak, iters=9)["frac_hbm"]
+
+    for dn, dt in DT.items():
+        es = torch.empty(0, dtype=dt).element_size()
+        n = BYTES // es
+
+        def mk():
+            if dt.is_floating_point:
+                return (torch.rand(n, device=dev) * 1.5 + 0.5).to(dt)
+            return torch.randint(1, 100, (n,), device=dev).to(dt)
+        a, b = [mk() for _ in range(R)], [mk() for _ in range(R)]
+        c = [torch.empty_like(a[0]) for _ in range(R)]
+        m = [torch.empty(n, dtype=torch.bool, device=dev) for _ in range(R)]
+        for op in ("add", "sub", "mul", "div", "max", "min"):
+            run(f"{op}<{dn}>", [lambda i=i, op=op: getattr(TF, op)(a[i], b[i], c[i]) for i in range(R)], 3 * n * es)
+        for op in ("addscalar", "subscalar", "rsubscalar", "mulscalar", "divscalar", "rdivscalar", "maxscalar", "minscalar"):
+            run(f"{op}<{dn}>", [lambda i=i, op=op: (getattr(TF, op)(2, a[i], c[i]) if op.startswith("r") else getattr(TF, op)(a[i], 2, c[i]))
+                               for i in range(R)], 2 * n * es)
+        for op in ("less", "greater", "equal", "notequal"):
+            if op in ("equal", "notequal"):
+                run(f"{op}<{dn}>", [lambda i=i, op=op: getattr(TF, op)(a[i], b[i], 0.0, m[i]) for i in range(R)], n * (2 * es + 1))
+            else:
+                run(f"{op}<{dn}>", [lambda i=i, op=op: getattr(TF, op)(a[i], b[i], m[i]) for i in range(R)], n * (2 * es + 1))
+        if dt.is_floating_point:
+            for op in ["sqrt", "exp", "log", "sin", "cos"] + (["tan"] if dn in ("f64", "f32") else []):
+                run(f"{op}<{dn}>", [lambda i=i, op=op: getattr(TF, op)(a[i], c[i]) for i in range(R)], 2 * n * es)
+            if dn in ("f64", "f32"):
+                run(f"pow<{dn}>", [lambda i=i: TF.pow(a[i], b[i], c[i]) for i in range(R)], 3 * n * es)
+                run(f"powscalar(2)<{dn}>", [lambda i=i: TF.powscalar(a[i], 2, c[i]) for i in range(R)], 2 * n * es)
+                run(f"powscalar(2.5)<{dn}>", [lambda i=i: TF.powscalar(a[i], 2.5, c[i]) for i in range(R)], 2 * n * es)
+        else:
+            run(f"invert<{dn}>", [lambda i=i: TF.invert(a[i], c[i]) for i in range(R)], 2 * n * es)
+        cases = [torch.randint(0, 2, (n,), device=dev, dtype=torch.int32) for _ in range(R)]
+        run(f"switch(2 sources, int32 cases)<{dn}>", [lambda i=i: TF.Switch([a[i], b[i]], cases[i], c[i]) for i in range(R)], n * (3 * es + 4))
+        del cases
+        run(f"switch(2 sources, bool cases)<{dn}>", [lambda i=i: TF.Switch([a[i], b[i]], m[i], c[i]) for i in range(R)], n * (3 * es + 1))
+        for dn2 in ("f32", "bf16", "i32", "i8"):
+            if dn2 != dn:
+                o = [torch.empty(n, dtype=DT[dn2], device=dev) for _ in range(R)]
+                run(f"todtype<{dn}->{dn2}>", [lambda i=i, o=o: TF.todtype(a[i], o[i]) for i in range(R)], n * (es + o[0].element_size()))
+                del o
+        x = [t.view(4096, n // 4096) for t in a]
+        for op in ("sum", "prod", "reducemax", "reducemin"):
+            for dims, oshape in (([1], (4096,)), ([0], (n // 4096,)), ([0, 1], (1,))):
+                o = torch.empty(oshape, dtype=dt, device=dev)
+                run(f"{op}<{dn}> [4096,{n // 4096}] dims{dims}", [lambda i=i, op=op, dims=dims, o=o: getattr(TF, op)(x[i], dims, False, o) for i in range(R)], n * es)
+        t3 = [t.view(64, 512, n // 32768) for t in a]
+        for perm in ([0, 2, 1], [1, 0, 2], [2, 0, 1]):
+            o = [torch.empty([t3[0].shape[q] for q in perm], dtype=dt, device=dev) for _ in range(R)]
+            run(f"transpose<{dn}> [64,512,{n // 32768}] {perm}", [lambda i=i, perm=perm, o=o: TF.transpose(t3[i], perm, o[i]) for i in range(R)], 2 * n * es)
+            del o
+        del a, b, c, m, x, t3
+        torch.cuda.empty_cache()
+    low = {k: v for k, v in res.items() if v < 0.8}
+    print(json.dumps({"sweep": "256 MiB per tensor, cuda-graph replay", "peak_gbs": peak, "peak_source": peak_kind, "count": len(res),
+                      "min": min(res.values()), "below_0.8": low, "ops": res}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -712,8 +785,11 @@ def main() -> None:
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op table of the other configs")
     ap.add_argument("--no-graph", action="store_true", help="with --op: launch directly instead of replaying a CUDA graph")
     ap.add_argument("--op", default=None, help="time one named op of the per-op table alone (single GPU)")
+    ap.add_argument("--sweep", action="store_true", help="every op x dtype on 256 MiB tensors as a fraction of the HBM peak (single GPU)")
     args = ap.parse_args()
-    if args.op:
+    if args.sweep:
+        run_sweep(args)
+    elif args.op:
         run_one_op(args)
     elif args.impl == "reference":
         run_reference(args)

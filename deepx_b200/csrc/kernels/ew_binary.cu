@@ -64,6 +64,15 @@ extern "C" int dx_ew_scalar(int op, int dtype, const void *a, double fs, int64_t
         if (fs == 3.0) return pow_small<3>(dtype, a, c, n, st);
         if (fs == -1.0) return pow_small<-1>(dtype, a, c, n, st);
     }
+    if (op == DX_DIVS && (dtype == DX_I8 || dtype == DX_I16)) {
+        const int64_t d = dtype == DX_I8 ? int64_t(int8_t(is)) : int64_t(int16_t(is));  // the scalar as the element type holds it
+        const uint64_t mag = uint64_t(d < 0 ? -d : d);
+        if (mag >= 2) {
+            const uint32_t magic = uint32_t((uint64_t(1) << 32) / mag + 1);
+            if (dtype == DX_I8) return launch_ew1((const int8_t *)a, (int8_t *)c, n, DivConstFn<int8_t>{magic, d < 0}, st, "ew_scalar");
+            return launch_ew1((const int16_t *)a, (int16_t *)c, n, DivConstFn<int16_t>{magic, d < 0}, st, "ew_scalar");
+        }
+    }
     switch (op) {
         case DX_ADDS: return scalar_all<DX_ADDS>(dtype, a, fs, is, c, n, st);
         case DX_SUBS: return scalar_all<DX_SUBS>(dtype, a, fs, is, c, n, st);

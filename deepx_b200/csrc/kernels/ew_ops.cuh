@@ -81,6 +81,20 @@ template <int K, typename T> struct PowSmallFn {
     }
 };
 
+// int8 / int16 divided by a constant d, |d| >= 2: |a| * (floor(2^32/|d|) + 1) >> 32 is the exact
+// truncated quotient for |a| < 2^16 (the error term is below 2^-16 <= 1/|d|), one multiply-high
+// instead of a division per element.
+template <typename T> struct DivConstFn {
+    uint32_t magic;
+    int negative;  // divisor < 0
+    __device__ __forceinline__ T operator()(T a) const {
+        const int x = a;
+        const uint32_t q = __umulhi(static_cast<uint32_t>(x < 0 ? -x : x), magic);
+        const int r = ((x < 0) != (negative != 0)) ? -static_cast<int>(q) : static_cast<int>(q);
+        return static_cast<T>(r);
+    }
+};
+
 // ---- unary ---------------------------------------------------------------------
 template <int OP, typename T> struct UnaryFn {
     __device__ __forceinline__ T operator()(T a) const {

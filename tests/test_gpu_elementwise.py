@@ -133,9 +133,15 @@ def test_small_integer_division_is_exact(mods):
         o16 = torch.empty(num.shape, dtype=torch.int16, device="cuda:0")
         TF.div(to_gpu(num), to_gpu(b), o16)
         assert_bit_exact(to_np(o16), O.div(num, b), f"div<int16> by {d}")
-    o16 = torch.empty(num.shape, dtype=torch.int16, device="cuda:0")
-    TF.divscalar(to_gpu(num), 7, o16)
-    assert_bit_exact(to_np(o16), O.divscalar(num, 7), "divscalar<int16>")
+    for d in [7, -7, 2, -2, 3, 1, -1, 255, 10923, 32767, -32768, 30000]:
+        o16 = torch.empty(num.shape, dtype=torch.int16, device="cuda:0")
+        TF.divscalar(to_gpu(num), d, o16)
+        assert_bit_exact(to_np(o16), O.divscalar(num, d), f"divscalar<int16> by {d}")
+    n8 = np.arange(-128, 128, dtype=np.int8)
+    for d in [5, -5, 2, 3, 1, -1, 127, -128, 100]:
+        o8 = torch.empty(n8.shape, dtype=torch.int8, device="cuda:0")
+        TF.divscalar(to_gpu(n8), d, o8)
+        assert_bit_exact(to_np(o8), O.divscalar(n8, d), f"divscalar<int8> by {d}")
     nz = num[num != 0]
     o16 = torch.empty(nz.shape, dtype=torch.int16, device="cuda:0")
     TF.rdivscalar(30000, to_gpu(nz), o16)
