@@ -661,6 +661,20 @@ def run_ours(args) -> None:
     e2e_ms = timed_ex(e2e_step, e2e_steps) / e2e_steps
     if abs(float(hs_np[0]) - got_sum) > 1e-4 * abs(got_sum) + 1e-3 or not np.array_equal(hm_np[:ref_rows], got_m):
         raise SystemExit("bench: the executor path and the direct path disagree — refusing to report a number")
+    executor_us = None
+    if world == 1:
+        # what one IR line costs on the host side: parse, registry lookup, tensor lookup, one launch of a 16-element op
+        ex.run("newtensor(vector<int32>:[16])->(tensor<float32>:tiny)")
+        ex.run("constant(var<float32>:1)->(tensor<float32>:tiny)")
+        tiny_ir = "addscalar(tensor<float32>:tiny, var<float32>:1)->(tensor<float32>:tiny) // author=miaobyte id=7"
+        for _ in range(100):
+            ex.run(tiny_ir)
+        ex.sync()
+        t0 = time.perf_counter()
+        for _ in range(3000):
+            ex.run(tiny_ir)
+        ex.sync()
+        executor_us = (time.perf_counter() - t0) / 3000 * 1e6
     ex.close()
     e2e_value = total_bytes / e2e_ms / 1e6
 
@@ -680,6 +694,8 @@ def run_ours(args) -> None:
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": 2 * my_rows * COLS * 4 * world,
                 "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
                 "path": "deepxIR text -> libdeepx_exec.so (dx_exec_upload / dx_exec_run / dx_exec_download), pinned host buffers"},
+        "executor": {"us_per_ir_line": None if executor_us is None else round(executor_us, 2),
+                     "what": "3000 addscalar lines on a 16-element tensor through dx_exec_run from Python (parse + dispatch + launch)"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "global_sum": got_sum,

@@ -73,6 +73,25 @@ void dx_exec_fusion_stats(dx_exec *e, uint64_t stats[4]) {
     stats[0] = f.programs; stats[1] = f.rmsnorm_groups; stats[2] = f.softmax_groups; stats[3] = f.lines_absorbed;
 }
 
+int dx_exec_bind_tensor(dx_exec *e, const char *name, int dtype, const int64_t *shape, int ndim, void *device_ptr) {
+    if (!e || !name || !*name || (ndim > 0 && !shape) || ndim < 0 || ndim > DX_MAX_DIMS) { g_err = "bind: bad argument"; return -1; }
+    const uint16_t prec = precision_of_dx(dtype);
+    if (dx_code_of(prec) < 0) { g_err = "bind: unsupported dtype code"; return -1; }
+    if (e->ex.mem().exists_tensor(name)) { g_err = std::string("bind: tensor already exists: ") + name; return -1; }
+    auto t = std::make_shared<Tensor>();
+    std::vector<int64_t> shp(shape, shape + ndim);
+    for (auto d : shp)
+        if (d < 0) { g_err = "bind: negative extent"; return -1; }
+    t->shape.set(shp);
+    t->shape.dtype = prec;
+    t->data = device_ptr;
+    t->pool = nullptr;  // not ours: never freed here
+    t->device = e->ex.mem().device();
+    if (t->shape.size > 0 && !device_ptr) { g_err = "bind: null pointer"; return -1; }
+    e->ex.mem().add_tensor(name, t);
+    return 0;
+}
+
 int dx_exec_tensor_info(dx_exec *e, const char *name, int *dtype, int64_t *shape, int cap) {
     if (!e || !name || !e->ex.mem().exists_tensor(name)) return -1;
     auto t = e->ex.mem().get_tensor(name);

@@ -22,6 +22,7 @@ SIGNATURES = {
     "dx_exec_run_program": (_i, [_vp, _cp, C.c_char_p, _sz]),
     "dx_exec_set_fusion": (None, [_vp, _i]),
     "dx_exec_fusion_stats": (None, [_vp, C.POINTER(C.c_uint64)]),
+    "dx_exec_bind_tensor": (_i, [_vp, _cp, _i, C.POINTER(C.c_int64), _i, _vp]),
     "dx_exec_tensor_info": (_i, [_vp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int64), _i]),
     "dx_exec_tensor_ptr": (_vp, [_vp, _cp]),
     "dx_exec_upload": (_i, [_vp, _cp, _vp, _sz]),
@@ -171,6 +172,12 @@ class Executor:
 
     def new(self, name: str, dtype: str, shape) -> None:
         self.run(f"newtensor(vector<int32>:[{' '.join(str(int(s)) for s in shape)}])->(tensor<{dtype}>:{name})")
+
+    def bind(self, name: str, dtype_code: int, shape, device_ptr: int) -> None:
+        """Registers memory the executor does not own (e.g. a heap tensor) under `name`."""
+        shp = (C.c_int64 * max(len(shape), 1))(*[int(s) for s in shape])
+        if lib().dx_exec_bind_tensor(self._h, name.encode(), dtype_code, shp, len(shape), device_ptr) != 0:
+            raise RuntimeError(lib().dx_exec_last_error().decode())
 
     def upload(self, name: str, array: np.ndarray) -> None:
         a = np.ascontiguousarray(array)

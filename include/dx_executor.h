@@ -48,6 +48,12 @@ void dx_exec_set_fusion(dx_exec *e, int on);
 /* [0] programs seen, [1] RMSNorm chains rewritten, [2] softmax chains rewritten, [3] IR lines absorbed. */
 void dx_exec_fusion_stats(dx_exec *e, uint64_t stats[4]);
 
+/* Registers device memory the executor does not own (a heap tensor mapped with dx_heap_open, a
+ * buffer of the embedding application) as tensor `name`, so IR ops can read and write it.  The
+ * executor never frees it; deltensor only forgets the name.  The memory must stay valid, on the
+ * executor's device, while the name is registered.  Fails if the name exists. */
+int dx_exec_bind_tensor(dx_exec *e, const char *name, int dtype, const int64_t *shape, int ndim, void *device_ptr);
+
 /* Tensor metadata: dtype is a dx_dtype code; shape receives up to cap extents; returns the rank,
  * or -1 if there is no such tensor. */
 int dx_exec_tensor_info(dx_exec *e, const char *name, int *dtype, int64_t *shape, int cap);

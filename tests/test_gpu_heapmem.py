@@ -72,6 +72,32 @@ def test_kernels_run_on_heap_tensors():
     heap.close()
 
 
+def test_executor_runs_ir_on_a_bound_heap_tensor():
+    """A heap tensor registered in the executor under a name is an ordinary operand of IR ops; deleting
+    the name does not free the heap allocation."""
+    from deepx_b200 import heapmem as H
+    from deepx_b200.executor import Executor
+    heap = H.Heap()
+    heap.create("weights", "float32", [8, 16])
+    w = np.arange(128, dtype=np.float32).reshape(8, 16)
+    H.copy_to_device(heap.ptr("weights"), w)
+    ex = Executor(0)
+    ex.bind("w", 1, [8, 16], heap.ptr("weights"))
+    with pytest.raises(RuntimeError):
+        ex.bind("w", 1, [8, 16], heap.ptr("weights"))
+    ex.run("newtensor(vector<int32>:[8 16])->(tensor<float32>:y)")
+    ex.run("mulscalar(tensor<float32>:w, var<float32>:2)->(tensor<float32>:y)")
+    ex.run("addscalar(tensor<float32>:w, var<float32>:1)->(tensor<float32>:w)")   # in place, into the heap tensor
+    assert np.array_equal(ex.download("y"), w * 2)
+    ex.run("deltensor()->(tensor<float32>:w)")
+    ex.sync()
+    back = np.empty_like(w)
+    H.copy_to_host(back, heap.ptr("weights"))
+    assert np.array_equal(back, w + 1)
+    ex.close()
+    heap.close()
+
+
 def test_bad_handle_is_an_error_not_a_fault():
     from deepx_b200 import heapmem as H
     with pytest.raises(H.HeapError):
