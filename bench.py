@@ -593,6 +593,8 @@ def run_ours(args) -> None:
 
     # parity guard on the timed outputs: global sum and row max against float64 on this rank's rows
     torch.cuda.synchronize()
+    if ops.peer is not None:
+        ops.peer.status()  # raises if a wait on a peer expired: a number with a skipped combine is not reported
     z64 = None
     got_sum = float(s.item())
     ref_rows = min(my_rows, 8)
@@ -661,7 +663,7 @@ def run_ours(args) -> None:
     e2e_ms = timed_ex(e2e_step, e2e_steps) / e2e_steps
     if abs(float(hs_np[0]) - got_sum) > 1e-4 * abs(got_sum) + 1e-3 or not np.array_equal(hm_np[:ref_rows], got_m):
         raise SystemExit("bench: the executor path and the direct path disagree — refusing to report a number")
-    executor_us = None
+    executor_us = compiled_us = None
     if world == 1:
         # what one IR line costs on the host side: parse, registry lookup, tensor lookup, one launch of a 16-element op
         ex.run("newtensor(vector<int32>:[16])->(tensor<float32>:tiny)")
@@ -675,6 +677,17 @@ def run_ours(args) -> None:
             ex.run(tiny_ir)
         ex.sync()
         executor_us = (time.perf_counter() - t0) / 3000 * 1e6
+        # the same line 200 times as one compiled program (CUDA graph): one launch call per replay
+        prog = ex.compile("\n".join([tiny_ir] * 200))
+        for _ in range(3):
+            prog.run()
+        ex.sync()
+        t0 = time.perf_counter()
+        for _ in range(50):
+            prog.run()
+        ex.sync()
+        compiled_us = (time.perf_counter() - t0) / (50 * 200) * 1e6
+        prog.free()
     ex.close()
     e2e_value = total_bytes / e2e_ms / 1e6
 
@@ -695,7 +708,9 @@ def run_ours(args) -> None:
                 "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
                 "path": "deepxIR text -> libdeepx_exec.so (dx_exec_upload / dx_exec_run / dx_exec_download), pinned host buffers"},
         "executor": {"us_per_ir_line": None if executor_us is None else round(executor_us, 2),
-                     "what": "3000 addscalar lines on a 16-element tensor through dx_exec_run from Python (parse + dispatch + launch)"},
+                     "us_per_ir_line_compiled": None if compiled_us is None else round(compiled_us, 2),
+                     "what": "3000 addscalar lines on a 16-element tensor through dx_exec_run from Python (parse + dispatch + launch); "
+                             "compiled: the same line 200x as one program captured into a CUDA graph (dx_exec_compile), 50 replays"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "global_sum": got_sum,

@@ -16,6 +16,11 @@ struct dx_exec {
     dx_exec(int device, size_t limit) : ex(device, limit) {}
 };
 
+struct dx_program {
+    dx_exec *owner;
+    std::shared_ptr<CompiledProgram> prog;
+};
+
 namespace {
 thread_local std::string g_err;
 int put(const std::string &s, char *out, size_t cap) {
@@ -72,6 +77,26 @@ void dx_exec_fusion_stats(dx_exec *e, uint64_t stats[4]) {
     const FusionStats &f = e->ex.fusion_stats();
     stats[0] = f.programs; stats[1] = f.rmsnorm_groups; stats[2] = f.softmax_groups; stats[3] = f.lines_absorbed;
 }
+
+dx_program *dx_exec_compile(dx_exec *e, const char *program) {
+    if (!e || !program) { g_err = "null executor or program"; return nullptr; }
+    std::string why;
+    auto cp = e->ex.compile(program, &why);
+    if (!cp) { g_err = "compile: " + why; return nullptr; }
+    return new dx_program{e, cp};
+}
+int dx_program_run(dx_program *p) {
+    if (!p) { g_err = "null program"; return 1; }
+    std::string why;
+    const int rc = p->owner->ex.replay(*p->prog, &why);
+    if (rc != 0) g_err = why;
+    return rc;
+}
+void dx_program_info(dx_program *p, size_t info[4]) {
+    if (!p || !info) return;
+    info[0] = p->prog->lines; info[1] = p->prog->ops; info[2] = p->prog->nodes; info[3] = p->prog->fused_groups;
+}
+void dx_program_free(dx_program *p) { delete p; }
 
 int dx_exec_bind_tensor(dx_exec *e, const char *name, int dtype, const int64_t *shape, int ndim, void *device_ptr) {
     if (!e || !name || !*name || (ndim > 0 && !shape) || ndim < 0 || ndim > DX_MAX_DIMS) { g_err = "bind: bad argument"; return -1; }

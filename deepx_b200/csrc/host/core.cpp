@@ -370,6 +370,8 @@ const ArgValue *Mem::get_arg(const std::string &name) const {
 
 void *Mem::scratch(size_t bytes) {
     if (bytes <= scratch_bytes_) return scratch_;
+    if (capturing) throw std::runtime_error("the reduce workspace would have to grow while a program is being captured");
+    ++scratch_generation_;
     if (scratch_) dx_pool_free(pool_, scratch_);
     scratch_bytes_ = std::max(bytes, size_t(1) << 20);
     scratch_ = dx_pool_alloc(pool_, scratch_bytes_);
@@ -406,34 +408,45 @@ void Param::parse(const std::string &text) {
 
 void Metadata::parse(const std::string &meta) {
     if (meta.empty()) return;
-    std::unordered_map<std::string, std::string> kv;
-    std::istringstream ss(meta);
-    std::string tok;
-    while (ss >> tok) {
-        const size_t eq = tok.find('=');
-        if (eq == std::string::npos) continue;
-        kv[tok.substr(0, eq)] = tok.substr(eq + 1);
-    }
     using std::chrono::system_clock;
-    if (kv.count("id")) id = std::stoi(kv["id"]);
-    if (kv.count("author")) author = kv["author"];
-    if (kv.count("created_at")) created_at = system_clock::from_time_t(time_t(std::stod(kv["created_at"])));
-    if (kv.count("sent_at")) sent_at = system_clock::from_time_t(time_t(std::stod(kv["sent_at"])));
-    if (kv.count("recv_at")) recv_at = system_clock::from_time_t(time_t(std::stod(kv["recv_at"])));
-    if (kv.count("benchmark.repeat")) benchmark_repeat = std::stoi(kv["benchmark.repeat"]);
+    // whitespace-separated key=value tokens; a token without '=' is ignored; the last value of a key wins
+    // (plain scanning: this runs once per IR line, and string streams cost more than the rest of the parse)
+    size_t pos = 0;
+    const size_t n = meta.size();
+    while (pos < n) {
+        while (pos < n && std::isspace(static_cast<unsigned char>(meta[pos]))) ++pos;
+        size_t end = pos;
+        while (end < n && !std::isspace(static_cast<unsigned char>(meta[end]))) ++end;
+        if (end > pos) {
+            const size_t eq = meta.find('=', pos);
+            if (eq != std::string::npos && eq < end) {
+                const std::string key = meta.substr(pos, eq - pos), val = meta.substr(eq + 1, end - eq - 1);
+                if (key == "id") id = std::stoi(val);
+                else if (key == "author") author = val;
+                else if (key == "created_at") created_at = system_clock::from_time_t(time_t(std::stod(val)));
+                else if (key == "sent_at") sent_at = system_clock::from_time_t(time_t(std::stod(val)));
+                else if (key == "recv_at") recv_at = system_clock::from_time_t(time_t(std::stod(val)));
+                else if (key == "benchmark.repeat") benchmark_repeat = std::stoi(val);
+            }
+        }
+        pos = end;
+    }
 }
 
 namespace {
 std::vector<Param> parse_params(const std::string &list) {
     std::vector<Param> out;
-    std::istringstream ss(list);
-    std::string item;
-    while (std::getline(ss, item, ',')) {
+    size_t pos = 0;
+    while (pos <= list.size()) {
+        size_t comma = list.find(',', pos);
+        if (comma == std::string::npos) comma = list.size();
+        std::string item = list.substr(pos, comma - pos);
         trim_spaces(item);
-        if (item.empty()) continue;
-        Param p;
-        p.parse(item);
-        out.push_back(p);
+        if (!item.empty()) {
+            out.emplace_back();
+            out.back().parse(item);
+        }
+        pos = comma + 1;
     }
     return out;
 }
@@ -743,6 +756,126 @@ std::vector<OpResp> Executor::run_program(const std::string &text) {
         }
     }
     return replies;
+}
+
+CompiledProgram::~CompiledProgram() {
+    if (exec) cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(exec));
+    if (graph) cudaGraphDestroy(static_cast<cudaGraph_t>(graph));
+}
+
+std::shared_ptr<CompiledProgram> Executor::compile(const std::string &text, std::string *error) {
+    auto failed = [&](const std::string &why) {
+        if (error) *error = why;
+        return std::shared_ptr<CompiledProgram>();
+    };
+    std::vector<TF> program;
+    {
+        std::istringstream ss(text);
+        std::string line;
+        while (std::getline(ss, line)) {
+            if (!line.empty() && line.back() == '\r') line.pop_back();
+            if (line.find_first_not_of(" \t") == std::string::npos) continue;
+            try {
+                program.emplace_back(line);
+            } catch (const std::exception &e) {
+                return failed("line " + std::to_string(program.size() + 1) + ": " + e.what());
+            }
+        }
+    }
+    if (program.empty()) return failed("empty program");
+    FusionStats before = fusion_;
+    const std::vector<PlanItem> plan = fuse ? plan_fusion(program, mem_, &fusion_) : std::vector<PlanItem>(program.size());
+    std::vector<TF> ops;
+    static const char *refused[] = {"newtensor", "deltensor", "renametensor", "print", "save", "load", "loadtensordata", "argset", "vecset"};
+    for (size_t i = 0; i < program.size(); ++i) {
+        if (plan[i].kind == PlanItem::ABSORBED) continue;
+        const TF &t = plan[i].kind == PlanItem::FUSED ? plan[i].fused : program[i];
+        for (const char *r : refused)
+            if (t.name == r) return failed("line " + std::to_string(i + 1) + ": " + t.name + " cannot be part of a compiled program (compute ops only)");
+        if (t.metadata.benchmark_repeat > 0) return failed("line " + std::to_string(i + 1) + ": a timed line (benchmark.repeat) cannot be captured");
+        ops.push_back(t);
+    }
+    if (ops.empty()) return failed("nothing to run after fusion");
+    // pass 1: a normal run — grows the workspace, does first-call set-up, and its results stand
+    for (size_t i = 0; i < ops.size(); ++i) {
+        const OpResp r = run(ops[i]);
+        if (r.result != "ok") return failed(ops[i].name + ": " + r.message);
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(mem_.stream());
+    cudaSetDevice(mem_.device());
+    if (cudaStreamSynchronize(st) != cudaSuccess) return failed(std::string("stream: ") + cudaGetErrorString(cudaGetLastError()));
+    // pass 2: the same ops, captured instead of executed
+    auto out = std::make_shared<CompiledProgram>();
+    if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+        return failed(std::string("cudaStreamBeginCapture: ") + cudaGetErrorString(cudaGetLastError()));
+    mem_.capturing = true;
+    std::string why;
+    for (size_t i = 0; i < ops.size() && why.empty(); ++i) {
+        const OpResp r = run(ops[i]);
+        if (r.result != "ok") why = ops[i].name + ": " + r.message;
+    }
+    mem_.capturing = false;
+    cudaGraph_t graph = nullptr;
+    const cudaError_t ce = cudaStreamEndCapture(st, &graph);
+    if (why.empty() && ce != cudaSuccess) why = std::string("cudaStreamEndCapture: ") + cudaGetErrorString(ce);
+    if (!why.empty()) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        return failed(why);
+    }
+    out->graph = graph;
+    cudaGraphExec_t exec = nullptr;
+    if (cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) return failed(std::string("cudaGraphInstantiate: ") + cudaGetErrorString(cudaGetLastError()));
+    out->exec = exec;
+    size_t nodes = 0;
+    cudaGraphGetNodes(graph, nullptr, &nodes);
+    out->nodes = nodes;
+    out->lines = program.size();
+    out->ops = ops.size();
+    out->fused_groups = size_t((fusion_.rmsnorm_groups - before.rmsnorm_groups) + (fusion_.softmax_groups - before.softmax_groups));
+    out->scratch_generation = mem_.scratch_generation();
+    for (const TF &t : ops) {
+        auto note = [&](const Param &q) {
+            if ((q.dtype.category & (CAT_TENSOR | CAT_LISTTENSOR)) == 0) return;
+            std::string names = q.textvalue;
+            trim_chars(names, "[]");
+            std::istringstream ns(names);
+            std::string nm;
+            while (ns >> nm) {
+                if (!mem_.exists_tensor(nm)) continue;
+                bool seen = false;
+                for (const auto &r : out->refs) seen |= (r.name == nm);
+                if (seen) continue;
+                const TensorPtr p = mem_.get_tensor(nm);
+                out->refs.push_back({nm, p->data, p->shape.dtype, p->shape.shape});
+            }
+        };
+        for (const auto &q : t.args) note(q);
+        for (const auto &q : t.returns) note(q);
+    }
+    return out;
+}
+
+int Executor::replay(CompiledProgram &program, std::string *error) {
+    auto failed = [&](const std::string &why) {
+        if (error) *error = why;
+        return 1;
+    };
+    if (!program.exec) return failed("program was not compiled");
+    std::lock_guard<std::mutex> lk(mu_);
+    if (program.scratch_generation != mem_.scratch_generation())
+        return failed("stale program: the reduce workspace moved since it was compiled; compile it again");
+    for (const auto &r : program.refs) {
+        if (!mem_.exists_tensor(r.name)) return failed("stale program: tensor " + r.name + " no longer exists; compile it again");
+        const TensorPtr p = mem_.get_tensor(r.name);
+        if (p->data != r.data || p->shape.dtype != r.precision || p->shape.shape != r.shape)
+            return failed("stale program: tensor " + r.name + " changed storage, dtype or shape; compile it again");
+    }
+    cudaSetDevice(mem_.device());
+    const cudaError_t e = cudaGraphLaunch(static_cast<cudaGraphExec_t>(program.exec), static_cast<cudaStream_t>(mem_.stream()));
+    if (e != cudaSuccess) return failed(std::string("cudaGraphLaunch: ") + cudaGetErrorString(e));
+    ops_run_ += program.ops;
+    return 0;
 }
 
 }  // namespace dxh

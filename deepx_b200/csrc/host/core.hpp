@@ -127,6 +127,11 @@ class Mem {
     int device() const { return device_; }
     void *stream() const { return stream_; }
     void *scratch(size_t bytes);  // grow-only workspace for reductions, from the pool
+    // While a program is being captured into a CUDA graph nothing may be allocated: the graph keeps
+    // the pointers it saw.  `capturing` makes scratch growth and staging temporaries throw instead;
+    // `scratch_generation` changes whenever the workspace moves, which invalidates earlier captures.
+    bool capturing = false;
+    uint64_t scratch_generation() const { return scratch_generation_; }
     size_t tensor_count() const { return tensors_.size(); }
     std::vector<std::string> tensor_names() const;
 
@@ -136,6 +141,7 @@ class Mem {
     void *stream_ = nullptr;
     void *scratch_ = nullptr;
     size_t scratch_bytes_ = 0;
+    uint64_t scratch_generation_ = 0;
     std::unordered_map<std::string, TensorPtr> tensors_;
     std::unordered_map<std::string, ArgValue> args_;
 };
@@ -225,6 +231,24 @@ struct FusionStats {
     uint64_t lines_absorbed = 0;  // IR lines that no longer run (chain steps, temp newtensor/deltensor)
 };
 
+struct CompiledProgram {
+    struct Ref {
+        std::string name;
+        void *data;
+        uint16_t precision;
+        std::vector<int64_t> shape;
+    };
+    void *graph = nullptr;  // cudaGraph_t
+    void *exec = nullptr;   // cudaGraphExec_t
+    std::vector<Ref> refs;
+    uint64_t scratch_generation = 0;
+    size_t lines = 0, ops = 0, nodes = 0, fused_groups = 0;
+    CompiledProgram() = default;
+    CompiledProgram(const CompiledProgram &) = delete;
+    CompiledProgram &operator=(const CompiledProgram &) = delete;
+    ~CompiledProgram();
+};
+
 // ---- executor: one IR line in, one reply out (executor/op-cuda/src/client/main.cpp:47-102) --------------------
 class Executor {
   public:
@@ -236,6 +260,15 @@ class Executor {
     // program run as one kernel; the replies of the lines that no longer run say "ok".
     std::vector<OpResp> run_program(const std::string &text);
     const FusionStats &fusion_stats() const { return fusion_; }
+    // A program whose kernels are captured once into a CUDA graph and then replayed with one launch
+    // call: for sequences of small ops the host cost per IR line (parse, dispatch, launch) is what
+    // limits throughput, and a replay has none of it.  The program may only compute: tensor lifetime,
+    // io and arg ops, timed lines and ops that need a temporary are refused (chains that the fusion
+    // pass absorbs, temporaries included, are fine).  compile() runs the program once (that run's
+    // results stand) and captures a second pass; replay() first checks that every tensor the program
+    // names still exists with the same storage, dtype and shape.
+    std::shared_ptr<CompiledProgram> compile(const std::string &text, std::string *error);
+    int replay(CompiledProgram &program, std::string *error);
     bool fuse = true;
     Mem &mem() { return mem_; }
     const TfFactory &factory() const { return factory_; }

@@ -215,6 +215,7 @@ struct Staged {
     TensorPtr out;
     void *tmp = nullptr;
     Staged(Mem &m, TensorPtr o, bool aliased) : mem(m), out(std::move(o)) {
+        if (aliased && mem.capturing) throw std::runtime_error("an op whose output is also its input needs a temporary, which a captured program cannot hold");
         if (aliased) {
             tmp = dx_pool_alloc(mem.pool(), size_t(std::max<int64_t>(out->shape.bytes(), 1)));
             if (!tmp) throw std::runtime_error(dx_last_error());

@@ -22,6 +22,10 @@ SIGNATURES = {
     "dx_exec_run_program": (_i, [_vp, _cp, C.c_char_p, _sz]),
     "dx_exec_set_fusion": (None, [_vp, _i]),
     "dx_exec_fusion_stats": (None, [_vp, C.POINTER(C.c_uint64)]),
+    "dx_exec_compile": (_vp, [_vp, _cp]),
+    "dx_program_run": (_i, [_vp]),
+    "dx_program_info": (None, [_vp, C.POINTER(C.c_size_t)]),
+    "dx_program_free": (None, [_vp]),
     "dx_exec_bind_tensor": (_i, [_vp, _cp, _i, C.POINTER(C.c_int64), _i, _vp]),
     "dx_exec_tensor_info": (_i, [_vp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int64), _i]),
     "dx_exec_tensor_ptr": (_vp, [_vp, _cp]),
@@ -113,6 +117,32 @@ class IRError(RuntimeError):
     pass
 
 
+class Program:
+    """A compiled program: its kernels captured into a CUDA graph (Executor.compile)."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    def run(self) -> None:
+        """Replays the graph on the executor's stream (asynchronous).  IRError when a tensor the
+        program names was deleted, re-created or reshaped since compilation."""
+        if lib().dx_program_run(self._h) != 0:
+            raise IRError(lib().dx_exec_last_error().decode())
+
+    def info(self) -> dict:
+        st = (C.c_size_t * 4)()
+        lib().dx_program_info(self._h, st)
+        return {"lines": st[0], "ops": st[1], "graph_nodes": st[2], "fused_chains": st[3]}
+
+    def free(self) -> None:
+        if self._h:
+            lib().dx_program_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.free()
+
+
 class Executor:
     def __init__(self, device: int = 0, pool_limit_bytes: int = 0):
         self._h = lib().dx_exec_create(device, pool_limit_bytes)
@@ -150,6 +180,13 @@ class Executor:
         if check and rc != 0:
             raise IRError("\n".join(r for r in replies if " ok" not in r.split("//")[0]))
         return replies
+
+    def compile(self, program: str) -> Program:
+        """Runs `program` once and captures it into a CUDA graph (compute ops only)."""
+        h = lib().dx_exec_compile(self._h, program.encode())
+        if not h:
+            raise IRError(lib().dx_exec_last_error().decode())
+        return Program(h)
 
     def set_fusion(self, on: bool) -> None:
         lib().dx_exec_set_fusion(self._h, 1 if on else 0)

@@ -48,6 +48,23 @@ void dx_exec_set_fusion(dx_exec *e, int on);
 /* [0] programs seen, [1] RMSNorm chains rewritten, [2] softmax chains rewritten, [3] IR lines absorbed. */
 void dx_exec_fusion_stats(dx_exec *e, uint64_t stats[4]);
 
+/* A program whose kernels are captured once into a CUDA graph and replayed with one launch call:
+ * for sequences of small ops the host cost per IR line is what limits throughput, and a replay
+ * has none of it (the reference pays a UDP round trip per line).  The program may only compute:
+ * tensor lifetime, io and arg ops, timed lines, and ops that would need a temporary are refused;
+ * op chains the fusion pass absorbs (with their temporaries) are fine.  dx_exec_compile runs the
+ * program once — those results stand — and captures a second pass; NULL on failure
+ * (dx_exec_last_error).  dx_program_run checks that every tensor the program names still has the
+ * same storage, dtype and shape, then launches the graph on the executor's stream (asynchronous);
+ * 0 ok, 1 = stale or failed (dx_exec_last_error), and the program must be compiled again.
+ * info: [0] IR lines, [1] ops captured after fusion, [2] graph nodes, [3] fused chains.
+ * Free programs before destroying their executor. */
+typedef struct dx_program dx_program;
+dx_program *dx_exec_compile(dx_exec *e, const char *program);
+int dx_program_run(dx_program *p);
+void dx_program_info(dx_program *p, size_t info[4]);
+void dx_program_free(dx_program *p);
+
 /* Registers device memory the executor does not own (a heap tensor mapped with dx_heap_open, a
  * buffer of the embedding application) as tensor `name`, so IR ops can read and write it.  The
  * executor never frees it; deltensor only forgets the name.  The memory must stay valid, on the

@@ -7,7 +7,7 @@ tests/golden/frontend_ir/<example>.ir.  The GPU tests replay those transcripts t
 executor and check every op's result, so the executor is exercised with exactly the text the
 real front end produces.
 
-    python tests/golden/record_frontend_ir.py [/root/reference]
+    python tests/golden/record_frontend_ir.py [path of the reference tree]
 """
 import contextlib
 import io
