@@ -800,6 +800,35 @@ def run_sweep(args) -> None:
             o = [torch.empty([t3[0].shape[q] for q in perm], dtype=dt, device=dev) for _ in range(R)]
             run(f"transpose<{dn}> [64,512,{n // 32768}] {perm}", [lambda i=i, perm=perm, o=o: TF.transpose(t3[i], perm, o[i]) for i in range(R)], 2 * n * es)
             del o
+        if dn in ("f32", "bf16", "i8"):
+            # concat of four equal parts along each axis of a 3-d tensor (output 256 MiB)
+            q3 = [t.view(64, 512, n // 32768) for t in a]
+            for axis in (0, 1, 2):
+                parts = [[q3[i].narrow(axis, k * (q3[i].shape[axis] // 4), q3[i].shape[axis] // 4).contiguous() for k in range(4)] for i in range(R)]
+                o = [torch.empty_like(q3[0]) for _ in range(R)]
+                run(f"concat<{dn}> 4 parts of [64,512,{n // 32768}] axis {axis}", [lambda i=i, axis=axis, parts=parts, o=o: TF.concat(parts[i], axis, o[i]) for i in range(R)], 2 * n * es)
+                del parts, o
+            # broadcastTo: a row repeated (inner axis kept), a column repeated (inner axis replicated), a scalar
+            row, col = a[0][: n // 4096].view(1, n // 4096).contiguous(), a[0][:4096].view(4096, 1).contiguous()
+            o = [torch.empty(4096, n // 4096, dtype=dt, device=dev) for _ in range(R)]
+            run(f"broadcastTo<{dn}> [1,{n // 4096}] -> [4096,{n // 4096}]", [lambda i=i: TF.broadcastTo(row, [4096, n // 4096], o[i]) for i in range(R)], n * es + row.numel() * es)
+            run(f"broadcastTo<{dn}> [4096,1] -> [4096,{n // 4096}]", [lambda i=i: TF.broadcastTo(col, [4096, n // 4096], o[i]) for i in range(R)], n * es + 4096 * es)
+            del o
+            # indexselect: rows of a [65536, n/65536] table by 2^16 random indices (axis 0), and along the inner axis
+            table = [t.view(65536, n // 65536) for t in a]
+            idx = torch.randint(0, 65536, (65536,), device=dev, dtype=torch.int32)
+            o = [torch.empty_like(table[0]) for _ in range(R)]
+            run(f"indexselect<{dn}> rows of [65536,{n // 65536}]", [lambda i=i: TF.indexselect(table[i], idx, 0, o[i]) for i in range(R)], 2 * n * es + 65536 * 4)
+            wide = [t.view(n // 1024, 1024) for t in a]
+            idx2 = torch.randint(0, 1024, (1024,), device=dev, dtype=torch.int32)
+            o2 = [torch.empty_like(wide[0]) for _ in range(R)]
+            run(f"indexselect<{dn}> inner axis of [{n // 1024},1024]", [lambda i=i: TF.indexselect(wide[i], idx2, 1, o2[i]) for i in range(R)], 2 * n * es + 4096)
+            del table, o, wide, o2
+            # repeat: [64,512,n/131072] x (1,2,2)
+            src = a[0][: n // 4].view(64, 512, n // 131072)
+            o = [torch.empty(64, 1024, n // 65536, dtype=dt, device=dev) for _ in range(R)]
+            run(f"repeat<{dn}> [64,512,{n // 131072}] x (1,2,2)", [lambda i=i: TF.repeat(src, [1, 2, 2], o[i]) for i in range(R)], n * es + (n // 4) * es)
+            del o, q3
         del a, b, c, m, x, t3
         torch.cuda.empty_cache()
     low = {k: v for k, v in res.items() if v < 0.8}

@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(CB) indexselect_kernel(const char *__restrict_
     }
 }
 
-// ---- repeat (per element; not on the bandwidth-critical list) -----------------------------------
+// ---- repeat, per element (only for ranks whose (S, r) axis pairs exceed the kernels' axis limit) ---
 struct RepeatParams {
     Dims outd;                 // output extents; stride = source bytes
     FastDiv rep[MAXD];         // repeats per axis
@@ -376,6 +376,77 @@ __global__ void __launch_bounds__(CB) repeat_kernel(const char *__restrict__ in,
         idx = q;
     }
     out[v] = *reinterpret_cast<const E *>(in + off);
+}
+
+// ---- repeat along the innermost axis (each source element r times in a row) ------------------
+// One thread builds one 16-byte output vector; its source elements are neighbours of the ones the
+// next threads read, so the (cached) element loads of a warp fall into a few sectors.
+struct InnerRepeatParams {
+    Dims rows;        // outer output axes; strides point into the source (0 for a repeat axis)
+    FastDiv run;      // 16-byte vectors per output row
+    FastDiv rep;      // r
+    uint32_t units;   // output vectors
+};
+template <typename E>
+__global__ void __launch_bounds__(CB) inner_repeat_kernel(const char *__restrict__ in, char *__restrict__ out, InnerRepeatParams p) {
+    constexpr int VEC = 16 / int(sizeof(E));
+    const uint32_t v = blockIdx.x * CB + threadIdx.x;
+    if (v >= p.units) return;
+    const uint32_t row = fd_div(v, p.run);
+    const uint32_t e0 = (v - row * p.run.d) * VEC;
+    const E *src = reinterpret_cast<const E *>(in + unravel_bytes(row, p.rows));
+    Pack<E, VEC> o;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) o.v[j] = src[fd_div(e0 + j, p.rep)];
+    st_stream<E, VEC>(reinterpret_cast<E *>(out) + int64_t(v) * VEC, o);
+}
+
+// r a power of two: the VEC / R (at least one) source elements of an output vector are one aligned
+// load, expanded in registers.
+template <typename E, int R>
+__global__ void __launch_bounds__(CB) inner_repeat_pow2_kernel(const char *__restrict__ in, char *__restrict__ out, InnerRepeatParams p) {
+    constexpr int VEC = 16 / int(sizeof(E));
+    constexpr int M = (VEC / R) > 0 ? (VEC / R) : 1;
+    const uint32_t v0 = blockIdx.x * (CB * CUNROLL) + threadIdx.x;
+    Pack<E, M> sv[CUNROLL];
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k) {  // every load of the thread is issued before the first store
+        const uint32_t v = v0 + k * CB;
+        if (v < p.units) {
+            const uint32_t row = fd_div(v, p.run);
+            const uint32_t e0 = (v - row * p.run.d) * VEC;
+            sv[k] = ld_cached<E, M>(reinterpret_cast<const E *>(in + unravel_bytes(row, p.rows)) + e0 / R);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < CUNROLL; ++k) {
+        const uint32_t v = v0 + k * CB;
+        if (v < p.units) {
+            Pack<E, VEC> o;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) o.v[j] = sv[k].v[(j / R) < M ? (j / R) : 0];
+            st_stream<E, VEC>(reinterpret_cast<E *>(out) + int64_t(v) * VEC, o);
+        }
+    }
+}
+template <typename E> void launch_inner_repeat(unsigned g, cudaStream_t st, const void *a, void *out, const InnerRepeatParams &q, int64_t r,
+                                               bool src_aligned) {
+    constexpr int VEC = 16 / int(sizeof(E));
+    const char *in = (const char *)a;
+    char *o = (char *)out;
+    // the wide source load needs the source rows aligned to VEC / r elements
+    if (src_aligned) {
+        const unsigned g4 = (unsigned)((int64_t(q.units) + int64_t(CB) * CUNROLL - 1) / (int64_t(CB) * CUNROLL));
+        switch (r) {
+            case 2: inner_repeat_pow2_kernel<E, 2><<<g4, CB, 0, st>>>(in, o, q); return;
+            case 4: inner_repeat_pow2_kernel<E, 4><<<g4, CB, 0, st>>>(in, o, q); return;
+            case 8: inner_repeat_pow2_kernel<E, 8><<<g4, CB, 0, st>>>(in, o, q); return;
+            case 16: inner_repeat_pow2_kernel<E, 16><<<g4, CB, 0, st>>>(in, o, q); return;
+            default: break;
+        }
+    }
+    (void)VEC;
+    inner_repeat_kernel<E><<<g, CB, 0, st>>>(in, o, q);
 }
 
 template <int W, typename E>
@@ -750,6 +821,59 @@ extern "C" int dx_repeat(int dtype, const void *a, const int64_t *a_shape, int n
     if (!a || !out) return fail(DX_E_ARG, "repeat: null pointer");
     if (n >= (1ll << 31)) return fail(DX_E_SHAPE, "repeat: output too large");
     if (overlaps(a, na * es, out, n * es)) return fail(DX_E_ALIAS, "repeat: output overlaps input");
+    // innermost axis repeated a few times: the splat kernel's words would be r elements wide, too narrow
+    if (ndim >= 1 && repeats[ndim - 1] > 1 && repeats[ndim - 1] <= 64 && aligned_to(out, 16) &&
+        (a_shape[ndim - 1] * repeats[ndim - 1] * es) % 16 == 0 && n * es / 16 < (1ll << 31)) {
+        InnerRepeatParams q;
+        q.rows.n = 0;
+        int64_t sstride = a_shape[ndim - 1];  // source stride, in elements, of the axis being added
+        bool fits = true;
+        std::vector<std::pair<int64_t, int64_t>> axes;  // (extent, source byte stride), innermost first
+        for (int i = ndim - 2; i >= 0; --i) {
+            if (repeats[i] > 1) axes.push_back({repeats[i], 0});
+            axes.push_back({a_shape[i], sstride * es});
+            sstride *= a_shape[i];
+        }
+        if (int(axes.size()) > MAXD) fits = false;
+        if (fits) {
+            for (auto it = axes.rbegin(); it != axes.rend(); ++it) {  // outermost first
+                q.rows.fd[q.rows.n] = make_fastdiv((uint32_t)it->first);
+                q.rows.stride[q.rows.n] = it->second;
+                ++q.rows.n;
+            }
+            q.run = make_fastdiv((uint32_t)(a_shape[ndim - 1] * repeats[ndim - 1] * es / 16));
+            q.rep = make_fastdiv((uint32_t)repeats[ndim - 1]);
+            q.units = (uint32_t)(n * es / 16);
+            const unsigned g = (unsigned)((int64_t(q.units) + CB - 1) / CB);
+            // every source row starts on a 16-byte boundary (so any VEC / r element load inside it is aligned)
+            const bool src_aligned = aligned_to(a, 16) && (a_shape[ndim - 1] * es) % 16 == 0;
+            const int64_t r = repeats[ndim - 1];
+            switch (es) {
+                case 8: launch_inner_repeat<uint64_t>(g, st, a, out, q, r, src_aligned); break;
+                case 4: launch_inner_repeat<uint32_t>(g, st, a, out, q, r, src_aligned); break;
+                case 2: launch_inner_repeat<uint16_t>(g, st, a, out, q, r, src_aligned); break;
+                default: launch_inner_repeat<uint8_t>(g, st, a, out, q, r, src_aligned); break;
+            }
+            return check_launch("repeat(inner)");
+        }
+    }
+    // Each axis of extent S repeated r times is the pair of axes (S, r) with source strides
+    // (stride, 0): the repeat is a broadcast of [S0,1,S1,1,…] to [S0,r0,S1,r1,…], which the word-wide
+    // run / splat kernels move at memory speed.  Only when that needs more axes than the kernels
+    // carry does the per-element kernel below run.
+    {
+        std::vector<int64_t> src_shape, dst_shape;
+        for (int i = 0; i < ndim; ++i) {
+            src_shape.push_back(a_shape[i]);
+            dst_shape.push_back(a_shape[i]);
+            if (repeats[i] > 1) {
+                src_shape.push_back(1);
+                dst_shape.push_back(repeats[i]);
+            }
+        }
+        if (int(dst_shape.size()) <= MAXD)
+            return dx_broadcast_to(dtype, a, src_shape.data(), int(src_shape.size()), dst_shape.data(), int(dst_shape.size()), out, stream);
+    }
     p.units = (uint32_t)n;
     const unsigned grid = (unsigned)((n + CB - 1) / CB);
     switch (es) {

@@ -176,7 +176,12 @@ def test_indexselect_out_of_range_is_flagged(mods):
 def test_repeat(mods, dtype):
     TF, O = mods
     rng = np.random.default_rng(seed_of("rep", dtype))
-    for ashape, rep in [((3, 4), (2, 3)), ((5,), (7,)), ((2, 3, 4), (1, 1, 1)), ((2, 1, 5), (3, 4, 2))]:
+    for ashape, rep in [((3, 4), (2, 3)), ((5,), (7,)), ((2, 3, 4), (1, 1, 1)), ((2, 1, 5), (3, 4, 2)),
+                        ((4, 8, 33, 64), (1, 4, 1, 1)),        # the KV-head repeat of grouped-query attention
+                        ((4, 64), (1, 2)), ((3, 5, 32), (2, 1, 4)), ((2, 3, 4, 16), (3, 1, 2, 8)), ((7, 48), (1, 64)),  # innermost-repeat kernel
+                        ((6, 130), (2, 1)), ((6, 130), (1, 3)), ((3, 5, 7), (2, 2, 2)), ((1, 1, 1), (2, 3, 4)),
+                        ((2, 2, 2, 2, 2, 2), (2, 1, 2, 1, 2, 3)),  # 6 axes x 2 = 11 axis pairs: still word-wide
+                        ((2, 1, 2, 1, 2, 1, 2), (2, 2, 2, 2, 2, 2, 2))]:  # 14 > 12: the per-element kernel
         a = make(rng, dtype, ashape)
         out = torch.empty([s * r for s, r in zip(ashape, rep)], dtype=TORCH_DTYPES[dtype], device="cuda:0")
         TF.repeat(to_gpu(a), list(rep), out)
