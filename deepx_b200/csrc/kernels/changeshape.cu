@@ -356,6 +356,90 @@ __global__ void __launch_bounds__(CB) indexselect_kernel(const char *__restrict_
     }
 }
 
+// Gather along the INNERMOST axis (slices of one element): a thread assembles a whole 16-byte output
+// vector from VEC element reads of one source row (neighbouring threads read the same row, so the
+// reads stay in L1) instead of moving one element per thread.
+struct InnerGatherParams {
+    FastDiv run;       // output vectors per row (indices / VEC)
+    int64_t axis_len;  // elements per source row
+    uint32_t units;    // output vectors
+};
+template <typename E, typename I>
+__global__ void __launch_bounds__(CB) indexselect_inner_kernel(const E *__restrict__ in, const I *__restrict__ idx, E *__restrict__ out,
+                                                               InnerGatherParams p, int32_t *oob) {
+    constexpr int VEC = 16 / int(sizeof(E));
+    const uint32_t v = blockIdx.x * CB + threadIdx.x;
+    if (v >= p.units) return;
+    const uint32_t row = fd_div(v, p.run);
+    const uint32_t j0 = (v - row * p.run.d) * VEC;
+    const E *src = in + int64_t(row) * p.axis_len;
+    int64_t ix[VEC];
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) ix[j] = static_cast<int64_t>(idx[j0 + j]);
+    Pack<E, VEC> o;
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+        const bool ok = ix[j] >= 0 && ix[j] < p.axis_len;
+        o.v[j] = ok ? src[ok ? ix[j] : 0] : E(0);
+        bad |= !ok;
+    }
+    if (bad && oob) atomicOr(oob, 1);
+    st_stream<E, VEC>(out + int64_t(v) * VEC, o);
+}
+
+// The same gather with the source rows staged in shared memory: random element reads cost one L1
+// sector access per lane from global memory (32 per warp load), but only a few bank conflicts from
+// shared memory.  A CTA keeps the (validated) index list in shared memory and walks groups of R
+// source rows: coalesced 16-byte loads in, picks, 16-byte stores out.
+struct InnerGatherSmemParams {
+    int64_t rows;   // source rows (product of the outer axes)
+    int K, J, R;    // elements per source row, indices, rows staged per pass
+    int row_vec;    // 1: source rows can be loaded as 16-byte vectors
+};
+template <typename E, typename I>
+__global__ void __launch_bounds__(CB) indexselect_inner_smem_kernel(const E *__restrict__ in, const I *__restrict__ idx, E *__restrict__ out,
+                                                                    InnerGatherSmemParams p, int32_t *oob) {
+    constexpr int VEC = 16 / int(sizeof(E));
+    extern __shared__ __align__(16) unsigned char smem_gather[];
+    int32_t *sidx = reinterpret_cast<int32_t *>(smem_gather);
+    E *srow = reinterpret_cast<E *>(smem_gather + ((size_t(p.J) * 4 + 15) / 16) * 16);
+    bool bad = false;
+    for (int j = threadIdx.x; j < p.J; j += CB) {
+        const int64_t ix = static_cast<int64_t>(idx[j]);
+        const bool ok = ix >= 0 && ix < p.K;
+        sidx[j] = ok ? int32_t(ix) : -1;
+        bad |= !ok;
+    }
+    if (bad && oob) atomicOr(oob, 1);
+    const int jvec = p.J / VEC;
+    for (int64_t r0 = int64_t(blockIdx.x) * p.R; r0 < p.rows; r0 += int64_t(gridDim.x) * p.R) {
+        const int nr = int(p.rows - r0 < p.R ? p.rows - r0 : p.R);
+        __syncthreads();  // the index list is complete / the previous group's picks are done
+        const E *src = in + r0 * p.K;
+        const int total = nr * p.K;
+        if (p.row_vec) {
+            for (int i = threadIdx.x; i < total / VEC; i += CB)
+                reinterpret_cast<Pack<E, VEC> *>(srow)[i] = ld_stream<E, VEC>(src + int64_t(i) * VEC);
+        } else {
+            for (int i = threadIdx.x; i < total; i += CB) srow[i] = src[i];
+        }
+        __syncthreads();
+        E *dst = out + r0 * p.J;
+        for (int v = threadIdx.x; v < nr * jvec; v += CB) {
+            const int lr = v / jvec, j0 = (v - lr * jvec) * VEC;
+            const E *row = srow + lr * p.K;
+            Pack<E, VEC> o;
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) {
+                const int32_t ix = sidx[j0 + j];
+                o.v[j] = ix >= 0 ? row[ix] : E(0);
+            }
+            st_stream<E, VEC>(dst + int64_t(lr) * p.J + j0, o);
+        }
+    }
+}
+
 // ---- repeat, per element (only for ranks whose (S, r) axis pairs exceed the kernels' axis limit) ---
 struct RepeatParams {
     Dims outd;                 // output extents; stride = source bytes
@@ -776,6 +860,51 @@ extern "C" int dx_indexselect(int dtype, const void *a, const int64_t *a_shape, 
     if (!a || !idx || !out) return fail(DX_E_ARG, "indexselect: null pointer");
     if (overlaps(a, na * es, out, n * es)) return fail(DX_E_ALIAS, "indexselect: output overlaps input");
     const int64_t slice_bytes = post * es;
+    if (post == 1 && (ni * es) % 16 == 0 && aligned_to(out, 16) && ni * 4 <= 16384 && a_shape[axis] * es <= 16384 && pre >= 64) {
+        // rows and index list fit in shared memory
+        InnerGatherSmemParams q;
+        q.rows = pre;
+        q.K = (int)a_shape[axis];
+        q.J = (int)ni;
+        q.R = (int)std::max<int64_t>(1, std::min<int64_t>(32768 / (a_shape[axis] * es), 32));
+        q.row_vec = (aligned_to(a, 16) && (a_shape[axis] * es) % 16 == 0) ? 1 : 0;
+        const size_t smem = ((size_t(q.J) * 4 + 15) / 16) * 16 + size_t(q.R) * q.K * es;
+        const int64_t groups = (pre + q.R - 1) / q.R;
+        const unsigned g = (unsigned)std::min<int64_t>(groups, int64_t(sm_count()) * 4);
+#define DX_INNER_SMEM(E)                                                                                                           \
+    do {                                                                                                                           \
+        if (idx_dtype == DX_I32) indexselect_inner_smem_kernel<E, int32_t><<<g, CB, smem, st>>>((const E *)a, (const int32_t *)idx, (E *)out, q, oob_flag); \
+        else indexselect_inner_smem_kernel<E, int64_t><<<g, CB, smem, st>>>((const E *)a, (const int64_t *)idx, (E *)out, q, oob_flag);       \
+    } while (0)
+        switch (es) {
+            case 8: DX_INNER_SMEM(uint64_t); break;
+            case 4: DX_INNER_SMEM(uint32_t); break;
+            case 2: DX_INNER_SMEM(uint16_t); break;
+            default: DX_INNER_SMEM(uint8_t); break;
+        }
+#undef DX_INNER_SMEM
+        return check_launch("indexselect(inner, staged)");
+    }
+    if (post == 1 && (ni * es) % 16 == 0 && aligned_to(out, 16) && n * es / 16 < (1ll << 31) && pre < (1ll << 31)) {
+        InnerGatherParams q;
+        q.run = make_fastdiv((uint32_t)(ni * es / 16));
+        q.axis_len = a_shape[axis];
+        q.units = (uint32_t)(n * es / 16);
+        const unsigned g = (unsigned)((int64_t(q.units) + CB - 1) / CB);
+#define DX_INNER_GATHER(E)                                                                                                        \
+    do {                                                                                                                          \
+        if (idx_dtype == DX_I32) indexselect_inner_kernel<E, int32_t><<<g, CB, 0, st>>>((const E *)a, (const int32_t *)idx, (E *)out, q, oob_flag); \
+        else indexselect_inner_kernel<E, int64_t><<<g, CB, 0, st>>>((const E *)a, (const int64_t *)idx, (E *)out, q, oob_flag);       \
+    } while (0)
+        switch (es) {
+            case 8: DX_INNER_GATHER(uint64_t); break;
+            case 4: DX_INNER_GATHER(uint32_t); break;
+            case 2: DX_INNER_GATHER(uint16_t); break;
+            default: DX_INNER_GATHER(uint8_t); break;
+        }
+#undef DX_INNER_GATHER
+        return check_launch("indexselect(inner)");
+    }
     const int w = widest_word(es, {slice_bytes}, {a, out});
     if (ni >= (1ll << 31) || slice_bytes / w >= (1ll << 31)) return fail(DX_E_SHAPE, "indexselect: extent too large");
     GatherParams p;

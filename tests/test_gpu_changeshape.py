@@ -152,6 +152,8 @@ def test_indexselect(mods, dtype, idt):
     for ashape, ishape, axis in [
         ((50, 896), (8, 20), 0), ((7, 9, 5), (4,), 1), ((7, 9, 5), (2, 3), 2), ((7, 9, 5), (6,), -1),
         ((100, 3), (1000,), 0), ((4, 33), (5, 1, 2), 1), ((10,), (3, 3), 0),
+        ((37, 100), (64,), 1), ((5, 6, 1000), (2, 16), 2), ((3, 70), (4, 8, 4), -1), ((9,), (32,), 0),  # innermost-axis vector kernel
+        ((100, 100), (64,), 1), ((70, 3, 40), (2, 16), 2), ((65, 1000), (16,), 1), ((1000, 7), (48,), -1), ((333, 4096), (16,), 1),  # staged in shared memory
     ]:
         a = make(rng, dtype, ashape)
         g = axis + len(ashape) if axis < 0 else axis
@@ -169,6 +171,19 @@ def test_indexselect_out_of_range_is_flagged(mods):
     flag = torch.zeros(1, dtype=torch.int32, device="cuda:0")
     TF.indexselect(to_gpu(a), to_gpu(idx), 0, out, flag)
     assert_bit_exact(to_np(out), O.indexselect(a, idx, 0), "indexselect oob rows are zero")
+    assert int(flag.item()) == 1
+    # the same along the innermost axis (the vector kernel): 16 indices, three of them out of range
+    idx2 = np.array([0, 2, 9, 1, -4, 2, 2, 1, 0, 0, 3, 1, 2, 0, 1, 2], dtype=np.int32)
+    out2 = torch.empty((4, 16), dtype=torch.float32, device="cuda:0")
+    flag.zero_()
+    TF.indexselect(to_gpu(a), to_gpu(idx2), 1, out2, flag)
+    assert_bit_exact(to_np(out2), O.indexselect(a, idx2, 1), "indexselect oob elements are zero")
+    assert int(flag.item()) == 1
+    big = np.arange(128 * 3, dtype=np.float32).reshape(128, 3)   # 128 rows: the staged kernel
+    out3 = torch.empty((128, 16), dtype=torch.float32, device="cuda:0")
+    flag.zero_()
+    TF.indexselect(to_gpu(big), to_gpu(idx2), 1, out3, flag)
+    assert_bit_exact(to_np(out3), O.indexselect(big, idx2, 1), "indexselect oob elements are zero (staged)")
     assert int(flag.item()) == 1
 
 
