@@ -698,7 +698,8 @@ def run_ours(args) -> None:
         "config": {"workload": "z=exp(x)*y+x, s=sum(z), m=reducemax(z,axis 1) on f32 [2048,1048576] U(-1,1) sharded on axis 0; "
                                "deepxIR ops exp,mul,add,sum,reducemax",
                    "rows": ROWS, "cols": COLS, "rows_per_gpu": my_rows, "parallelism": f"axis0-shard x{world}",
-                   "l2": "inputs larger than L2 (8 GiB per tensor)", "algorithmic_bytes_per_step": total_bytes},
+                   "l2": "inputs larger than L2 (8 GiB per tensor)", "algorithmic_bytes_per_step": total_bytes,
+                   "combine": "none (1 GPU)" if world == 1 else ("peer-memory kernel (dx_comm)" if ops.peer is not None else "NCCL all-reduce")},
         "roofline": {"bound": "hbm", "kernel": "ew2_kernel<mul,f32> (t=t*y)", "achieved": round(achieved, 1), "peak": peak,
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "traffic": round(MUL_TRAFFIC_PER_ROW * my_rows), "traffic_source": "ncu dram read+write of the same kernel on 256 rows "

@@ -35,16 +35,32 @@ class PeerComm:
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
         self.device = torch.cuda.current_device() if device is None else device
+        # Every step that can fail locally is followed by an exchange of who succeeded, so that either
+        # all ranks end up with a working communicator or all of them raise (nobody is left waiting).
         self._h = N.lib.dx_comm_create(self.rank, self.world, self.device)
-        if not self._h:
-            raise N.DxError(N.E_CUDA, N.lib.dx_last_error().decode())
-        buf = C.create_string_buffer(64)
-        N.check(N.lib.dx_comm_handle(self._h, buf))
+        mine = None
+        why = ""
+        if self._h:
+            buf = C.create_string_buffer(64)
+            if N.lib.dx_comm_handle(self._h, buf) == N.OK:
+                mine = bytes(buf.raw)
+        if mine is None:
+            why = N.lib.dx_last_error().decode()
         handles: list = [None] * self.world
-        dist.all_gather_object(handles, bytes(buf.raw), group=group)
-        N.check(N.lib.dx_comm_connect(self._h, b"".join(handles)))
+        dist.all_gather_object(handles, (mine, why), group=group)
+        if any(h is None for h, _ in handles):
+            self.close()
+            raise RuntimeError("PeerComm: mailbox set-up failed on rank(s) " +
+                               ", ".join(f"{r}: {w}" for r, (h, w) in enumerate(handles) if h is None))
+        rc = N.lib.dx_comm_connect(self._h, b"".join(h for h, _ in handles))
+        status: list = [None] * self.world
+        dist.all_gather_object(status, (rc, "" if rc == N.OK else N.lib.dx_last_error().decode()), group=group)
+        if any(r != N.OK for r, _ in status):
+            self.close()
+            raise RuntimeError("PeerComm: mapping the peers' mailboxes failed on rank(s) " +
+                               ", ".join(f"{i}: {w}" for i, (r, w) in enumerate(status) if r != N.OK))
         self.max_bytes = int(N.lib.dx_comm_max_bytes())
-        dist.barrier(group=group)  # nobody publishes into a mailbox that a peer has not mapped yet
+        # the second exchange also guarantees that nobody publishes into a mailbox a peer has not mapped yet
 
     def fits(self, t: torch.Tensor) -> bool:
         return t.is_cuda and t.is_contiguous() and t.dtype != torch.bool and t.numel() * t.element_size() <= self.max_bytes

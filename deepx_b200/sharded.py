@@ -87,7 +87,14 @@ class ShardedOps:
         self.peer = None
         if peer_combine and self.world > 1 and torch.cuda.is_available():
             from .comm import PeerComm
-            self.peer = PeerComm(group)
+            try:
+                self.peer = PeerComm(group)  # raises on every rank or on none
+            except RuntimeError as e:
+                # e.g. CUDA IPC not permitted in this container: the library all-reduce does the combine
+                import sys
+                if self.rank == 0:
+                    print(f"deepx_b200.sharded: peer-memory combine unavailable ({e}); using the group's all-reduce", file=sys.stderr)
+                self.peer = None
 
     def __getattr__(self, name):
         return getattr(self.tf, name)
