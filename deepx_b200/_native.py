@@ -61,6 +61,7 @@ SIGNATURES = {
     "dx_comm_allreduce": (_i, [_vp, _i, _i, _vp, _i64, _vp]),
     "dx_comm_status": (_i, [_vp, _vp]),
     "dx_comm_destroy": (None, [_vp]),
+    "dx_reduce_allreduce": (_i, [_vp, _i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp, _sz, _vp]),
     "dx_comm_emulate": (_vp, [_i, _i]),
     "dx_comm_emulated_allreduce": (_i, [_vp, _i, _i, _pvp, _i, _i64, _vp]),
     "dx_rmsnorm": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _d, _d, _vp]),

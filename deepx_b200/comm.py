@@ -74,6 +74,12 @@ class PeerComm:
             N.check(N.lib.dx_comm_allreduce(self._h, OPS[op], _dtype_code(t), t.data_ptr(), t.numel(), st))
         return t
 
+    def reduce_allreduce(self, op: str, A: torch.Tensor, dims, keepdims: bool, B: torch.Tensor) -> None:
+        """sum / prod / reducemax / reducemin of this rank's block into B, combined over the ranks; where
+        the local reduction ends in a one-CTA finish step, that kernel also does the exchange."""
+        from . import tensorfunc as TF
+        TF._reduce(OPS[op], A, dims, keepdims, B, comm_handle=self._h)
+
     def set_timeout_ms(self, ms: int) -> None:
         N.check(N.lib.dx_comm_set_timeout_ms(self._h, ms))
 

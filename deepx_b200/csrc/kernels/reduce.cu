@@ -26,6 +26,7 @@
 #include <mutex>
 #include <vector>
 
+#include "comm.cuh"
 #include "common.cuh"
 #include "reduce_ops.cuh"
 
@@ -289,6 +290,49 @@ __global__ void __launch_bounds__(RB) cols_finish_kernel(const acc_t<T> *__restr
     out[o] = narrow<T>(r);
 }
 
+// ---- the finish step and the cross-GPU exchange in one kernel ------------------------------------
+// When a reduction crosses the axis the tensor is sharded along, the per-rank result is a partial
+// that has to be combined over the ranks.  If the local reduction ends in a finish step that one CTA
+// can do (a handful of outputs: the global sum of the sharded chain is one), that CTA goes straight
+// on to the peer exchange (comm.cuh): combine this rank's partials, store the result into every
+// peer's mailbox, wait for theirs, combine in rank order, write `out`.  One launch is both the tail
+// of the reduction and the all-reduce.
+static_assert(RB == COMM_THREADS, "the exchange is written for the reduce kernels' CTA size");
+struct PeerTail {
+    Peers peers;
+    int rank;
+    long long wait_cycles;
+};
+template <int OP, typename T>
+__global__ void __launch_bounds__(RB) rows_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, uint32_t nout, uint32_t split,
+                                                              PeerTail tail) {
+    using A = acc_t<T>;
+    const uint32_t o = threadIdx.x >> 5;  // one CTA, one warp per output
+    const int lane = threadIdx.x & 31;
+    if (o < nout) {
+        A r = identity<OP, T>();
+        for (uint32_t c = lane; c < split; c += 32) r = combine<OP>(r, partial[size_t(o) * split + c]);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) r = combine<OP>(r, shfl_down(r, d, 32));
+        if (lane == 0) out[o] = narrow<T>(r);
+    }
+    __syncthreads();  // this CTA's own stores to `out` are visible to all its threads
+    exchange_chunk<OP, T>(tail.peers, tail.rank, 0, out, nout, tail.wait_cycles);
+}
+template <int OP, typename T>
+__global__ void __launch_bounds__(RB) cols_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, int64_t nout, uint32_t split,
+                                                              PeerTail tail) {
+    using A = acc_t<T>;
+    const int64_t o = threadIdx.x;  // one CTA, one thread per output
+    if (o < nout) {
+        A r = partial[o];
+        for (uint32_t c = 1; c < split; ++c) r = combine<OP>(r, partial[int64_t(c) * nout + o]);
+        out[o] = narrow<T>(r);
+    }
+    __syncthreads();
+    exchange_chunk<OP, T>(tail.peers, tail.rank, 0, out, nout, tail.wait_cycles);
+}
+
 template <typename T> __global__ void fill_kernel(T *out, int64_t n, T v) {
     int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) out[i] = v;
@@ -480,7 +524,8 @@ int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, in
 }
 
 template <int OP, typename T>
-int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cudaStream_t st) {
+int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cudaStream_t st, const PeerTail *tail = nullptr,
+             bool *exchanged = nullptr) {
     using A = acc_t<T>;
     switch (pl.kind) {
         case PLAN_EMPTY_OUT: return DX_OK;
@@ -543,6 +588,11 @@ int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cud
         if (int e = check_launch("reduce(rows/block)")) return e;
         if (q.rows.split > 1) {
             const unsigned grid = (q.rows.nout + RB / 32 - 1) / (RB / 32);
+            if (tail && grid == 1) {
+                rows_finish_peer_kernel<OP, T><<<1, RB, 0, st>>>(partial, out, q.rows.nout, q.rows.split, *tail);
+                if (exchanged) *exchanged = true;
+                return check_launch("reduce(rows/finish + exchange)");
+            }
             rows_finish_kernel<OP, T><<<grid, RB, 0, st>>>(partial, out, q.rows.nout, q.rows.split);
             return check_launch("reduce(rows/finish)");
         }
@@ -552,6 +602,11 @@ int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cud
     if (int e = check_launch("reduce(cols)")) return e;
     if (q.cols.split > 1) {
         const unsigned grid = (unsigned)((q.cols.nout + RB - 1) / RB);
+        if (tail && grid == 1) {
+            cols_finish_peer_kernel<OP, T><<<1, RB, 0, st>>>(partial, out, q.cols.nout, q.cols.split, *tail);
+            if (exchanged) *exchanged = true;
+            return check_launch("reduce(cols/finish + exchange)");
+        }
         cols_finish_kernel<OP, T><<<grid, RB, 0, st>>>(partial, out, q.cols.nout, q.cols.split);
         return check_launch("reduce(cols/finish)");
     }
@@ -560,12 +615,13 @@ int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cud
 }
 
 template <typename T>
-int run_op(int op, const Plan &pl, const void *a, void *out, void *ws, size_t wsb, cudaStream_t st) {
+int run_op(int op, const Plan &pl, const void *a, void *out, void *ws, size_t wsb, cudaStream_t st, const PeerTail *tail = nullptr,
+           bool *exchanged = nullptr) {
     switch (op) {
-        case DX_SUM: return run_plan<DX_SUM, T>(pl, (const T *)a, (T *)out, ws, wsb, st);
-        case DX_PROD: return run_plan<DX_PROD, T>(pl, (const T *)a, (T *)out, ws, wsb, st);
-        case DX_RMAX: return run_plan<DX_RMAX, T>(pl, (const T *)a, (T *)out, ws, wsb, st);
-        case DX_RMIN: return run_plan<DX_RMIN, T>(pl, (const T *)a, (T *)out, ws, wsb, st);
+        case DX_SUM: return run_plan<DX_SUM, T>(pl, (const T *)a, (T *)out, ws, wsb, st, tail, exchanged);
+        case DX_PROD: return run_plan<DX_PROD, T>(pl, (const T *)a, (T *)out, ws, wsb, st, tail, exchanged);
+        case DX_RMAX: return run_plan<DX_RMAX, T>(pl, (const T *)a, (T *)out, ws, wsb, st, tail, exchanged);
+        case DX_RMIN: return run_plan<DX_RMIN, T>(pl, (const T *)a, (T *)out, ws, wsb, st, tail, exchanged);
         default: return fail(DX_E_ARG, "reduce: unknown op code %d", op);
     }
 }
@@ -604,6 +660,43 @@ extern "C" int dx_reduce(int op, int dtype, const void *a, const int64_t *shape,
         case DX_I8: return run_op<int8_t>(op, pl, a, out, workspace, workspace_bytes, st);
         default: return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
     }
+}
+
+// Local reduction followed by the combine over the ranks of `comm`, result on every rank.  When the
+// local reduction ends in a one-CTA finish step that CTA also does the exchange (one launch less,
+// and the collective is part of the reduce kernel); otherwise the exchange kernel follows on the
+// same stream.  The combined output must fit a mailbox slot (dx_comm_max_bytes).
+extern "C" int dx_reduce_allreduce(dx_comm *comm, int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
+                                   int ndims, void *out, void *workspace, size_t workspace_bytes, void *stream) {
+    cudaStream_t st = as_stream(stream);
+    if (dx_dtype_size(dtype) == 0 || dtype == DX_BOOL)
+        return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
+    PeerTail tail;
+    if (!comm_device_view(comm, &tail.peers, &tail.rank, &tail.wait_cycles))
+        return fail(DX_E_ARG, "reduce+allreduce: the communicator is not connected (or emulates its ranks)");
+    Plan pl;
+    if (int e = make_plan(dtype, shape, ndim, dims, ndims, sm_count(), residency(op, dtype), &pl)) return e;
+    if (pl.nout > 0 && !out) return fail(DX_E_ARG, "reduce: null output");
+    if (pl.nin > 0 && !a) return fail(DX_E_ARG, "reduce: null input");
+    if (a == out && pl.nin > 0 && pl.kind != PLAN_COPY) return fail(DX_E_ALIAS, "reduce: output aliases input");
+    if (size_t(pl.nout) * dx_dtype_size(dtype) > dx_comm_max_bytes())
+        return fail(DX_E_WORKSPACE, "reduce+allreduce: %lld output bytes exceed the mailbox slot; reduce locally and use a library all-reduce",
+                    (long long)(pl.nout * dx_dtype_size(dtype)));
+    bool exchanged = false;
+    int rc;
+    switch (dtype) {
+        case DX_F64: rc = run_op<double>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
+        case DX_F32: rc = run_op<float>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
+        case DX_F16: rc = run_op<f16>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
+        case DX_BF16: rc = run_op<bf16>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
+        case DX_I64: rc = run_op<int64_t>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
+        case DX_I32: rc = run_op<int32_t>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
+        case DX_I16: rc = run_op<int16_t>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
+        case DX_I8: rc = run_op<int8_t>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
+        default: return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
+    }
+    if (rc != DX_OK || exchanged || pl.nout == 0) return rc;
+    return dx_comm_allreduce(comm, op, dtype, out, pl.nout, stream);
 }
 
 // ---- reduce without any device allocation ---------------------------------------------------------

@@ -100,9 +100,13 @@ class ShardedOps:
         return getattr(self.tf, name)
 
     def _reduce(self, op: str, A: torch.Tensor, dims, keepdims: bool, B: torch.Tensor) -> None:
-        getattr(self.tf, op)(A, dims, keepdims, B)
         cd = self.tf.checked_dims(A.shape, dims)
-        if shards_axis0(cd, A.dim()):
+        crosses = shards_axis0(cd, A.dim())
+        if crosses and self.peer is not None and self.world > 1 and self.peer.fits(B):
+            self.peer.reduce_allreduce(op, A, dims, keepdims, B)  # reduce and exchange, fused where the plan allows
+            return
+        getattr(self.tf, op)(A, dims, keepdims, B)
+        if crosses:
             combine_partials(B, op, self.group, self.peer)
 
     def sum(self, A, dims, keepdims, B): self._reduce("sum", A, dims, keepdims, B)  # noqa: A003

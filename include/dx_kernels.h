@@ -208,6 +208,13 @@ int dx_comm_set_timeout_ms(dx_comm *c, int ms);
 int dx_comm_allreduce(dx_comm *c, int op, int dtype, void *buf, int64_t n, void *stream);
 int dx_comm_status(dx_comm *c, void *stream);
 void dx_comm_destroy(dx_comm *c);
+/* dx_reduce on this rank's shard followed by the combine over the ranks, result on every rank.
+ * Where the local reduction ends in a one-CTA finish step (few outputs — the global sum of a sharded
+ * tensor is one) that CTA also performs the exchange, so a single launch is the tail of the
+ * reduction and the all-reduce; otherwise the exchange kernel follows on the same stream.  The
+ * output must fit dx_comm_max_bytes(); workspace as for dx_reduce. */
+int dx_reduce_allreduce(dx_comm *c, int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims, int ndims,
+                        void *out, void *workspace, size_t workspace_bytes, void *stream);
 /* The same protocol with every rank on ONE GPU (all mailboxes local, all ranks' CTAs in one
  * launch, which is the only safe way to run kernels that wait on each other on one device):
  * bufs[r] is rank r's buffer.  Ranks >= active_ranks are left out, so the others' waits expire

@@ -94,3 +94,29 @@ def test_argument_errors():
     assert N.lib.dx_comm_create(3, 2, 0) is None
     assert N.lib.dx_comm_emulate(0, 0) is None
     assert N.lib.dx_comm_emulate(99, 0) is None
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "int32"])
+def test_reduce_with_fused_exchange_on_one_rank(dtype):
+    """A world of one: the reduce kernels that finish with the exchange run the whole protocol against
+    their own mailbox, so the result must equal the plain reduction (every plan shape: one-CTA finish
+    fused, many outputs followed by the exchange kernel, no finish step at all)."""
+    from deepx_b200 import _native as N
+    from deepx_b200 import tensorfunc as TF
+    h = N.lib.dx_comm_create(0, 1, 0)
+    assert h
+    rng = np.random.default_rng(seed_of("fusedcomm", dtype))
+    for shape, dims in [((512, 4096), [0, 1]), ((300, 1000), [0]), ((64, 200000), [0, 1]), ((8, 64, 4096), [0, 2]), ((5, 7), [0]),
+                        ((4096, 8), [0]), ((3, 100000), [1])]:
+        a = make(rng, dtype, shape, 0.0, 1.0)
+        A = to_gpu(a)
+        cd = TF.checked_dims(A.shape, dims)
+        oshape = TF.reduced_shape(A.shape, cd, False)
+        for op, code in (("sum", N.SUM), ("reducemax", N.RMAX)):
+            plain = torch.empty(oshape, dtype=A.dtype, device=A.device)
+            fused = torch.empty(oshape, dtype=A.dtype, device=A.device)
+            getattr(TF, op)(A, dims, False, plain)
+            TF._reduce(code, A, dims, False, fused, comm_handle=h)
+            N.check(N.lib.dx_comm_status(h, None))
+            assert np.array_equal(to_np(plain).view(np.uint8), to_np(fused).view(np.uint8)), (dtype, shape, dims, op)
+    N.lib.dx_comm_destroy(h)

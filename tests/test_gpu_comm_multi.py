@@ -55,6 +55,15 @@ WORKER = textwrap.dedent("""
     ops.peer.status()
     assert abs(s.item() - x.double().sum().item()) <= 1e-5 * x.double().abs().sum().item()
     assert torch.equal(m.cpu(), x.max(0).values)
+    # a block big enough that the local sum is split over CTAs: its one-CTA finish kernel does the exchange itself
+    big = torch.from_numpy(np.random.default_rng(6).uniform(-1, 1, (256 * world, 8192)).astype(np.float32))
+    mine = big[rank * 256:(rank + 1) * 256].cuda().contiguous()
+    ops.sum(mine, [0, 1], False, s)
+    ops.peer.status()
+    assert abs(s.item() - big.double().sum().item()) <= 1e-5 * big.double().abs().sum().item()
+    every = [None] * world
+    dist.all_gather_object(every, float(s.item()))
+    assert len(set(every)) == 1   # identical bits on every rank
     dist.barrier()
     dist.destroy_process_group()
     print("rank", rank, "ok")
