@@ -1429,6 +1429,9 @@ int launch_tf32x3(const float *A, const float *B, float *C, int64_t batch, int64
 }  // namespace
 }  // namespace dx
 
+namespace dx {
+int matmul_skinny(int dtype, const void *A, const void *B, void *C, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st);
+}
 using namespace dx;
 
 // Reads and clears the status word the tensor-core kernel writes when a bounded wait expires.
@@ -1459,6 +1462,14 @@ extern "C" int dx_matmul(int dtype, const void *A, const void *B, void *C, int64
     }
     if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return fail(DX_E_SHAPE, "matmul: extent too large");
     if (K == 0) return dx_fill(dtype, C, 0.0, 0, batch * M * N, stream);
+    if (M <= 16) {
+        // a handful of rows: reading B once is all the work — the streaming kernel (DX_GEMM_SKINNY=0 turns it off)
+        static const bool skinny_on = [] { const char *e = std::getenv("DX_GEMM_SKINNY"); return !(e && e[0] == '0'); }();
+        if (skinny_on) {
+            const int rc = matmul_skinny(dtype, A, B, C, batch, M, N, K, st);
+            if (rc != DX_E_UNSUPPORTED) return rc;
+        }
+    }
     switch (dtype) {
         case DX_BF16:
         case DX_F16: {

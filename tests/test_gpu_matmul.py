@@ -221,6 +221,40 @@ def test_matmul_fp32_simt_path_is_tighter(mods, monkeypatch):
     assert (np.abs(got - a64 @ b64) <= 4e-6 * (np.abs(a64) @ np.abs(b64))).all()
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16", "float32"])
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8, 9, 16])
+def test_matmul_few_rows_streaming_kernel(mods, dtype, m, monkeypatch):
+    """Few rows (a decoding step): the weight-streaming kernel, forced here for every M <= 16 — K slices
+    across a cluster, every N and K raggedness, batches; same tolerances as the tile kernels."""
+    TF, O, N = mods
+    monkeypatch.setenv("DX_GEMM_SKINNY_ROWS", "16")
+    rng = np.random.default_rng(seed_of("skinny", dtype, m))
+    for Nn, K in [(8, 8), (264, 100), (4104, 4096), (1000, 5000), (16384, 72), (256, 20000)]:
+        a = make(rng, dtype, (m, K), -1.0, 1.0)
+        b = make(rng, dtype, (K, Nn), -1.0, 1.0)
+        check(TF, N, a, b, dtype, f"matmul skinny<{dtype}> {(m, Nn, K)}")
+    a3 = make(rng, dtype, (3, m, 520), -1.0, 1.0)
+    b3 = make(rng, dtype, (3, 520, 136), -1.0, 1.0)
+    check(TF, N, a3, b3, dtype, f"matmul skinny<{dtype}> batched")
+
+
+def test_matmul_few_rows_is_deterministic_and_matches_the_tile_kernel(mods, monkeypatch):
+    TF, O, N = mods
+    rng = np.random.default_rng(12)
+    a = make(rng, "bfloat16", (4, 4096), -1.0, 1.0)
+    b = make(rng, "bfloat16", (4096, 4096), -1.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    outs = []
+    for _ in range(3):
+        Cc = torch.empty((4, 4096), dtype=torch.bfloat16, device="cuda:0")
+        TF.matmul(A, B, Cc)
+        outs.append(to_np(Cc).view(np.uint16).copy())
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    got = to_np(Cc).astype(np.float64)
+    assert np.abs(got - ref).max() <= 1e-2 * np.abs(ref).max()
+
+
 def test_matmul_golden_arange(mods):
     """arange [2,3,4] x [2,4,5]: the worked example in executor/op-ompsimd/test/tensorfunc/4_tensor_matmul.cpp:22-35."""
     TF, O, N = mods
