@@ -602,6 +602,196 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     }
 }
 
+// ---- few rows of A (M <= 128): one row of tiles, split along K across a cluster ---------------------
+// With at most one row of tiles the persistent kernels above put ceil(N/256) CTAs on 148 SMs and are
+// bound by how fast so few SMs can pull B out of HBM.  Here a tile is 128 x 64 and the K range of a
+// tile is divided among the CS <= 8 CTAs of a cluster: N/64 x CS CTAs, each streaming its own slab
+// of B through a 6-stage TMA ring into tcgen05 MMAs (M128 N64 K16; rows beyond M are TMA zero fill
+// and cost no HBM traffic).  Every CTA leaves its 128 x 64 fp32 partial in its own shared memory
+// (over the drained ring); after a cluster barrier every CTA adds, for its share of the tile's columns,
+// the partials of all ranks in rank order through distributed shared memory and writes those columns of
+// the M live rows.  No workspace, no atomics: same bits every run.
+constexpr int S_BN = 64;
+constexpr int S_STAGES = 4;  // 96 KiB: two CTAs per SM
+constexpr int S_STAGE_BYTES = A_STAGE_BYTES + B_BOX_BYTES;  // 16 KiB of A + 8 KiB of B
+constexpr int S_PARTIAL_BYTES = BM * S_BN * 4;              // 32 KiB, reuses the ring after the main loop
+constexpr int S_SMEM_BYTES = S_STAGES * S_STAGE_BYTES + 1024 + 256;
+constexpr int S_TMEM_COLS = 64;
+static_assert(S_PARTIAL_BYTES <= S_STAGES * S_STAGE_BYTES, "partial tile must fit in the ring");
+
+__host__ __device__ constexpr uint32_t make_idesc_n(int ab_format, int n) {
+    return (1u << 4) | (uint32_t(ab_format) << 7) | (uint32_t(ab_format) << 10) | (0u << 15) | (1u << 16) |
+           (uint32_t(n >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+}
+struct SplitKParams {
+    int M, N, K, batch;
+    int tiles_n, k_blocks, kb_per_rank;
+    int *status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tcgen05_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, T *__restrict__ C,
+                               SplitKParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + S_STAGES * S_STAGE_BYTES;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (S_STAGES + s); };
+    const uint32_t tfull_bar = bars + 8u * (2 * S_STAGES);
+    constexpr int SLOT_OFF = 8 * (2 * S_STAGES + 1);
+    const uint32_t tmem_slot = bars + SLOT_OFF;
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + S_STAGES * S_STAGE_BYTES + SLOT_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + S_STAGES * S_STAGE_BYTES + SLOT_OFF + 8);
+    float *partial = reinterpret_cast<float *>(gen_base);  // [BM][S_BN], valid after the main loop
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    uint32_t cs;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(cs));
+    const uint32_t rank = cluster_ctarank();
+    const int tn = blockIdx.x / cs;
+    const int b = blockIdx.y;
+    const int kb0 = int(rank) * p.kb_per_rank;
+    const int kb1 = min(p.k_blocks, kb0 + p.kb_per_rank);
+    const int nkb = max(kb1 - kb0, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, S_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_EMPTY); }
+                    break;
+                }
+                const uint32_t sa = smem_base + stage * S_STAGE_BYTES;
+                mbar_expect_tx(full_bar(stage), S_STAGE_BYTES);
+                tma_load_3d(sa, &tmap_a, full_bar(stage), kb * BK, 0, b);
+                tma_load_3d(sa + A_STAGE_BYTES, &tmap_b, full_bar(stage), tn * S_BN, kb * BK, b);
+                if (++stage == S_STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000ll) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && nkb > 0) {
+            constexpr uint32_t idesc = make_idesc_n(std::is_same<T, bf16>::value ? 1 : 0, S_BN);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_FULL); }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_base + stage * S_STAGE_BYTES;
+                const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t adesc = make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+                    const uint64_t bdesc = make_smem_desc(sb + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
+                    umma_f16(tmem_base, adesc, bdesc, idesc, (kb | k) != 0);
+                }
+                umma_commit(empty_bar(stage));
+                if (++stage == S_STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (ok) umma_commit(tfull_bar);
+        }
+    } else {
+        // epilogue warps: TMEM lane quarter warp % 4; only rows < M matter
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        bool have = false;
+        uint32_t r0[32], r1[32];
+        if (nkb > 0) {
+            if (mbar_wait(tfull_bar, 0, abort_flag)) {
+                tc_fence_after();
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + 0, r0);
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + 32, r1);
+                tmem_ld_wait();
+                have = true;
+            } else if (lane == 0 && !*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL);
+            }
+        }
+        // the ring is drained (every MMA that read it has completed): the partial tile goes on top of it
+        // column-major [S_BN][BM]: the 32 lanes of a warp (32 rows) write neighbouring words
+        if (row < p.M) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                partial[j * BM + row] = have ? __uint_as_float(r0[j]) : 0.f;
+                partial[(32 + j) * BM + row] = have ? __uint_as_float(r1[j]) : 0.f;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // every CTA's partial is in place
+    {
+        // Reduce-scatter across the cluster: rank r sums columns [r, r+1) * S_BN / cs of the tile over all
+        // ranks (always in rank order 0..cs-1, whoever does the adding) with 16-byte loads from the peers'
+        // shared memory, and writes those columns of C.  Spreading the adds over the cluster matters:
+        // 4-byte remote loads by one leader alone cost more than the whole main loop.
+        const uint32_t pbase = smem_u32(partial);
+        uint32_t peer[8];
+#pragma unroll
+        for (uint32_t r = 0; r < 8; ++r) peer[r] = r < cs ? mapa_u32(pbase, r) : 0u;
+        const int cols_per = S_BN / int(cs);
+        const int col0 = int(rank) * cols_per;
+        const int quads = (p.M + 3) / 4;  // groups of four rows (rows are contiguous in the column-major partial)
+        T *cbase = C + size_t(b) * p.M * p.N;
+        for (int u = threadIdx.x; u < cols_per * quads; u += NUM_THREADS) {
+            const int qd = u / cols_per, col = col0 + (u - qd * cols_per);  // neighbouring threads: neighbouring columns of C
+            const uint32_t off = uint32_t(col * BM + qd * 4) * 4u;
+            float4 v[8];
+#pragma unroll
+            for (uint32_t r = 0; r < 8; ++r) {
+                if (r < cs) asm("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[r].x), "=f"(v[r].y), "=f"(v[r].z), "=f"(v[r].w) : "r"(peer[r] + off));
+                else v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float4 acc = v[0];
+#pragma unroll
+            for (uint32_t r = 1; r < 8; ++r) { acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w; }
+            const int gcol = tn * S_BN + col;
+            if (gcol < p.N) {
+                const float out4[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (qd * 4 + j < p.M) cbase[size_t(qd * 4 + j) * p.N + gcol] = from_compute<T>(out4[j]);
+            }
+        }
+    }
+    cluster_sync_all();  // nobody leaves while a peer may still read its shared memory
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, S_TMEM_COLS);
+    }
+}
+
 // ---- float32 on the tensor cores: three TF32 products per fp32 product ------------------------------
 // kind::tf32 reads 32-bit words and keeps 10 mantissa bits, which alone misses the 1e-5 bound.  Each
 // operand is therefore split IN SHARED MEMORY into hi = round-to-tf32(x) and lo = x − hi (exact in
@@ -1322,6 +1512,65 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
     return check_launch("matmul(tcgen05)");
 }
 
+// Few rows: the split-K cluster kernel.  DX_E_UNSUPPORTED = not a shape for it.
+template <typename T> int launch_splitk(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+    if (M > BM || batch > 65535) return DX_E_UNSUPPORTED;
+    const int64_t tiles_n = (N + S_BN - 1) / S_BN;
+    const int64_t k_blocks = (K + BK - 1) / BK;
+    // worth it only where the persistent kernels would leave most SMs idle
+    const int64_t big_tiles = ((N + BN - 1) / BN) * batch;
+    if (big_tiles * 2 > sm_count() || k_blocks < 8 || tiles_n * 8 >= (1ll << 31)) return DX_E_UNSUPPORTED;
+    int cs = 1;
+    while (cs < 8 && tiles_n * batch * cs < 2 * sm_count() && k_blocks / (cs * 2) >= 4) cs *= 2;
+    if (cs < 4) return DX_E_UNSUPPORTED;  // measured: with fewer than four K slices per tile the persistent kernels are as fast
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return fail(DX_E_CUDA, "matmul: device index %d out of range", dev);
+    int *status;
+    {
+        std::lock_guard<std::mutex> lk(g_setup_mu);
+        if (!g_status_ptr[dev]) {
+            void *sym = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&sym, g_gemm_status);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_status_ptr[dev] = static_cast<int *>(sym);
+        }
+        status = g_status_ptr[dev];
+        static bool attr_set[64][2] = {};
+        const int ti = std::is_same<T, bf16>::value ? 0 : 1;
+        if (!attr_set[dev][ti]) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_splitk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, S_SMEM_BYTES);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            attr_set[dev][ti] = true;
+        }
+    }
+    const CUtensorMapDataType dt = std::is_same<T, bf16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap ma, mb;
+    if (int e = make_map(&ma, dt, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, BK, BM)) return e;
+    if (int e = make_map(&mb, dt, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, B_BOX_N, BK)) return e;
+    SplitKParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.tiles_n = (int)tiles_n;
+    p.k_blocks = (int)k_blocks;
+    p.kb_per_rank = (int)((k_blocks + cs - 1) / cs);
+    p.status = status;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles_n * cs), (unsigned)batch, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = S_SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_splitk_kernel<T>, ma, mb, C, p);
+    if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 split-K): %s", cudaGetErrorString(e));
+    return check_launch("matmul(tcgen05 split-K)");
+}
+
 // float32 through the tensor cores (three TF32 products per product).
 bool g_tf32_attr[64] = {};
 int g_tf32_pair_slots[64] = {};
@@ -1475,6 +1724,14 @@ extern "C" int dx_matmul(int dtype, const void *A, const void *B, void *C, int64
         case DX_F16: {
             // TMA needs 16-byte aligned bases and row pitches; anything else takes the SIMT path.
             const bool tma_ok = (K % 8 == 0) && (N % 8 == 0) && aligned_to(A, 16) && aligned_to(B, 16);
+            if (tma_ok && M <= BM) {
+                static const bool splitk_on = [] { const char *e = std::getenv("DX_GEMM_SPLITK"); return !(e && e[0] == '0'); }();
+                if (splitk_on) {
+                    const int rc = dtype == DX_BF16 ? launch_splitk<bf16>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, st)
+                                                    : launch_splitk<f16>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);
+                    if (rc != DX_E_UNSUPPORTED) return rc;
+                }
+            }
             if (tma_ok) {
                 return dtype == DX_BF16 ? launch_tcgen05<bf16>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, st)
                                         : launch_tcgen05<f16>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);

@@ -255,6 +255,37 @@ def test_matmul_few_rows_is_deterministic_and_matches_the_tile_kernel(mods, monk
     assert np.abs(got - ref).max() <= 1e-2 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("m", [3, 16, 17, 64, 100, 128])
+def test_matmul_one_tile_row_split_k(mods, dtype, m):
+    """Up to 128 rows and few columns of tiles: the split-K cluster kernel (128 x 64 tiles, K divided over the
+    CTAs of a cluster, partials combined through distributed shared memory)."""
+    TF, O, N = mods
+    rng = np.random.default_rng(seed_of("splitk", dtype, m))
+    for Nn, K in [(8, 512), (264, 520), (4096, 4096), (4104, 1000), (1000, 11008), (64, 8192), (11008, 4096)]:
+        a = make(rng, dtype, (m, K), -1.0, 1.0)
+        b = make(rng, dtype, (K, Nn), -1.0, 1.0)
+        check(TF, N, a, b, dtype, f"matmul split-K<{dtype}> {(m, Nn, K)}")
+    a3 = make(rng, dtype, (3, m, 1032), -1.0, 1.0)
+    b3 = make(rng, dtype, (3, 1032, 136), -1.0, 1.0)
+    check(TF, N, a3, b3, dtype, f"matmul split-K<{dtype}> batched")
+
+
+def test_matmul_split_k_is_deterministic(mods):
+    TF, O, N = mods
+    rng = np.random.default_rng(13)
+    a = make(rng, "bfloat16", (32, 4096), -1.0, 1.0)
+    b = make(rng, "bfloat16", (4096, 4096), -1.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    outs = []
+    for _ in range(3):
+        Cc = torch.empty((32, 4096), dtype=torch.bfloat16, device="cuda:0")
+        TF.matmul(A, B, Cc)
+        N.check(N.lib.dx_matmul_status(None))
+        outs.append(to_np(Cc).view(np.uint16).copy())
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+
+
 def test_matmul_golden_arange(mods):
     """arange [2,3,4] x [2,4,5]: the worked example in executor/op-ompsimd/test/tensorfunc/4_tensor_matmul.cpp:22-35."""
     TF, O, N = mods
