@@ -166,6 +166,49 @@ def run_reference(args) -> None:
     }), flush=True)
 
 
+def udp_round_trip_us(ir_line: str, trips: int = 2000):
+    """One IR line as one datagram to the executor process on loopback, reply awaited — what the
+    reference's Python front end pays per op (front/py/deepx/scheduler/client/udpconn.py:31-44 blocks
+    on the reply).  None when the process cannot be started; never raises."""
+    import socket
+    import subprocess
+    proc = None
+    try:
+        from deepx_b200.executor import BIN_PATH
+        port = 21000 + os.getpid() % 20000
+        env = dict(os.environ, DEEPX_PORT=str(port), DEEPX_POOL_BYTES=str(256 << 20))
+        proc = subprocess.Popen([str(BIN_PATH)], env=env, stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        if "listening" not in proc.stdout.readline():
+            return None
+        sock = socket.socket(socket.AF_INET, socket.SOCK_DGRAM)
+        sock.settimeout(20)
+
+        def send(line):
+            sock.sendto(line.encode(), ("127.0.0.1", port))
+            return sock.recvfrom(65536)[0]
+
+        if b" ok" not in send("newtensor(vector<int32>:[16])->(tensor<float32>:tiny) // id=1"):
+            return None
+        payload = ir_line.encode()
+        for _ in range(200):
+            send(ir_line)
+        t0 = time.perf_counter()
+        for _ in range(trips):
+            sock.sendto(payload, ("127.0.0.1", port))
+            reply = sock.recvfrom(65536)[0]
+        dt = time.perf_counter() - t0
+        return dt / trips * 1e6 if b" ok" in reply else None
+    except Exception:
+        return None
+    finally:
+        if proc is not None:
+            proc.terminate()
+            try:
+                proc.communicate(timeout=20)
+            except Exception:
+                proc.kill()
+
+
 def cpu_baseline_leg() -> dict:
     """Bounded CPU baseline beside the GPU number (rank 0, N=1): ~10 s of oracle work."""
     import numpy as np
@@ -664,11 +707,11 @@ def run_ours(args) -> None:
     if abs(float(hs_np[0]) - got_sum) > 1e-4 * abs(got_sum) + 1e-3 or not np.array_equal(hm_np[:ref_rows], got_m):
         raise SystemExit("bench: the executor path and the direct path disagree — refusing to report a number")
     executor_us = compiled_us = None
+    tiny_ir = "addscalar(tensor<float32>:tiny, var<float32>:1)->(tensor<float32>:tiny) // author=miaobyte id=7"
     if world == 1:
         # what one IR line costs on the host side: parse, registry lookup, tensor lookup, one launch of a 16-element op
         ex.run("newtensor(vector<int32>:[16])->(tensor<float32>:tiny)")
         ex.run("constant(var<float32>:1)->(tensor<float32>:tiny)")
-        tiny_ir = "addscalar(tensor<float32>:tiny, var<float32>:1)->(tensor<float32>:tiny) // author=miaobyte id=7"
         for _ in range(100):
             ex.run(tiny_ir)
         ex.sync()
@@ -689,6 +732,7 @@ def run_ours(args) -> None:
         compiled_us = (time.perf_counter() - t0) / (50 * 200) * 1e6
         prog.free()
     ex.close()
+    udp_us = udp_round_trip_us(tiny_ir) if world == 1 else None
     e2e_value = total_bytes / e2e_ms / 1e6
 
     line = {
@@ -710,8 +754,10 @@ def run_ours(args) -> None:
                 "path": "deepxIR text -> libdeepx_exec.so (dx_exec_upload / dx_exec_run / dx_exec_download), pinned host buffers"},
         "executor": {"us_per_ir_line": None if executor_us is None else round(executor_us, 2),
                      "us_per_ir_line_compiled": None if compiled_us is None else round(compiled_us, 2),
+                     "us_per_udp_round_trip": None if udp_us is None else round(udp_us, 2),
                      "what": "3000 addscalar lines on a 16-element tensor through dx_exec_run from Python (parse + dispatch + launch); "
-                             "compiled: the same line 200x as one program captured into a CUDA graph (dx_exec_compile), 50 replays"},
+                             "compiled: the same line 200x as one program captured into a CUDA graph (dx_exec_compile), 50 replays; "
+                             "udp: the same line as one datagram to the deepx-op-b200 process on loopback, reply awaited, 2000 times"},
         "gpu_launches": int(launches),
         "clocks": clocks,
         "global_sum": got_sum,

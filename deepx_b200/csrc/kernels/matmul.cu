@@ -148,9 +148,9 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 // Instruction descriptor (32-bit) for kind::f16: D format [4,6) 1 = f32; A format [7,10), B format
 // [10,13) (0 = f16, 1 = bf16); A major bit 15, B major bit 16 (0 = K-major, 1 = MN-major);
 // N>>3 in [17,23); M>>4 in [24,29).
-__host__ __device__ constexpr uint32_t make_idesc(int ab_format) {
+__host__ __device__ constexpr uint32_t make_idesc_n(int ab_format, int n) {
     return (1u << 4) | (uint32_t(ab_format) << 7) | (uint32_t(ab_format) << 10) | (0u << 15) | (1u << 16) |
-           (uint32_t(BN >> 3) << 17) | (uint32_t(BM >> 4) << 24);
+           (uint32_t(n >> 3) << 17) | (uint32_t(BM >> 4) << 24);
 }
 
 // Tile order.  The CTAs that run at the same time take consecutive tile numbers, so the order decides
@@ -170,12 +170,19 @@ __device__ __forceinline__ void grouped_tile_coords(int tile, int tiles_m, int t
     tm = first_m + (r - tn * gm);
 }
 
-struct GemmParams {
-    int M, N, K, batch;
-    int tiles_m, tiles_n, num_tiles, k_blocks;
-    int raster;  // rows of tiles per raster group
-    int *status;
-};
+// ---- the way out: TMEM → registers → C ----------------------------------------------------------
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int PENDING> __device__ __forceinline__ void bulk_wait_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2<bf16>(float lo, float hi) {
@@ -187,28 +194,129 @@ template <> __device__ __forceinline__ uint32_t pack2<f16>(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
+constexpr int EPI_BOX_ROWS = 32, EPI_BOX_COLS = 64;                // one TMA store: a warp's 32 rows × 64 columns
+constexpr int EPI_BUF_BYTES = EPI_BOX_ROWS * EPI_BOX_COLS * 2;    // 4 KiB, 128 bytes per row
+constexpr int EPI_WARP_BYTES = 2 * EPI_BUF_BYTES;                 // double-buffered per warp
+constexpr int EPI_BYTES = 4 * EPI_WARP_BYTES;                     // 32 KiB for the four epilogue warps
+
+// One epilogue warp drains its 32 rows of a finished accumulator (`width` columns at `tmem_acc`),
+// rounding fp32 to the 16-bit type once.  With `by_tma` it stages 32 rows × 64 columns at a time in
+// its own shared-memory buffer — rows of 128 bytes, 16-byte chunks XOR-swizzled by row so that the
+// warp's writes spread over all banks and match the store's 128-byte swizzle — and one lane hands
+// the block to a TMA store: whole 128-byte lines leave the SM asynchronously, rows and columns past
+// the edge of C are clipped by the copy engine.  Two buffers alternate; a buffer is rewritten only
+// after the store issued from it two blocks ago has finished reading.  Without `by_tma` (C's base or
+// pitch is not a multiple of 16 bytes) each lane stores its own row from registers.
 template <typename T>
+__device__ __forceinline__ void drain_accumulator(uint32_t tmem_acc, int width, T *C, const CUtensorMap *tmap_c, bool by_tma,
+                                                  uint32_t stage_smem, int &buf, int M, int N, int b, int row0, int col0,
+                                                  int lane) {
+    const int row = row0 + lane;
+    const bool vec_ok = (N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+#pragma unroll 1
+    for (int c0 = 0; c0 < width; c0 += EPI_BOX_COLS) {
+        uint32_t r[2][32];
+        tmem_ld_32x32b_x32(tmem_acc + c0, r[0]);
+        tmem_ld_32x32b_x32(tmem_acc + c0 + 32, r[1]);
+        tmem_ld_wait();
+        const int col = col0 + c0;
+        if (row0 >= M || col >= N) continue;  // the whole block lies outside C (same answer in every lane)
+        if (by_tma) {
+            if (lane == 0) bulk_wait_read<1>();
+            __syncwarp();
+            const uint32_t src = stage_smem + buf * EPI_BUF_BYTES;
+            const uint32_t dst = src + lane * 128;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int v = 0; v < 4; ++v) {
+                    const int chunk = h * 4 + v;
+                    st_shared_v4(dst + ((chunk ^ (lane & 7)) << 4),
+                                 pack2<T>(__uint_as_float(r[h][8 * v + 0]), __uint_as_float(r[h][8 * v + 1])),
+                                 pack2<T>(__uint_as_float(r[h][8 * v + 2]), __uint_as_float(r[h][8 * v + 3])),
+                                 pack2<T>(__uint_as_float(r[h][8 * v + 4]), __uint_as_float(r[h][8 * v + 5])),
+                                 pack2<T>(__uint_as_float(r[h][8 * v + 6]), __uint_as_float(r[h][8 * v + 7])));
+                }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, read next by the copy engine
+            __syncwarp();
+            if (lane == 0) {
+                tma_store_3d(tmap_c, src, col, row0, b);
+                bulk_commit();
+            }
+            buf ^= 1;
+        } else if (row < M) {
+            T *crow = C + (size_t(b) * M + row) * N;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int hc = col + 32 * h;
+                if (vec_ok && hc + 32 <= N) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint4 o;
+                        o.x = pack2<T>(__uint_as_float(r[h][8 * v + 0]), __uint_as_float(r[h][8 * v + 1]));
+                        o.y = pack2<T>(__uint_as_float(r[h][8 * v + 2]), __uint_as_float(r[h][8 * v + 3]));
+                        o.z = pack2<T>(__uint_as_float(r[h][8 * v + 4]), __uint_as_float(r[h][8 * v + 5]));
+                        o.w = pack2<T>(__uint_as_float(r[h][8 * v + 6]), __uint_as_float(r[h][8 * v + 7]));
+                        *reinterpret_cast<uint4 *>(crow + hc + 8 * v) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (hc + j < N) crow[hc + j] = from_compute<T>(__uint_as_float(r[h][j]));
+                }
+            }
+        }
+    }
+}
+
+// Tile width BN_ (256, 128 or 64 columns) is chosen by the host from how many tiles each width
+// gives: a narrow tile has a worse ratio of shared-memory reads to math, but 128 × 256 tiles of a
+// matrix with few rows leave most SMs without work.  Narrower tiles take a deeper ring.
+template <int BN_> struct TileCfg {
+    static constexpr int B_STAGE = B_BOX_BYTES * (BN_ / B_BOX_N);
+    static constexpr int STAGE = A_STAGE_BYTES + B_STAGE;
+    static constexpr int NSTAGES = (192 * 1024) / STAGE;  // 4, 6, 8
+    static constexpr int RING = NSTAGES * STAGE;
+    static constexpr int SMEM = RING + EPI_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+    static constexpr int TMEM = ACC_STAGES * BN_;
+};
+static_assert(TileCfg<256>::SMEM <= 227 * 1024 && TileCfg<128>::SMEM <= 227 * 1024 && TileCfg<64>::SMEM <= 227 * 1024, "shared memory");
+
+struct GemmParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, num_tiles, k_blocks;
+    int raster;   // rows of tiles per raster group
+    int c_by_tma; // C leaves through TMA stores (its base and pitch are multiples of 16 bytes)
+    int *status;
+};
+
+template <typename T, int BN_>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, T *__restrict__ C,
-                        GemmParams p) {
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                        const __grid_constant__ CUtensorMap tmap_c, T *__restrict__ C, GemmParams p) {
+    using Cfg = TileCfg<BN_>;
+    constexpr int NS = Cfg::NSTAGES;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle atoms are 1024 bytes: stage bases must be 1024-byte aligned
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = smem_base + STAGES * STAGE_BYTES;
+    const uint32_t epi_smem = smem_base + Cfg::RING;
+    constexpr int BAR_OFF = Cfg::RING + EPI_BYTES;
+    const uint32_t bars = smem_base + BAR_OFF;
     auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-    auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
-    auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + ACC_STAGES + a); };
-    const uint32_t tmem_slot = bars + 8u * (2 * STAGES + 2 * ACC_STAGES);
+    auto empty_bar = [&](int s) { return bars + 8u * (NS + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * NS + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * NS + ACC_STAGES + a); };
+    constexpr int SLOT_OFF = 8 * (2 * NS + 2 * ACC_STAGES);
+    const uint32_t tmem_slot = bars + SLOT_OFF;
     uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 2 * ACC_STAGES));
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + STAGES * STAGE_BYTES + 8 * (2 * STAGES + 2 * ACC_STAGES) + 8);
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + BAR_OFF + SLOT_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + BAR_OFF + SLOT_OFF + 8);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NS; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
@@ -220,8 +328,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        prefetch_tmap(&tmap_c);
     }
-    if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+    if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -242,14 +351,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         ok = false;
                         break;
                     }
-                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint32_t sa = smem_base + stage * Cfg::STAGE;
                     const uint32_t sb = sa + A_STAGE_BYTES;
-                    mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+                    mbar_expect_tx(full_bar(stage), Cfg::STAGE);
                     tma_load_3d(sa, &tmap_a, full_bar(stage), kb * BK, tm * BM, b);
 #pragma unroll
-                    for (int j = 0; j < BN / B_BOX_N; ++j)
-                        tma_load_3d(sb + j * B_BOX_BYTES, &tmap_b, full_bar(stage), tn * BN + j * B_BOX_N, kb * BK, b);
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    for (int j = 0; j < BN_ / B_BOX_N; ++j)
+                        tma_load_3d(sb + j * B_BOX_BYTES, &tmap_b, full_bar(stage), tn * BN_ + j * B_BOX_N, kb * BK, b);
+                    if (++stage == NS) { stage = 0; phase ^= 1; }
                 }
             }
             if (*abort_flag) {
@@ -261,7 +370,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     } else if (warp == 1) {
         // ===== MMA issuer =====
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(std::is_same<T, bf16>::value ? 1 : 0);
+            constexpr uint32_t idesc = make_idesc_n(std::is_same<T, bf16>::value ? 1 : 0, BN_);
             int stage = 0;
             uint32_t phase = 0;
             int acc = 0;
@@ -273,7 +382,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                     break;
                 }
                 tc_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * BN;
+                const uint32_t tmem_d = tmem_base + acc * BN_;
                 for (int kb = 0; kb < p.k_blocks; ++kb) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
                         if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_FULL); }
@@ -281,7 +390,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t sa = smem_base + stage * STAGE_BYTES;
+                    const uint32_t sa = smem_base + stage * Cfg::STAGE;
                     const uint32_t sb = sa + A_STAGE_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -293,7 +402,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                         umma_f16(tmem_d, adesc, bdesc, idesc, (kb | k) != 0);
                     }
                     umma_commit(empty_bar(stage));  // stage reusable once these MMAs have read it
-                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                    if (++stage == NS) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
                 umma_commit(tfull_bar(acc));  // accumulator complete
@@ -305,7 +414,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int q = warp & 3;
         int acc = 0;
         uint32_t acc_phase = 0;
-        const bool vec_ok = (p.N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+        int buf = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
             int b, tm, tn;
             grouped_tile_coords(tile, p.tiles_m, p.tiles_n, p.raster, b, tm, tn);
@@ -314,44 +423,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 break;
             }
             tc_fence_after();
-            const int row = tm * BM + q * 32 + lane;
-            T *crow = C + (size_t(b) * p.M + row) * p.N;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c0, r);
-                tmem_ld_wait();
-                const int col = tn * BN + c0;
-                if (row < p.M) {
-                    if (vec_ok && col + 32 <= p.N) {
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 o;
-                            o.x = pack2<T>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                            o.y = pack2<T>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                            o.z = pack2<T>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                            o.w = pack2<T>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                            *reinterpret_cast<uint4 *>(crow + col + 8 * v) = o;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < p.N) crow[col + j] = from_compute<T>(__uint_as_float(r[j]));
-                    }
-                }
-            }
+            drain_accumulator<T>(tmem_base + (uint32_t(q * 32) << 16) + acc * BN_, BN_, C, &tmap_c, p.c_by_tma != 0,
+                                 epi_smem + q * EPI_WARP_BYTES, buf, p.M, p.N, b, tm * BM + q * 32, tn * BN_, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
             if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
+        if (lane == 0) bulk_wait_read<0>();  // the staging buffers must outlive the stores that read them
     }
     // Teardown: everyone meets, then the allocating warp frees TMEM.
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        tmem_dealloc(tmem_base, Cfg::TMEM);
     }
 }
 
@@ -369,7 +455,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 constexpr int P_STAGES = 6;
 constexpr int P_B_STAGE_BYTES = B_BOX_BYTES * 2;                 // 64 K × 128 N
 constexpr int P_STAGE_BYTES = A_STAGE_BYTES + P_B_STAGE_BYTES;   // 32 KiB
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + EPI_BYTES + 1024 + 256;
 constexpr int PBM = 256;                                         // tile rows per pair
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -425,17 +511,20 @@ __host__ __device__ constexpr uint32_t make_idesc_pair(int ab_format) {
 struct PairParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, num_tiles, k_blocks;  // tiles of 256 × 256
-    int raster;  // rows of tiles per raster group
+    int raster;   // rows of tiles per raster group
+    int c_by_tma; // C leaves through TMA stores
     int *status;
 };
 
 template <typename T>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
     gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                             T *__restrict__ C, PairParams p) {
+                             const __grid_constant__ CUtensorMap tmap_c, T *__restrict__ C, PairParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bars = smem_base + P_STAGES * P_STAGE_BYTES;
+    const uint32_t epi_smem = smem_base + P_STAGES * P_STAGE_BYTES;
+    constexpr int BAR_OFF = P_STAGES * P_STAGE_BYTES + EPI_BYTES;
+    const uint32_t bars = smem_base + BAR_OFF;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (P_STAGES + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * P_STAGES + a); };
@@ -443,8 +532,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     constexpr int SLOT_OFF = 8 * (2 * P_STAGES + 2 * ACC_STAGES);
     const uint32_t tmem_slot = bars + SLOT_OFF;
     uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + P_STAGES * P_STAGE_BYTES + SLOT_OFF);
-    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + P_STAGES * P_STAGE_BYTES + SLOT_OFF + 8);
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + BAR_OFF + SLOT_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + BAR_OFF + SLOT_OFF + 8);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -465,6 +554,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        prefetch_tmap(&tmap_c);
     }
     if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
     tc_fence_before();
@@ -550,7 +640,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int q = warp & 3;
         int acc = 0;
         uint32_t acc_phase = 0;
-        const bool vec_ok = (p.N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
+        int buf = 0;
         for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
             int b, tm, tn;
             tile_coords(tile, b, tm, tn);
@@ -559,37 +649,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 break;
             }
             tc_fence_after();
-            const int row = tm * PBM + int(rank) * BM + q * 32 + lane;
-            T *crow = C + (size_t(b) * p.M + row) * p.N;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c0, r);
-                tmem_ld_wait();
-                const int col = tn * BN + c0;
-                if (row < p.M) {
-                    if (vec_ok && col + 32 <= p.N) {
-#pragma unroll
-                        for (int v = 0; v < 4; ++v) {
-                            uint4 o;
-                            o.x = pack2<T>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
-                            o.y = pack2<T>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
-                            o.z = pack2<T>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
-                            o.w = pack2<T>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
-                            *reinterpret_cast<uint4 *>(crow + col + 8 * v) = o;
-                        }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (col + j < p.N) crow[col + j] = from_compute<T>(__uint_as_float(r[j]));
-                    }
-                }
-            }
+            drain_accumulator<T>(tmem_base + (uint32_t(q * 32) << 16) + acc * BN, BN, C, &tmap_c, p.c_by_tma != 0,
+                                 epi_smem + q * EPI_WARP_BYTES, buf, p.M, p.N, b, tm * PBM + int(rank) * BM + q * 32, tn * BN, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));  // the leader's barrier collects all eight warps
             if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
+        if (lane == 0) bulk_wait_read<0>();  // the staging buffers must outlive the stores that read them
     }
     // Teardown: neither CTA may leave (or free TMEM) while the other can still signal its barriers
     // or read its shared memory, so the whole pair meets first.
@@ -619,10 +686,6 @@ constexpr int S_SMEM_BYTES = S_STAGES * S_STAGE_BYTES + 1024 + 256;
 constexpr int S_TMEM_COLS = 64;
 static_assert(S_PARTIAL_BYTES <= S_STAGES * S_STAGE_BYTES, "partial tile must fit in the ring");
 
-__host__ __device__ constexpr uint32_t make_idesc_n(int ab_format, int n) {
-    return (1u << 4) | (uint32_t(ab_format) << 7) | (uint32_t(ab_format) << 10) | (0u << 15) | (1u << 16) |
-           (uint32_t(n >> 3) << 17) | (uint32_t(BM >> 4) << 24);
-}
 struct SplitKParams {
     int M, N, K, batch;
     int tiles_n, k_blocks, kb_per_rank;
@@ -1437,6 +1500,60 @@ template <typename T> int pair_slots(int dev) {
     return n;
 }
 
+// Persistent single-CTA kernel at tile width BN_.
+template <typename T, int BN_>
+int launch_single(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, T *C, int64_t batch, int64_t M, int64_t N,
+                  int64_t K, bool c_by_tma, int *status, int dev, cudaStream_t st) {
+    using Cfg = TileCfg<BN_>;
+    {
+        static bool attr_set[64] = {};
+        std::lock_guard<std::mutex> lk(g_setup_mu);
+        if (!attr_set[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<T, BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            attr_set[dev] = true;
+        }
+    }
+    GemmParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.tiles_m = (int)((M + BM - 1) / BM);
+    p.tiles_n = (int)((N + BN_ - 1) / BN_);
+    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n * batch;
+    if (tiles >= (1ll << 31)) return fail(DX_E_SHAPE, "matmul: too many tiles");
+    p.num_tiles = (int)tiles;
+    p.k_blocks = (int)((K + BK - 1) / BK);
+    p.status = status;
+    p.raster = raster_group(M, N, K, (int)sizeof(T), p.tiles_m);
+    p.c_by_tma = c_by_tma ? 1 : 0;
+    const int grid = (int)std::min<int64_t>(tiles, sm_count());
+    gemm_tcgen05_kernel<T, BN_><<<grid, NUM_THREADS, Cfg::SMEM, st>>>(ma, mb, mc, C, p);
+    return check_launch("matmul(tcgen05)");
+}
+
+// Tile width for the single-CTA kernel: the width whose waves × time per tile is least.  Per 64-deep
+// K block a 128 × 256 tile keeps the tensor core busy for 512 cycles; narrower tiles are bound by
+// shared-memory reads instead (A is re-read for fewer columns): about 280 and 192 cycles.
+int pick_tile_n(int64_t M, int64_t N, int64_t K, int64_t batch) {
+    static const int forced = [] {
+        const char *e = std::getenv("DX_GEMM_TILE_N");
+        const int v = e ? std::atoi(e) : 0;
+        return (v == 256 || v == 128 || v == 64) ? v : 0;
+    }();
+    if (forced) return forced;
+    const int64_t sms = sm_count(), tiles_m = (M + BM - 1) / BM, k_blocks = (K + BK - 1) / BK;
+    const int widths[3] = {256, 128, 64};
+    const int64_t cycles[3] = {512, 280, 192};
+    int best = 256;
+    int64_t best_cost = -1;
+    for (int i = 0; i < 3; ++i) {
+        const int64_t tiles = tiles_m * ((N + widths[i] - 1) / widths[i]) * batch;
+        const int64_t waves = (tiles + sms - 1) / sms;
+        const int64_t cost = waves * (k_blocks * cycles[i] + 1500);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = widths[i]; }
+    }
+    return best;
+}
+
 template <typename T>
 int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
     int dev = 0;
@@ -1452,17 +1569,19 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
             g_status_ptr[dev] = static_cast<int *>(sym);
         }
         status = g_status_ptr[dev];
-        const int ti = std::is_same<T, bf16>::value ? 0 : 1;
-        if (!g_attr_set[dev][ti]) {
-            cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-            g_attr_set[dev][ti] = true;
-        }
     }
     const CUtensorMapDataType dt = std::is_same<T, bf16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap ma, mb;
+    CUtensorMap ma, mb, mc;
     if (int e = make_map(&ma, dt, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, BK, BM)) return e;
     if (int e = make_map(&mb, dt, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, B_BOX_N, BK)) return e;
+    // C through TMA stores when its base is 16-byte aligned (its pitch is: N % 8 == 0 on this path); DX_GEMM_TMA_STORE=0 turns it off
+    static const bool tma_store_on = [] { const char *e = std::getenv("DX_GEMM_TMA_STORE"); return !(e && e[0] == '0'); }();
+    const bool c_by_tma = tma_store_on && aligned_to(C, 16);
+    if (c_by_tma) {
+        if (int e = make_map(&mc, dt, C, (uint64_t)N, (uint64_t)M, (uint64_t)batch, EPI_BOX_COLS, EPI_BOX_ROWS)) return e;
+    } else {
+        mc = ma;  // never used by the kernel
+    }
 
     // ---- CTA-pair form: worth it once there is at least one 256 × 256 tile per pair of SMs ----
     const int64_t ptiles_m = (M + PBM - 1) / PBM, ptiles_n = (N + BN - 1) / BN;
@@ -1480,6 +1599,7 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
         pp.k_blocks = (int)((K + BK - 1) / BK);
         pp.status = status;
         pp.raster = raster_group(M, N, K, (int)sizeof(*A), ptiles_m);
+        pp.c_by_tma = c_by_tma ? 1 : 0;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ptiles, pairs), 1, 1);
         cfg.blockDim = dim3(NUM_THREADS, 1, 1);
@@ -1492,24 +1612,15 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<T>, ma, mb, C, pp);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<T>, ma, mb, mc, C, pp);
         if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 pair): %s", cudaGetErrorString(e));
         return check_launch("matmul(tcgen05 pair)");
     }
-
-    GemmParams p;
-    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
-    p.tiles_m = (int)((M + BM - 1) / BM);
-    p.tiles_n = (int)((N + BN - 1) / BN);
-    const int64_t tiles = int64_t(p.tiles_m) * p.tiles_n * batch;
-    if (tiles >= (1ll << 31)) return fail(DX_E_SHAPE, "matmul: too many tiles");
-    p.num_tiles = (int)tiles;
-    p.k_blocks = (int)((K + BK - 1) / BK);
-    p.status = status;
-    p.raster = raster_group(M, N, K, (int)sizeof(*A), p.tiles_m);
-    const int grid = (int)std::min<int64_t>(tiles, sm_count());
-    gemm_tcgen05_kernel<T><<<grid, NUM_THREADS, SMEM_BYTES, st>>>(ma, mb, C, p);
-    return check_launch("matmul(tcgen05)");
+    switch (pick_tile_n(M, N, K, batch)) {
+        case 64: return launch_single<T, 64>(ma, mb, mc, C, batch, M, N, K, c_by_tma, status, dev, st);
+        case 128: return launch_single<T, 128>(ma, mb, mc, C, batch, M, N, K, c_by_tma, status, dev, st);
+        default: return launch_single<T, 256>(ma, mb, mc, C, batch, M, N, K, c_by_tma, status, dev, st);
+    }
 }
 
 // Few rows: the split-K cluster kernel.  DX_E_UNSUPPORTED = not a shape for it.
