@@ -1,17 +1,20 @@
 // dx_matmul: batched row-major C[b,M,N] = A[b,M,K] · B[b,K,N].
 //
-// bf16 / f16: a persistent, warp-specialised tcgen05 kernel (sm_100a).
-//   * one CTA per SM walks output tiles of 128 × 256;
+// bf16 / f16: persistent, warp-specialised tcgen05 kernels (sm_100a).
+//   * one CTA per SM walks output tiles of 128 × 256 (or 128 × 128 / 128 × 64 when the matrix gives
+//     too few wide tiles; a pair of CTAs shares 256 × 256 tiles when there are enough of those);
 //   * warp 0 (one elected lane) is the TMA producer: per 64-deep K block it loads an
 //     A tile (128 rows × 64 K, K-major) and four B tiles (64 K × 64 N, N-major) into a
-//     4-stage shared-memory ring with 128-byte swizzle, completing on an mbarrier;
+//     shared-memory ring with 128-byte swizzle, completing on an mbarrier;
 //   * warp 1 (one elected lane) issues tcgen05.mma (M128 N256 K16, kind::f16, fp32
 //     accumulate) four times per stage, reading operands straight from shared memory
 //     through matrix descriptors; tcgen05.commit releases the stage / publishes the tile;
 //   * accumulators live in TMEM, double-buffered (2 × 256 columns), so the epilogue of
 //     tile i overlaps the main loop of tile i+1;
-//   * warps 2-5 are the epilogue: tcgen05.ld their 32-lane quarter, round fp32 → 16-bit
-//     once, 16-byte stores.
+//   * warps 2-9 are the epilogue, two per TMEM lane quarter: tcgen05.ld, round fp32 → 16-bit
+//     once, turn 32 × 64 blocks round in shared memory, store whole 128-byte lines of C.
+// Matrices with few rows take cluster kernels that split K (one row of 128 × 64 tiles, or a few
+// rows of 256 × 256 pair tiles) and combine the partial tiles through distributed shared memory.
 // B is consumed in its natural [K,N] layout (MN-major operand), so no transpose pass.
 // No cluster launch and no multicast: every CTA loads its own tiles; A and B fit in L2.
 //
@@ -37,7 +40,8 @@ constexpr int BM = 128, BN = 256, BK = 64;   // CTA tile; BK·2 bytes = one 128-
 constexpr int UMMA_K = 16;
 constexpr int STAGES = 4;
 constexpr int ACC_STAGES = 2;
-constexpr int NUM_THREADS = 192;             // TMA warp, MMA warp, 4 epilogue warps
+constexpr int NUM_THREADS = 192;             // TMA warp, MMA warp, 4 epilogue warps (the split-K kernels)
+constexpr int G_THREADS = 320;               // TMA warp, MMA warp, 8 epilogue warps (the persistent tile kernels)
 constexpr int A_STAGE_BYTES = BM * BK * 2;   // 16 KiB
 constexpr int B_BOX_N = 64;                  // one TMA box of B: 64 K-rows × 64 N (128 bytes wide)
 constexpr int B_BOX_BYTES = BK * B_BOX_N * 2;  // 8 KiB
@@ -171,17 +175,13 @@ __device__ __forceinline__ void grouped_tile_coords(int tile, int tiles_m, int t
 }
 
 // ---- the way out: TMEM → registers → C ----------------------------------------------------------
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
-    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-                 ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
-                 : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int PENDING> __device__ __forceinline__ void bulk_wait_read() {
-    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
-}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
 }
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -194,77 +194,68 @@ template <> __device__ __forceinline__ uint32_t pack2<f16>(float lo, float hi) {
     return *reinterpret_cast<uint32_t *>(&v);
 }
 
-constexpr int EPI_BOX_ROWS = 32, EPI_BOX_COLS = 64;                // one TMA store: a warp's 32 rows × 64 columns
-constexpr int EPI_BUF_BYTES = EPI_BOX_ROWS * EPI_BOX_COLS * 2;    // 4 KiB, 128 bytes per row
-constexpr int EPI_WARP_BYTES = 2 * EPI_BUF_BYTES;                 // double-buffered per warp
-constexpr int EPI_BYTES = 4 * EPI_WARP_BYTES;                     // 32 KiB for the four epilogue warps
+constexpr int EPI_ROWS = 32, EPI_COLS = 64;              // one block: a warp's 32 rows × 64 columns
+constexpr int EPI_WARP_BYTES = EPI_ROWS * EPI_COLS * 2;  // 4 KiB per epilogue warp, 128 bytes per row
+constexpr int EPI_BYTES = 8 * EPI_WARP_BYTES;            // 32 KiB for the eight epilogue warps
 
 // One epilogue warp drains its 32 rows of a finished accumulator (`width` columns at `tmem_acc`),
-// rounding fp32 to the 16-bit type once.  With `by_tma` it stages 32 rows × 64 columns at a time in
-// its own shared-memory buffer — rows of 128 bytes, 16-byte chunks XOR-swizzled by row so that the
-// warp's writes spread over all banks and match the store's 128-byte swizzle — and one lane hands
-// the block to a TMA store: whole 128-byte lines leave the SM asynchronously, rows and columns past
-// the edge of C are clipped by the copy engine.  Two buffers alternate; a buffer is rewritten only
-// after the store issued from it two blocks ago has finished reading.  Without `by_tma` (C's base or
-// pitch is not a multiple of 16 bytes) each lane stores its own row from registers.
+// rounding fp32 to the 16-bit type once.  Out of TMEM a lane holds one ROW; stored like that, one
+// store instruction touches 32 different rows, 16 bytes each.  So when C allows 16-byte stores
+// (`staged`: base and pitch multiples of 16 bytes) the warp turns each block of 32 rows × 64 columns
+// round in its own 4 KiB of shared memory — rows of 128 bytes, the 16-byte chunks of a row
+// XOR-swizzled by the row number so that both directions are free of bank conflicts — and writes it
+// out with eight lanes per row: every store instruction covers four whole 128-byte lines of C.
+// (A TMA store of the same block costs the issuing lane about 300 cycles per 4 KiB, measured, and the
+// wait before its buffer may be reused another 200; the plain stores need neither.)
+// Without `staged` each lane stores its own row from registers.
 template <typename T>
-__device__ __forceinline__ void drain_accumulator(uint32_t tmem_acc, int width, T *C, const CUtensorMap *tmap_c, bool by_tma,
-                                                  uint32_t stage_smem, int &buf, int M, int N, int b, int row0, int col0,
-                                                  int lane) {
+__device__ __forceinline__ void drain_accumulator(uint32_t tmem_acc, int width, T *C, bool staged, uint32_t stage_smem, int M, int N,
+                                                  int b, int row0, int col0, int lane) {
     const int row = row0 + lane;
-    const bool vec_ok = (N % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0;
 #pragma unroll 1
-    for (int c0 = 0; c0 < width; c0 += EPI_BOX_COLS) {
+    for (int c0 = 0; c0 < width; c0 += EPI_COLS) {
         uint32_t r[2][32];
         tmem_ld_32x32b_x32(tmem_acc + c0, r[0]);
         tmem_ld_32x32b_x32(tmem_acc + c0 + 32, r[1]);
         tmem_ld_wait();
         const int col = col0 + c0;
         if (row0 >= M || col >= N) continue;  // the whole block lies outside C (same answer in every lane)
-        if (by_tma) {
-            if (lane == 0) bulk_wait_read<1>();
-            __syncwarp();
-            const uint32_t src = stage_smem + buf * EPI_BUF_BYTES;
-            const uint32_t dst = src + lane * 128;
+        if (staged) {
+            const uint32_t mine = stage_smem + lane * 128;
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int v = 0; v < 4; ++v) {
                     const int chunk = h * 4 + v;
-                    st_shared_v4(dst + ((chunk ^ (lane & 7)) << 4),
+                    st_shared_v4(mine + ((chunk ^ (lane & 7)) << 4),
                                  pack2<T>(__uint_as_float(r[h][8 * v + 0]), __uint_as_float(r[h][8 * v + 1])),
                                  pack2<T>(__uint_as_float(r[h][8 * v + 2]), __uint_as_float(r[h][8 * v + 3])),
                                  pack2<T>(__uint_as_float(r[h][8 * v + 4]), __uint_as_float(r[h][8 * v + 5])),
                                  pack2<T>(__uint_as_float(r[h][8 * v + 6]), __uint_as_float(r[h][8 * v + 7])));
                 }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy writes, read next by the copy engine
             __syncwarp();
-            if (lane == 0) {
-                tma_store_3d(tmap_c, src, col, row0, b);
-                bulk_commit();
+            // lane → (row lane/8 of a group of four rows, chunk lane%8): 4 rows × 128 bytes per instruction
+            const int chunk = lane & 7;
+            const int gcol = col + chunk * 8;
+            uint4 v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int rr = i * 4 + (lane >> 3);
+                v[i] = ld_shared_v4(stage_smem + rr * 128 + ((chunk ^ (rr & 7)) << 4));
             }
-            buf ^= 1;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int rr = i * 4 + (lane >> 3);
+                if (row0 + rr < M && gcol < N) *reinterpret_cast<uint4 *>(C + (size_t(b) * M + row0 + rr) * N + gcol) = v[i];
+            }
+            __syncwarp();  // the block is in registers / on its way before the next one overwrites the buffer
         } else if (row < M) {
             T *crow = C + (size_t(b) * M + row) * N;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int hc = col + 32 * h;
-                if (vec_ok && hc + 32 <= N) {
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 o;
-                        o.x = pack2<T>(__uint_as_float(r[h][8 * v + 0]), __uint_as_float(r[h][8 * v + 1]));
-                        o.y = pack2<T>(__uint_as_float(r[h][8 * v + 2]), __uint_as_float(r[h][8 * v + 3]));
-                        o.z = pack2<T>(__uint_as_float(r[h][8 * v + 4]), __uint_as_float(r[h][8 * v + 5]));
-                        o.w = pack2<T>(__uint_as_float(r[h][8 * v + 6]), __uint_as_float(r[h][8 * v + 7]));
-                        *reinterpret_cast<uint4 *>(crow + hc + 8 * v) = o;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        if (hc + j < N) crow[hc + j] = from_compute<T>(__uint_as_float(r[h][j]));
-                }
-            }
+                for (int j = 0; j < 32; ++j)
+                    if (col + 32 * h + j < N) crow[col + 32 * h + j] = from_compute<T>(__uint_as_float(r[h][j]));
         }
     }
 }
@@ -286,16 +277,20 @@ struct GemmParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, num_tiles, k_blocks;
     int raster;   // rows of tiles per raster group
-    int c_by_tma; // C leaves through TMA stores (its base and pitch are multiples of 16 bytes)
+    int c_staged; // C takes 16-byte stores (base and pitch multiples of 16 bytes): blocks are turned round in shared memory
     int *status;
 };
 
 template <typename T, int BN_>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                        const __grid_constant__ CUtensorMap tmap_c, T *__restrict__ C, GemmParams p) {
+__global__ void __launch_bounds__(G_THREADS, 1)
+    gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, T *__restrict__ C,
+                        GemmParams p) {
     using Cfg = TileCfg<BN_>;
     constexpr int NS = Cfg::NSTAGES;
+    // A lane quarter of TMEM is reachable from warps with the same warp % 4 only: two warps per quarter, each
+    // taking half of the tile's columns (a 64-column tile has one 64-column block per quarter: four warps work).
+    constexpr int EPI_WARPS = BN_ >= 128 ? 8 : 4;
+    constexpr int EPI_WIDTH = BN_ >= 128 ? BN_ / 2 : BN_;
     extern __shared__ uint8_t smem_raw[];
     // 128-byte swizzle atoms are 1024 bytes: stage bases must be 1024-byte aligned
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -322,13 +317,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (int a = 0; a < ACC_STAGES; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 4);  // one arrival per epilogue warp
+            mbar_init(tempty_bar(a), EPI_WARPS);  // one arrival per working epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
-        prefetch_tmap(&tmap_c);
     }
     if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM);
     tc_fence_before();
@@ -409,12 +403,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
             }
         }
-    } else {
-        // ===== epilogue: warps 2..5; a warp may touch TMEM lanes 32·(warp%4) .. +31 =====
+    } else if (warp - 2 < EPI_WARPS) {
+        // ===== epilogue: warps 2..9; a warp may touch TMEM lanes 32·(warp%4) .. +31 =====
         const int q = warp & 3;
+        const int c_first = ((warp - 2) >> 2) * EPI_WIDTH;  // this warp's share of the tile's columns
         int acc = 0;
         uint32_t acc_phase = 0;
-        int buf = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
             int b, tm, tn;
             grouped_tile_coords(tile, p.tiles_m, p.tiles_n, p.raster, b, tm, tn);
@@ -423,14 +417,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 break;
             }
             tc_fence_after();
-            drain_accumulator<T>(tmem_base + (uint32_t(q * 32) << 16) + acc * BN_, BN_, C, &tmap_c, p.c_by_tma != 0,
-                                 epi_smem + q * EPI_WARP_BYTES, buf, p.M, p.N, b, tm * BM + q * 32, tn * BN_, lane);
+            drain_accumulator<T>(tmem_base + (uint32_t(q * 32) << 16) + acc * BN_ + c_first, EPI_WIDTH, C, p.c_staged != 0,
+                                 epi_smem + (warp - 2) * EPI_WARP_BYTES, p.M, p.N, b, tm * BM + q * 32, tn * BN_ + c_first, lane);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
             if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
-        if (lane == 0) bulk_wait_read<0>();  // the staging buffers must outlive the stores that read them
     }
     // Teardown: everyone meets, then the allocating warp frees TMEM.
     tc_fence_before();
@@ -512,14 +505,14 @@ struct PairParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, num_tiles, k_blocks;  // tiles of 256 × 256
     int raster;   // rows of tiles per raster group
-    int c_by_tma; // C leaves through TMA stores
+    int c_staged; // C takes 16-byte stores
     int *status;
 };
 
 template <typename T>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(G_THREADS, 1)
     gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                             const __grid_constant__ CUtensorMap tmap_c, T *__restrict__ C, PairParams p) {
+                             T *__restrict__ C, PairParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t epi_smem = smem_base + P_STAGES * P_STAGE_BYTES;
@@ -548,13 +541,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         for (int a = 0; a < ACC_STAGES; ++a) {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), 8);  // used in the leader only: 4 epilogue warps × 2 CTAs
+            mbar_init(tempty_bar(a), 16);  // used in the leader only: 8 epilogue warps × 2 CTAs
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
-        prefetch_tmap(&tmap_c);
     }
     if (warp == 1) tmem_alloc_pair(tmem_slot, TMEM_COLS);
     tc_fence_before();
@@ -636,11 +628,12 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
     } else {
-        // ===== epilogue: warps 2..5 of BOTH CTAs, each CTA drains its own 128 rows from its own TMEM =====
+        // ===== epilogue: warps 2..9 of BOTH CTAs, each CTA drains its own 128 rows from its own TMEM;
+        // two warps per TMEM lane quarter, each taking 128 of the 256 columns =====
         const int q = warp & 3;
+        const int c_first = ((warp - 2) >> 2) * (BN / 2);
         int acc = 0;
         uint32_t acc_phase = 0;
-        int buf = 0;
         for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
             int b, tm, tn;
             tile_coords(tile, b, tm, tn);
@@ -649,14 +642,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
                 break;
             }
             tc_fence_after();
-            drain_accumulator<T>(tmem_base + (uint32_t(q * 32) << 16) + acc * BN, BN, C, &tmap_c, p.c_by_tma != 0,
-                                 epi_smem + q * EPI_WARP_BYTES, buf, p.M, p.N, b, tm * PBM + int(rank) * BM + q * 32, tn * BN, lane);
+            drain_accumulator<T>(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c_first, BN / 2, C, p.c_staged != 0,
+                                 epi_smem + (warp - 2) * EPI_WARP_BYTES, p.M, p.N, b, tm * PBM + int(rank) * BM + q * 32,
+                                 tn * BN + c_first, lane);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));  // the leader's barrier collects all eight warps
+            if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));  // the leader's barrier collects all sixteen warps
             if (++acc == ACC_STAGES) { acc = 0; acc_phase ^= 1; }
         }
-        if (lane == 0) bulk_wait_read<0>();  // the staging buffers must outlive the stores that read them
     }
     // Teardown: neither CTA may leave (or free TMEM) while the other can still signal its barriers
     // or read its shared memory, so the whole pair meets first.
@@ -852,6 +845,224 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, S_TMEM_COLS);
+    }
+}
+
+// ---- a few rows of tiles (M of a few hundred): 256 x 256 pair tiles, K split across a cluster ---------
+// What bounds a tile kernel on this part is how fast an SM can pull operands out of L2 (about 64 bytes
+// per clock): a 128 x 256 tile of one CTA needs 96 bytes per clock to keep its tensor core busy, the
+// 256 x 256 tile of a CTA pair needs 64 per SM because the B panel is shared.  A matrix with two or
+// four rows of tiles gives too few pair tiles for the machine, so here the K range of one pair tile is
+// divided among KS <= 4 pairs of one cluster (2·KS CTAs): every pair runs the cta_group::2 main loop
+// over its slice of K; then CTA (slice s, half h) collects columns [s, s+1)·256/KS of rows h·128.. from
+// all KS slices — each CTA pushes its fp32 partial of those columns into the collector's shared memory
+// (over the drained ring) with remote stores — adds them in slice order and writes them to C.
+// One tile per cluster, no workspace, no atomics: same bits every run.
+constexpr int PS_PARTIAL_BYTES = BM * BN * 4;  // 128 KiB
+constexpr int PS_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + 256;
+static_assert(PS_PARTIAL_BYTES <= P_STAGES * P_STAGE_BYTES, "partial tile must fit in the ring");
+
+struct PairSplitParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, k_blocks, kb_per_slice;
+    int *status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tcgen05_pair_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                    T *__restrict__ C, PairSplitParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    constexpr int BAR_OFF = P_STAGES * P_STAGE_BYTES;
+    const uint32_t bars = smem_base + BAR_OFF;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (P_STAGES + s); };
+    const uint32_t tfull_bar = bars + 8u * (2 * P_STAGES);
+    constexpr int SLOT_OFF = 8 * (2 * P_STAGES + 1);
+    const uint32_t tmem_slot = bars + SLOT_OFF;
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + BAR_OFF + SLOT_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + BAR_OFF + SLOT_OFF + 8);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    uint32_t csize;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t half = rank & 1u;        // which 128 rows of the pair tile
+    const uint32_t slice = rank >> 1;       // which part of K
+    const uint32_t leader = rank & ~1u;     // the CTA of this pair that issues the MMAs
+    const uint32_t ks = csize >> 1;
+    const int tile = blockIdx.x / csize;
+    const int per_batch = p.tiles_m * p.tiles_n;
+    const int b = tile / per_batch;
+    const int tm = (tile - b * per_batch) / p.tiles_n;
+    const int tn = tile - b * per_batch - tm * p.tiles_n;
+    const int kb0 = int(slice) * p.kb_per_slice;
+    const int kb1 = min(p.k_blocks, kb0 + p.kb_per_slice);
+    const int nkb = max(kb1 - kb0, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);   // used in the pair's leader only
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, BN);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_EMPTY); }
+                    break;
+                }
+                const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+                const uint32_t sb = sa + A_STAGE_BYTES;
+                const uint32_t leader_full = mapa_u32(full_bar(stage), leader);
+                if (half == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);  // both CTAs' bytes
+                tma_load_3d_pair(sa, &tmap_a, leader_full, kb * BK, tm * PBM + int(half) * BM, b);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    tma_load_3d_pair(sb + j * B_BOX_BYTES, &tmap_b, leader_full, tn * BN + int(half) * 128 + j * B_BOX_N, kb * BK, b);
+                if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000ll) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && half == 0 && nkb > 0) {
+            constexpr uint32_t idesc = make_idesc_pair(std::is_same<T, bf16>::value ? 1 : 0);
+            const uint16_t mask = uint16_t(0x3u << leader);  // this pair's two CTAs
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_FULL); }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+                const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t adesc = make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+                    const uint64_t bdesc = make_smem_desc(sb + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
+                    umma_f16_pair(tmem_base, adesc, bdesc, idesc, (kb | k) != 0);
+                }
+                umma_commit_pair(empty_bar(stage), mask);
+                if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (ok) umma_commit_pair(tfull_bar, mask);  // both CTAs' accumulators complete
+        }
+    }
+    // ---- combine the KS partial tiles ----
+    // Barrier 1: every CTA of the cluster has finished its main loop (its epilogue warps arrive only after
+    // their accumulator is complete), so every ring is drained and may be overwritten.
+    bool have = false;
+    if (warp >= 2 && nkb > 0) {
+        if (mbar_wait(tfull_bar, 0, abort_flag)) {
+            tc_fence_after();
+            have = true;
+        } else if (lane == 0 && !*abort_flag) {
+            *abort_flag = 1;
+            atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    // Push: slice o of the cluster owns columns [o, o+1)·256/KS.  Each epilogue warp sends its 32 rows of
+    // every 32-column chunk to the owner's receive buffer for this slice — remote 16-byte stores, which
+    // unlike remote loads nobody has to wait for.  A receive buffer is row-major [128][256/KS] floats with
+    // the 16-byte chunks of a row XOR-swizzled by the row number (conflict-free for writer and reader).
+    const int cols_per = BN / int(ks);
+    const uint32_t pitch = uint32_t(cols_per) * 4u;
+    const uint32_t recv_bytes = uint32_t(BM) * pitch;  // per source slice; KS of them = 128 KiB
+    if (warp >= 2) {
+        tc_fence_after();
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            if (have) {
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + c0, r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+            const int owner = c0 / cols_per;
+            const int cin = c0 - owner * cols_per;  // first column inside the owner's share
+            const uint32_t dst = mapa_u32(smem_base + slice * recv_bytes + uint32_t(row) * pitch, uint32_t(2 * owner) + half);
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                const uint32_t chunk = uint32_t(cin / 4 + v) ^ uint32_t(row & 7);
+                asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst + chunk * 16u), "r"(r[4 * v + 0]),
+                             "r"(r[4 * v + 1]), "r"(r[4 * v + 2]), "r"(r[4 * v + 3])
+                             : "memory");
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // barrier 2: every slice's share has arrived (release/acquire over the cluster)
+    {
+        // Local sum over the KS receive buffers in slice order, round once, 8-byte stores: a warp covers
+        // 128 consecutive columns of one row of C.
+        const int chunks_per_row = cols_per / 4;
+        const int row_base = tm * PBM + int(half) * BM;
+        const int live = min(BM, p.M - row_base);  // rows of this CTA inside C (may be <= 0)
+        const int col_base = tn * BN + int(slice) * cols_per;
+        T *cbase = C + size_t(b) * p.M * p.N;
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(C) & 7) == 0;  // N % 8 == 0 on this path
+        for (int u = threadIdx.x; u < max(live, 0) * chunks_per_row; u += NUM_THREADS) {
+            const int row = u / chunks_per_row, chunk = u - row * chunks_per_row;
+            const uint32_t off = uint32_t(row) * pitch + ((uint32_t(chunk) ^ uint32_t(row & 7)) << 4);
+            float4 acc = *reinterpret_cast<const float4 *>(gen_base + off);
+            for (uint32_t s = 1; s < ks; ++s) {
+                const float4 v = *reinterpret_cast<const float4 *>(gen_base + s * recv_bytes + off);
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            const int gcol = col_base + chunk * 4;
+            T *dst = cbase + size_t(row_base + row) * p.N + gcol;
+            if (vec_ok && gcol + 4 <= p.N) {
+                uint2 o;
+                o.x = pack2<T>(acc.x, acc.y);
+                o.y = pack2<T>(acc.z, acc.w);
+                *reinterpret_cast<uint2 *>(dst) = o;
+            } else {
+                const float out4[4] = {acc.x, acc.y, acc.z, acc.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (gcol + j < p.N) dst[j] = from_compute<T>(out4[j]);
+            }
+        }
+    }
+    // the pair frees its TMEM together
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, BN);
     }
 }
 
@@ -1482,7 +1693,7 @@ template <typename T> int pair_slots(int dev) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2u * (unsigned)sm_count(), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(G_THREADS, 1, 1);
     cfg.dynamicSmemBytes = P_SMEM_BYTES;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1502,8 +1713,8 @@ template <typename T> int pair_slots(int dev) {
 
 // Persistent single-CTA kernel at tile width BN_.
 template <typename T, int BN_>
-int launch_single(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mc, T *C, int64_t batch, int64_t M, int64_t N,
-                  int64_t K, bool c_by_tma, int *status, int dev, cudaStream_t st) {
+int launch_single(const CUtensorMap &ma, const CUtensorMap &mb, T *C, int64_t batch, int64_t M, int64_t N, int64_t K, bool c_staged,
+                  int *status, int dev, cudaStream_t st) {
     using Cfg = TileCfg<BN_>;
     {
         static bool attr_set[64] = {};
@@ -1524,33 +1735,44 @@ int launch_single(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMa
     p.k_blocks = (int)((K + BK - 1) / BK);
     p.status = status;
     p.raster = raster_group(M, N, K, (int)sizeof(T), p.tiles_m);
-    p.c_by_tma = c_by_tma ? 1 : 0;
+    p.c_staged = c_staged ? 1 : 0;
     const int grid = (int)std::min<int64_t>(tiles, sm_count());
-    gemm_tcgen05_kernel<T, BN_><<<grid, NUM_THREADS, Cfg::SMEM, st>>>(ma, mb, mc, C, p);
+    gemm_tcgen05_kernel<T, BN_><<<grid, G_THREADS, Cfg::SMEM, st>>>(ma, mb, C, p);
     return check_launch("matmul(tcgen05)");
 }
 
-// Tile width for the single-CTA kernel: the width whose waves × time per tile is least.  Per 64-deep
-// K block a 128 × 256 tile keeps the tensor core busy for 512 cycles; narrower tiles are bound by
-// shared-memory reads instead (A is re-read for fewer columns): about 280 and 192 cycles.
-int pick_tile_n(int64_t M, int64_t N, int64_t K, int64_t batch) {
+// Cost model, in SM cycles, behind the choice of kernel and tile width; the constants are fitted to
+// measurements.  What bounds the main loop is operand traffic out of L2: an SM takes in about 64 bytes
+// per clock, all SMs together about 6800.  Per 64-deep K block a single CTA pulls 48 / 32 / 24 KiB for
+// a 128 × 256 / 128 / 64 tile (770 / 512 / 384 cycles, more than the 512 / 256 / 128 the tensor core
+// needs); the two CTAs of a pair pull 32 KiB each for a 256 × 256 tile and stay near the tensor core's
+// 512.  On top comes what a tile costs besides its main loop — mostly writing C, which overlaps the
+// next tile's main loop only in part: about 0.75 × (400 + bytes / 20) cycles per CTA tile, and about
+// 4300 per pair tile (the pair's barriers cross SMs).  With K of a few hundred that term decides.
+int64_t tiles_cost(int64_t tiles, int64_t slots, int64_t k_blocks, int64_t cycles_per_kb, int64_t bytes_per_kb, int64_t per_tile) {
+    const int64_t waves = (tiles + slots - 1) / slots;
+    return std::max<int64_t>(waves * (k_blocks * cycles_per_kb + per_tile), tiles * k_blocks * bytes_per_kb / 6800);
+}
+constexpr int64_t PAIR_TILE_OVERHEAD = 4300;
+constexpr int64_t single_tile_overhead(int bn) { return (400 + int64_t(BM) * bn * 2 / 20) * 3 / 4; }
+int pick_tile_n(int64_t M, int64_t N, int64_t K, int64_t batch, int64_t *cost_out = nullptr) {
     static const int forced = [] {
         const char *e = std::getenv("DX_GEMM_TILE_N");
         const int v = e ? std::atoi(e) : 0;
         return (v == 256 || v == 128 || v == 64) ? v : 0;
     }();
-    if (forced) return forced;
     const int64_t sms = sm_count(), tiles_m = (M + BM - 1) / BM, k_blocks = (K + BK - 1) / BK;
     const int widths[3] = {256, 128, 64};
-    const int64_t cycles[3] = {512, 280, 192};
+    const int64_t cycles[3] = {770, 512, 384};
     int best = 256;
     int64_t best_cost = -1;
     for (int i = 0; i < 3; ++i) {
+        if (forced && widths[i] != forced) continue;
         const int64_t tiles = tiles_m * ((N + widths[i] - 1) / widths[i]) * batch;
-        const int64_t waves = (tiles + sms - 1) / sms;
-        const int64_t cost = waves * (k_blocks * cycles[i] + 1500);
+        const int64_t cost = tiles_cost(tiles, sms, k_blocks, cycles[i], A_STAGE_BYTES + int64_t(widths[i]) * BK * 2, single_tile_overhead(widths[i]));
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = widths[i]; }
     }
+    if (cost_out) *cost_out = best_cost;
     return best;
 }
 
@@ -1571,17 +1793,12 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
         status = g_status_ptr[dev];
     }
     const CUtensorMapDataType dt = std::is_same<T, bf16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap ma, mb, mc;
+    CUtensorMap ma, mb;
     if (int e = make_map(&ma, dt, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, BK, BM)) return e;
     if (int e = make_map(&mb, dt, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, B_BOX_N, BK)) return e;
-    // C through TMA stores when its base is 16-byte aligned (its pitch is: N % 8 == 0 on this path); DX_GEMM_TMA_STORE=0 turns it off
-    static const bool tma_store_on = [] { const char *e = std::getenv("DX_GEMM_TMA_STORE"); return !(e && e[0] == '0'); }();
-    const bool c_by_tma = tma_store_on && aligned_to(C, 16);
-    if (c_by_tma) {
-        if (int e = make_map(&mc, dt, C, (uint64_t)N, (uint64_t)M, (uint64_t)batch, EPI_BOX_COLS, EPI_BOX_ROWS)) return e;
-    } else {
-        mc = ma;  // never used by the kernel
-    }
+    // 16-byte stores into C need its base aligned (its pitch is: N % 8 == 0 on this path); DX_GEMM_STAGED_STORE=0 turns them off
+    static const bool staged_on = [] { const char *e = std::getenv("DX_GEMM_STAGED_STORE"); return !(e && e[0] == '0'); }();
+    const bool c_staged = staged_on && aligned_to(C, 16);
 
     // ---- CTA-pair form: worth it once there is at least one 256 × 256 tile per pair of SMs ----
     const int64_t ptiles_m = (M + PBM - 1) / PBM, ptiles_n = (N + BN - 1) / BN;
@@ -1589,7 +1806,11 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
     const int pairs = pair_slots<T>(dev);
     int mode = -1;  // auto
     if (const char *env = std::getenv("DX_GEMM_CTA_PAIR")) mode = (env[0] == '1') ? 1 : (env[0] == '0' ? 0 : -1);
-    const bool use_pair = pairs > 0 && ptiles < (1ll << 31) && (mode == 1 || (mode == -1 && ptiles >= pairs));
+    int64_t single_cost = 0;
+    const int tile_n = pick_tile_n(M, N, K, batch, &single_cost);
+    const int64_t k_blocks_all = (K + BK - 1) / BK;
+    const bool pair_cheaper = pairs > 0 && tiles_cost(ptiles, pairs, k_blocks_all, 550, 2 * P_STAGE_BYTES, PAIR_TILE_OVERHEAD) <= single_cost;
+    const bool use_pair = pairs > 0 && ptiles < (1ll << 31) && (mode == 1 || (mode == -1 && pair_cheaper));
     if (use_pair) {
         PairParams pp;
         pp.M = (int)M; pp.N = (int)N; pp.K = (int)K; pp.batch = (int)batch;
@@ -1599,10 +1820,10 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
         pp.k_blocks = (int)((K + BK - 1) / BK);
         pp.status = status;
         pp.raster = raster_group(M, N, K, (int)sizeof(*A), ptiles_m);
-        pp.c_by_tma = c_by_tma ? 1 : 0;
+        pp.c_staged = c_staged ? 1 : 0;
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2u * (unsigned)std::min<int64_t>(ptiles, pairs), 1, 1);
-        cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+        cfg.blockDim = dim3(G_THREADS, 1, 1);
         cfg.dynamicSmemBytes = P_SMEM_BYTES;
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
@@ -1612,14 +1833,14 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<T>, ma, mb, mc, C, pp);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<T>, ma, mb, C, pp);
         if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 pair): %s", cudaGetErrorString(e));
         return check_launch("matmul(tcgen05 pair)");
     }
-    switch (pick_tile_n(M, N, K, batch)) {
-        case 64: return launch_single<T, 64>(ma, mb, mc, C, batch, M, N, K, c_by_tma, status, dev, st);
-        case 128: return launch_single<T, 128>(ma, mb, mc, C, batch, M, N, K, c_by_tma, status, dev, st);
-        default: return launch_single<T, 256>(ma, mb, mc, C, batch, M, N, K, c_by_tma, status, dev, st);
+    switch (tile_n) {
+        case 64: return launch_single<T, 64>(ma, mb, C, batch, M, N, K, c_staged, status, dev, st);
+        case 128: return launch_single<T, 128>(ma, mb, C, batch, M, N, K, c_staged, status, dev, st);
+        default: return launch_single<T, 256>(ma, mb, C, batch, M, N, K, c_staged, status, dev, st);
     }
 }
 
@@ -1632,7 +1853,7 @@ template <typename T> int launch_splitk(const T *A, const T *B, T *C, int64_t ba
     const int64_t big_tiles = ((N + BN - 1) / BN) * batch;
     if (big_tiles * 2 > sm_count() || k_blocks < 8 || tiles_n * 8 >= (1ll << 31)) return DX_E_UNSUPPORTED;
     int cs = 1;
-    while (cs < 8 && tiles_n * batch * cs < 2 * sm_count() && k_blocks / (cs * 2) >= 4) cs *= 2;
+    while (cs < 8 && tiles_n * batch * cs * 2 <= 2 * sm_count() && k_blocks / (cs * 2) >= 4) cs *= 2;  // two CTAs per SM: stay within one wave
     if (cs < 4) return DX_E_UNSUPPORTED;  // measured: with fewer than four K slices per tile the persistent kernels are as fast
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1680,6 +1901,90 @@ template <typename T> int launch_splitk(const T *A, const T *B, T *C, int64_t ba
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_splitk_kernel<T>, ma, mb, C, p);
     if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 split-K): %s", cudaGetErrorString(e));
     return check_launch("matmul(tcgen05 split-K)");
+}
+
+// A few rows of 256 x 256 tiles: K split over the pairs of a cluster.  DX_E_UNSUPPORTED = not a shape for it.
+// How many clusters of 2·ks CTAs of the pair split-K kernel the device runs at once (0 = none): the CTAs
+// of a cluster must sit in one GPC, which caps it well below SMs / cluster size.  Looked up once.
+template <typename T> int pair_splitk_clusters(int dev, int ks) {
+    static int known[64][2][2] = {};  // 0 unknown, else clusters + 1
+    const int ti = std::is_same<T, bf16>::value ? 0 : 1, ci = ks == 2 ? 0 : 1;
+    std::lock_guard<std::mutex> lk(g_setup_mu);
+    if (known[dev][ti][ci] == 0) {
+        int n = 0;
+        if (cudaFuncSetAttribute(gemm_tcgen05_pair_splitk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(2 * ks * sm_count()), 1, 1);
+            cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+            cfg.dynamicSmemBytes = PS_SMEM_BYTES;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = (unsigned)(2 * ks);
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_splitk_kernel<T>, &cfg) != cudaSuccess) n = 0;
+        }
+        if (n <= 0) { n = 0; cudaGetLastError(); }
+        known[dev][ti][ci] = n + 1;
+    }
+    return known[dev][ti][ci] - 1;
+}
+
+// A few rows of 256 x 256 tiles: K split over the pairs of a cluster.  DX_E_UNSUPPORTED = not a shape for it.
+template <typename T>
+int launch_pair_splitk(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64_t N, int64_t K, cudaStream_t st) {
+    const int64_t tiles_m = (M + PBM - 1) / PBM, tiles_n = (N + BN - 1) / BN;
+    const int64_t tiles = tiles_m * tiles_n * batch;
+    const int64_t k_blocks = (K + BK - 1) / BK;
+    if (M <= BM || tiles * 2 > sm_count() / 2) return DX_E_UNSUPPORTED;  // one row of tiles, or enough tiles for the persistent kernels
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return fail(DX_E_CUDA, "matmul: device index %d out of range", dev);
+    // the widest split whose clusters all run at once and whose slices keep at least 48 K blocks: the two
+    // cluster barriers, the push and the late start cost about as much as 30 K blocks of main loop
+    int ks = 0;
+    for (int cand = 4; cand >= 2 && !ks; cand >>= 1)
+        if (k_blocks / cand >= 48 && tiles <= pair_splitk_clusters<T>(dev, cand)) ks = cand;
+    if (!ks) return DX_E_UNSUPPORTED;
+    int *status;
+    {
+        std::lock_guard<std::mutex> lk(g_setup_mu);
+        if (!g_status_ptr[dev]) {
+            void *sym = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&sym, g_gemm_status);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_status_ptr[dev] = static_cast<int *>(sym);
+        }
+        status = g_status_ptr[dev];
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * ks * 2), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = PS_SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)(ks * 2);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const CUtensorMapDataType dt = std::is_same<T, bf16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap ma, mb;
+    if (int e = make_map(&ma, dt, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, BK, BM)) return e;
+    if (int e = make_map(&mb, dt, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, B_BOX_N, BK)) return e;
+    PairSplitParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.tiles_m = (int)tiles_m;
+    p.tiles_n = (int)tiles_n;
+    p.k_blocks = (int)k_blocks;
+    p.kb_per_slice = (int)((k_blocks + ks - 1) / ks);
+    p.status = status;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_splitk_kernel<T>, ma, mb, C, p);
+    if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 pair split-K): %s", cudaGetErrorString(e));
+    return check_launch("matmul(tcgen05 pair split-K)");
 }
 
 // float32 through the tensor cores (three TF32 products per product).
@@ -1840,6 +2145,14 @@ extern "C" int dx_matmul(int dtype, const void *A, const void *B, void *C, int64
                 if (splitk_on) {
                     const int rc = dtype == DX_BF16 ? launch_splitk<bf16>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, st)
                                                     : launch_splitk<f16>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);
+                    if (rc != DX_E_UNSUPPORTED) return rc;
+                }
+            }
+            if (tma_ok && M > BM) {
+                static const bool psplit_on = [] { const char *e = std::getenv("DX_GEMM_PAIR_SPLITK"); return !(e && e[0] == '0'); }();
+                if (psplit_on) {
+                    const int rc = dtype == DX_BF16 ? launch_pair_splitk<bf16>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, st)
+                                                    : launch_pair_splitk<f16>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);
                     if (rc != DX_E_UNSUPPORTED) return rc;
                 }
             }

@@ -286,6 +286,41 @@ def test_matmul_split_k_is_deterministic(mods):
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("m", [129, 256, 300, 512, 700])
+def test_matmul_few_tile_rows_pair_split_k(mods, dtype, m):
+    """Two to four rows of 256 x 256 tiles and a long K: the cluster kernel that splits K over CTA pairs
+    (partials combined through distributed shared memory); ragged M, N and K, last K slice short."""
+    TF, O, N = mods
+    rng = np.random.default_rng(seed_of("pairsplitk", dtype, m))
+    for Nn, K in [(256, 1024), (520, 2056), (4096, 4096), (1000, 1032), (264, 8192)]:
+        a = make(rng, dtype, (m, K), -1.0, 1.0)
+        b = make(rng, dtype, (K, Nn), -1.0, 1.0)
+        check(TF, N, a, b, dtype, f"matmul pair split-K<{dtype}> {(m, Nn, K)}")
+    a3 = make(rng, dtype, (2, m, 2048), -1.0, 1.0)
+    b3 = make(rng, dtype, (2, 2048, 264), -1.0, 1.0)
+    check(TF, N, a3, b3, dtype, f"matmul pair split-K<{dtype}> batched")
+
+
+def test_matmul_pair_split_k_is_deterministic_and_close_to_the_tile_kernel(mods, monkeypatch):
+    TF, O, N = mods
+    rng = np.random.default_rng(14)
+    a = make(rng, "bfloat16", (512, 4096), -1.0, 1.0)
+    b = make(rng, "bfloat16", (4096, 2048), -1.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    outs = []
+    for _ in range(3):
+        Cc = torch.empty((512, 2048), dtype=torch.bfloat16, device="cuda:0")
+        TF.matmul(A, B, Cc)
+        N.check(N.lib.dx_matmul_status(None))
+        outs.append(to_np(Cc).view(np.uint16).copy())
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    # against the unsplit kernel: the K slices are added in a different order, so one 16-bit rounding apart at most
+    ref = (a.astype(np.float64) @ b.astype(np.float64))
+    got = to_np(Cc).astype(np.float64)
+    assert np.abs(got - ref).max() <= 1e-2 * np.abs(ref).max()
+
+
 def test_matmul_golden_arange(mods):
     """arange [2,3,4] x [2,4,5]: the worked example in executor/op-ompsimd/test/tensorfunc/4_tensor_matmul.cpp:22-35."""
     TF, O, N = mods
