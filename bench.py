@@ -883,6 +883,67 @@ def run_sweep(args) -> None:
                       "min": min(res.values()), "below_0.8": low, "ops": res}), flush=True)
 
 
+def run_matmul_sweep(args) -> None:
+    """`--matmul-sweep`: dx_matmul over a list of shapes (square, tall, wide, few rows, short K, batched) in bf16
+    and float32, CUDA-graph replay over rotating buffers, with the library GEMM (torch.matmul: cuBLAS; float32 with
+    TF32 off) timed the same way beside it as a yardstick.  Prints one JSON line per shape."""
+    import torch
+    from deepx_b200 import tensorfunc as TF
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    shapes = [
+        (1, 8192, 4096, 4096), (1, 4096, 4096, 4096), (1, 2048, 2048, 2048), (1, 1024, 1024, 1024), (1, 16384, 4096, 4096),
+        (1, 8192, 8192, 8192), (1, 4096, 11008, 4096), (1, 4096, 4096, 11008), (1, 2048, 151936, 896), (1, 32768, 896, 896),
+        (1, 32768, 4864, 896), (1, 32768, 896, 4864), (1, 1024, 4096, 4096), (1, 512, 4096, 4096), (1, 256, 4096, 4096),
+        (1, 128, 4096, 4096), (1, 32, 4096, 4096), (1, 768, 2048, 8192), (32, 2048, 2048, 128), (32, 2048, 128, 2048),
+        (224, 2048, 2048, 64), (16, 1024, 1024, 1024), (64, 512, 512, 512), (8, 4096, 4096, 512), (1, 4096, 4096, 256),
+        (1, 1000, 1000, 1000), (1, 8192, 4104, 4096), (1, 3000, 5000, 7000),
+    ]
+
+    def replay_us(fns, iters=18):
+        for f in fns:
+            f()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(iters):
+                fns[i % len(fns)]()
+        g.replay()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            g.replay()
+            e.record()
+            torch.cuda.synchronize()
+            best = min(best, s.elapsed_time(e) / iters * 1e3)
+        return best
+
+    for name, dt in (("bf16", torch.bfloat16), ("f32", torch.float32)):
+        for (b, M, N, K) in shapes:
+            flop = 2.0 * b * M * N * K
+            if name == "f32" and flop > 6e11:
+                continue
+            R = 3
+            As = [torch.randn((b, M, K), device=dev).mul_(0.05).to(dt) for _ in range(R)]
+            Bs = [torch.randn((b, K, N), device=dev).mul_(0.05).to(dt) for _ in range(R)]
+            Cs = [torch.empty((b, M, N), device=dev, dtype=dt) for _ in range(R)]
+            Cl = torch.empty((b, M, N), device=dev, dtype=dt)
+            ours = replay_us([lambda i=i: TF.matmul(As[i], Bs[i], Cs[i]) for i in range(R)])
+            lib = replay_us([lambda i=i: torch.matmul(As[i], Bs[i], out=Cl) for i in range(R)])
+            torch.matmul(As[0], Bs[0], out=Cl)
+            TF.matmul(As[0], Bs[0], Cs[0])
+            err = float((Cs[0].double() - Cl.double()).abs().max() / (Cl.double().abs().max() + 1e-300))
+            print(json.dumps({"dtype": name, "batch": b, "M": M, "N": N, "K": K, "us": round(ours, 1), "tflops": round(flop / ours / 1e6, 1),
+                              "library_us": round(lib, 1), "library_tflops": round(flop / lib / 1e6, 1),
+                              "speed_vs_library": round(lib / ours, 3), "max_diff_vs_library_rel": err}), flush=True)
+            del As, Bs, Cs, Cl
+    from deepx_b200 import _native as N_
+    N_.check(N_.lib.dx_matmul_status(None))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -893,8 +954,11 @@ def main() -> None:
     ap.add_argument("--no-graph", action="store_true", help="with --op: launch directly instead of replaying a CUDA graph")
     ap.add_argument("--op", default=None, help="time one named op of the per-op table alone (single GPU)")
     ap.add_argument("--sweep", action="store_true", help="every op x dtype on 256 MiB tensors as a fraction of the HBM peak (single GPU)")
+    ap.add_argument("--matmul-sweep", action="store_true", help="dx_matmul over many shapes with the library GEMM beside it (single GPU)")
     args = ap.parse_args()
-    if args.sweep:
+    if args.matmul_sweep:
+        run_matmul_sweep(args)
+    elif args.sweep:
         run_sweep(args)
     elif args.op:
         run_one_op(args)

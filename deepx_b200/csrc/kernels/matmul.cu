@@ -1854,7 +1854,12 @@ template <typename T> int launch_splitk(const T *A, const T *B, T *C, int64_t ba
     if (big_tiles * 2 > sm_count() || k_blocks < 8 || tiles_n * 8 >= (1ll << 31)) return DX_E_UNSUPPORTED;
     int cs = 1;
     while (cs < 8 && tiles_n * batch * cs * 2 <= 2 * sm_count() && k_blocks / (cs * 2) >= 4) cs *= 2;  // two CTAs per SM: stay within one wave
-    if (cs < 4) return DX_E_UNSUPPORTED;  // measured: with fewer than four K slices per tile the persistent kernels are as fast
+    bool forced = false;
+    if (const char *e = std::getenv("DX_GEMM_SPLITK_CS")) {  // tuning override: 2, 4 or 8 K slices
+        const int v = std::atoi(e);
+        if ((v == 2 || v == 4 || v == 8) && k_blocks / v >= 1) { cs = v; forced = true; }
+    }
+    if (cs < 4 && !forced) return DX_E_UNSUPPORTED;  // measured: with fewer than four K slices per tile the persistent kernels are as fast
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return fail(DX_E_CUDA, "matmul: device index %d out of range", dev);
@@ -1873,6 +1878,9 @@ template <typename T> int launch_splitk(const T *A, const T *B, T *C, int64_t ba
         if (!attr_set[dev][ti]) {
             cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_splitk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, S_SMEM_BYTES);
             if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            // two CTAs of 97 KiB per SM need the large shared-memory split of the L1
+            cudaFuncSetAttribute(gemm_tcgen05_splitk_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaGetLastError();
             attr_set[dev][ti] = true;
         }
     }
