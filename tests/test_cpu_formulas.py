@@ -4,6 +4,10 @@
   sign * ((|a| * (floor(2^32 / |d|) + 1)) >> 32)                     (DivConstFn, ew_ops.cuh)
 * division with a per-element divisor through fp32:  trunc(a / b) == int(fl32(a) / fl32(b)) with the
   IEEE-rounded quotient                                              (BinaryFn<DX_DIV>, ew_ops.cuh)
+* the same without conversion instructions: int -> float through the bits of 1.5·2^23 + v, and the
+  truncation as round-to-nearest of (q·(1 + p) − copysign(0.5, q)) + 1.5·2^23, with q the IEEE quotient
+  and p = 2^-17 for int16, q an approximate quotient (up to 2 ulp off) and p = 2^-12 for int8
+                                                                     (trunc_pushed, small_int_to_float)
 """
 import numpy as np
 
@@ -34,3 +38,40 @@ def test_fp32_quotient_truncates_to_the_integer_quotient():
             continue
         got = np.trunc(a.astype(np.float32) / np.float32(b)).astype(np.int64)
         assert np.array_equal(got, np.trunc(a / int(b)).astype(np.int64)), b
+
+
+def _trunc_pushed(q32, push):
+    """The kernel's truncation (trunc_pushed, ew_ops.cuh) in numpy: fma(q, push, -copysign(0.5, q)) rounded once
+    to fp32, plus 1.5·2^23 rounded to fp32, minus 1.5·2^23 as integers."""
+    q32 = q32.astype(np.float32)
+    half = np.copysign(np.float32(0.5), q32)
+    u = (q32.astype(np.float64) * np.float64(np.float32(push)) - half.astype(np.float64)).astype(np.float32)  # one rounding, like fma
+    f = (u + np.float32(12582912.0)).astype(np.float32)
+    return f.view(np.int32).astype(np.int64) - 0x4B400000
+
+
+def test_int8_approximate_quotient_pushed_away_from_zero_truncates_exactly():
+    a8, b8 = np.meshgrid(np.arange(-128, 128), np.array([b for b in range(-128, 128) if b != 0]))
+    want = np.trunc(a8 / b8).astype(np.int64)
+    exact = a8.astype(np.float64) / b8.astype(np.float64)
+    for ulps in (-2.5, -1.0, 0.0, 1.0, 2.5):  # the reciprocal unit's error bound is 2 ulp of the quotient
+        approx = (exact * (1.0 + ulps * 2.0 ** -23)).astype(np.float32)
+        assert np.array_equal(_trunc_pushed(approx, 1.000244140625), want), ulps
+    # signed zeros (0 / negative gives -0.0): both must truncate to 0
+    assert np.array_equal(_trunc_pushed(np.array([0.0, -0.0], dtype=np.float32), 1.000244140625), [0, 0])
+
+
+def test_int16_ieee_quotient_pushed_away_from_zero_truncates_exactly():
+    a = np.arange(-32768, 32768)
+    rng = np.random.default_rng(2)
+    for b in list(range(1, 600)) + [-1, -2, -3, -255, 32767, -32768, 21845, 10923, -4097, 16384, -16385] + list(rng.integers(-32768, 32768, 600)):
+        if b == 0:
+            continue
+        q = a.astype(np.float32) / np.float32(b)  # IEEE-rounded, as __fdiv_rn
+        assert np.array_equal(_trunc_pushed(q, 1.00000762939453125), np.trunc(a / int(b)).astype(np.int64)), b
+
+
+def test_small_int_to_float_through_the_magic_number():
+    v = np.arange(-32768, 32768, dtype=np.int32)
+    f = (np.int32(0x4B400000) + v).view(np.float32) - np.float32(12582912.0)
+    assert np.array_equal(f, v.astype(np.float32))
