@@ -237,7 +237,35 @@ __global__ void __launch_bounds__(RB) cols_kernel(const T *__restrict__ in, T *_
         if (p.red.n == 1) return base + int64_t(r) * p.red.stride[0];
         return base + unravel(r, p.red);
     };
-    if (live) {
+    if constexpr (sizeof(T) == 1 && VEC % 4 == 0 && (OP == DX_RMAX || OP == DX_RMIN)) {
+        // int8 max / min: four elements per 32-bit word with the byte-wise SIMD max / min, instead of unpacking
+        // sixteen bytes of every vector one by one (which made this the one instruction-bound column reduction)
+        if (live) {
+            uint32_t pk[VEC / 4];
+#pragma unroll
+            for (int j = 0; j < VEC / 4; ++j) pk[j] = OP == DX_RMAX ? 0x80808080u : 0x7f7f7f7fu;
+            uint32_t r = r0 + ty;
+            for (; r + (RUNROLL - 1) * ny < r1; r += RUNROLL * ny) {
+                Pack<T, VEC> v[RUNROLL];
+#pragma unroll
+                for (int k = 0; k < RUNROLL; ++k) v[k] = ld_stream<T, VEC>(addr(r + k * ny));
+#pragma unroll
+                for (int k = 0; k < RUNROLL; ++k) {
+                    const uint32_t *w = reinterpret_cast<const uint32_t *>(&v[k]);
+#pragma unroll
+                    for (int j = 0; j < VEC / 4; ++j) pk[j] = OP == DX_RMAX ? __vmaxs4(pk[j], w[j]) : __vmins4(pk[j], w[j]);
+                }
+            }
+            for (; r < r1; r += ny) {
+                Pack<T, VEC> v = ld_stream<T, VEC>(addr(r));
+                const uint32_t *w = reinterpret_cast<const uint32_t *>(&v);
+#pragma unroll
+                for (int j = 0; j < VEC / 4; ++j) pk[j] = OP == DX_RMAX ? __vmaxs4(pk[j], w[j]) : __vmins4(pk[j], w[j]);
+            }
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = static_cast<A>(static_cast<int8_t>((pk[i / 4] >> (8 * (i % 4))) & 0xffu));
+        }
+    } else if (live) {
         uint32_t r = r0 + ty;
         for (; r + (RUNROLL - 1) * ny < r1; r += RUNROLL * ny) {
             Pack<T, VEC> v[RUNROLL];
