@@ -7,7 +7,7 @@ tests/golden/frontend_ir/<example>.ir.  The GPU tests replay those transcripts t
 executor and check every op's result, so the executor is exercised with exactly the text the
 real front end produces.
 
-    python tests/golden/record_frontend_ir.py [path of the reference tree]
+    python tests/golden/record_frontend_ir.py <path of the reference tree>
 """
 import contextlib
 import io
@@ -17,7 +17,9 @@ import sys
 import threading
 from pathlib import Path
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    raise SystemExit(__doc__)
+REF = Path(sys.argv[1])
 OUT = Path(__file__).resolve().parent / "frontend_ir"
 EXAMPLES = [
     "2_ir/1_init_zeroones.py", "2_ir/2_elementwise_add.py", "2_ir/2_elementwise_operator.py", "2_ir/2_elementwise_sqrtlog.py",

@@ -321,6 +321,27 @@ def test_matmul_pair_split_k_is_deterministic_and_close_to_the_tile_kernel(mods,
     assert np.abs(got - ref).max() <= 1e-2 * np.abs(ref).max()
 
 
+@pytest.mark.parametrize("force", ["0", "1"])
+def test_matmul_output_not_16_byte_aligned(mods, monkeypatch, force):
+    """C starting 2 bytes past a 16-byte boundary: the tile kernels store each lane's own row with scalar stores
+    instead of turning blocks round for 16-byte stores; same bits as the aligned result."""
+    TF, O, N = mods
+    monkeypatch.setenv("DX_GEMM_CTA_PAIR", force)
+    rng = np.random.default_rng(21)
+    a = make(rng, "bfloat16", (300, 520), -1.0, 1.0)
+    b = make(rng, "bfloat16", (520, 264), -1.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    aligned = torch.empty((300, 264), dtype=torch.bfloat16, device="cuda:0")
+    TF.matmul(A, B, aligned)
+    buf = torch.zeros(300 * 264 + 8, dtype=torch.bfloat16, device="cuda:0")
+    off = buf[1:1 + 300 * 264].view(300, 264)
+    assert off.data_ptr() % 16 == 2
+    TF.matmul(A, B, off)
+    N.check(N.lib.dx_matmul_status(None))
+    assert np.array_equal(to_np(off).view(np.uint16), to_np(aligned).view(np.uint16))
+    assert float(buf[0]) == 0.0 and float(buf[1 + 300 * 264:].abs().sum()) == 0.0  # nothing written outside C
+
+
 def test_matmul_golden_arange(mods):
     """arange [2,3,4] x [2,4,5]: the worked example in executor/op-ompsimd/test/tensorfunc/4_tensor_matmul.cpp:22-35."""
     TF, O, N = mods
