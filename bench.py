@@ -131,6 +131,10 @@ def run_reference(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # torch.distributed.run pins OMP_NUM_THREADS to 1 for its workers; this arm is one process on all host cores
+    # (the other ranks have exited), so give the OpenMP runtime the cores this process may run on before it loads
+    if os.environ.get("WORLD_SIZE", "1") != "1" or "OMP_NUM_THREADS" not in os.environ:
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
     import numpy as np
     from oracle import oracle as O
     O.build()
