@@ -16,6 +16,10 @@ namespace dx {
 constexpr int EW_BLOCK = 256;
 constexpr int EW_UNROLL = 4;
 
+// Whether a functor offers `pair(a0, a1, c0, c1)`, two elements per call (packed arithmetic inside).
+template <typename F, typename = void> struct functor_has_pair : std::false_type {};
+template <typename F> struct functor_has_pair<F, std::void_t<decltype(F::has_pair)>> : std::integral_constant<bool, F::has_pair> {};
+
 template <int VEC, typename TA, typename TC, typename F>
 __global__ void __launch_bounds__(EW_BLOCK) ew1_kernel(const TA *a, TC *c, int64_t n, F f) {
     constexpr int64_t TILE = int64_t(EW_BLOCK) * EW_UNROLL * VEC;
@@ -28,8 +32,13 @@ __global__ void __launch_bounds__(EW_BLOCK) ew1_kernel(const TA *a, TC *c, int64
 #pragma unroll
         for (int u = 0; u < EW_UNROLL; ++u) {
             Pack<TC, VEC> vc;
+            if constexpr (functor_has_pair<F>::value && VEC % 2 == 0) {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) vc.v[i] = f(va[u].v[i]);
+                for (int i = 0; i < VEC; i += 2) f.pair(va[u].v[i], va[u].v[i + 1], vc.v[i], vc.v[i + 1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) vc.v[i] = f(va[u].v[i]);
+            }
             st_stream<TC, VEC>(c + base + (int64_t(u) * EW_BLOCK + threadIdx.x) * VEC, vc);
         }
     } else {

@@ -113,6 +113,80 @@ template <typename T> struct DivConstFn {
 };
 
 // ---- unary ---------------------------------------------------------------------
+// sin / cos for arguments that came from a 16-bit float, in fp32 to about 1.4 ulp (every finite f16 argument
+// then rounds to the same f16 as the C library's sinf / cosf; checked on the CPU).  The library routine costs
+// about 30 instructions per element, two of them int<->float conversions on the quarter-rate unit, which
+// held these ops at 0.62–0.73 of the copy bandwidth (4 bytes of traffic per element).  Here: quadrant n =
+// nearest integer to x·2/π by adding 1.5·2^23 (its low mantissa bits are n), three-constant Cody–Waite
+// reduction with FMAs, one short polynomial each for sin and cos on [−π/4, π/4] (Cephes single-precision
+// coefficients), select and sign by n.  Beyond 1e5 (bf16 only), inf and nan take the library's full reduction.
+template <int WANT_COS> __device__ __forceinline__ float trig_of_16bit(float x) {
+    if (!(fabsf(x) < 100000.0f)) return WANT_COS ? cosf(x) : sinf(x);
+    const float j = __fmaf_rn(x, 0.636619747f, 12582912.0f);
+    const int n = __float_as_int(j) + WANT_COS;
+    const float jf = j - 12582912.0f;
+    float r = __fmaf_rn(jf, -1.57079601e+00f, x);
+    r = __fmaf_rn(jf, -3.13916473e-07f, r);
+    r = __fmaf_rn(jf, -5.39030253e-15f, r);
+    const float r2 = r * r;
+    float ps = __fmaf_rn(r2, -1.9515295891e-4f, 8.3321608736e-3f);
+    ps = __fmaf_rn(ps, r2, -1.6666654611e-1f);
+    float s = __fmaf_rn(r * r2, ps, r);
+    s = (r == 0.0f) ? r : s;  // sin(-0) is -0: the sum above would give +0
+    float pc = __fmaf_rn(r2, 2.443315711809948e-5f, -1.388731625493765e-3f);
+    pc = __fmaf_rn(pc, r2, 4.166664568298827e-2f);
+    pc = __fmaf_rn(pc, r2, -0.5f);
+    const float c = __fmaf_rn(pc, r2, 1.0f);
+    const float v = (n & 1) ? c : s;
+    return (n & 2) ? -v : v;
+}
+
+// Two fp32 values in one 64-bit register and the packed fp32 instructions of sm_100 (one instruction, two
+// results): the routines below are bound by how many instructions a warp can issue, not by the FMA pipe.
+struct F2 { unsigned long long v; };
+__device__ __forceinline__ F2 f2_pack(float lo, float hi) { F2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void f2_unpack(F2 a, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a.v)); }
+__device__ __forceinline__ F2 f2_splat(float c) { return f2_pack(c, c); }
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) { F2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v)); return r; }
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) { F2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) { F2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
+
+// trig_of_16bit for two arguments at once: the same operations in the same order (same bits), the floating-point
+// ones as packed instructions.
+template <int WANT_COS> __device__ __forceinline__ void trig_of_16bit_x2(float x0, float x1, float &y0, float &y1) {
+    if (!(fabsf(x0) < 100000.0f) || !(fabsf(x1) < 100000.0f)) {
+        y0 = trig_of_16bit<WANT_COS>(x0);
+        y1 = trig_of_16bit<WANT_COS>(x1);
+        return;
+    }
+    const F2 x = f2_pack(x0, x1);
+    const F2 j = f2_fma(x, f2_splat(0.636619747f), f2_splat(12582912.0f));
+    float j0, j1;
+    f2_unpack(j, j0, j1);
+    const int n0 = __float_as_int(j0) + WANT_COS, n1 = __float_as_int(j1) + WANT_COS;
+    const F2 jf = f2_add(j, f2_splat(-12582912.0f));
+    F2 r = f2_fma(jf, f2_splat(-1.57079601e+00f), x);
+    r = f2_fma(jf, f2_splat(-3.13916473e-07f), r);
+    r = f2_fma(jf, f2_splat(-5.39030253e-15f), r);
+    const F2 r2 = f2_mul(r, r);
+    F2 ps = f2_fma(r2, f2_splat(-1.9515295891e-4f), f2_splat(8.3321608736e-3f));
+    ps = f2_fma(ps, r2, f2_splat(-1.6666654611e-1f));
+    const F2 s = f2_fma(f2_mul(r, r2), ps, r);
+    F2 pc = f2_fma(r2, f2_splat(2.443315711809948e-5f), f2_splat(-1.388731625493765e-3f));
+    pc = f2_fma(pc, r2, f2_splat(4.166664568298827e-2f));
+    pc = f2_fma(pc, r2, f2_splat(-0.5f));
+    const F2 c = f2_fma(pc, r2, f2_splat(1.0f));
+    float s0, s1, c0, c1, r0, r1;
+    f2_unpack(s, s0, s1);
+    f2_unpack(c, c0, c1);
+    f2_unpack(r, r0, r1);
+    s0 = (r0 == 0.0f) ? r0 : s0;
+    s1 = (r1 == 0.0f) ? r1 : s1;
+    const float v0 = (n0 & 1) ? c0 : s0, v1 = (n1 & 1) ? c1 : s1;
+    y0 = (n0 & 2) ? -v0 : v0;
+    y1 = (n1 & 2) ? -v1 : v1;
+}
+
 template <int OP, typename T> struct UnaryFn {
     __device__ __forceinline__ T operator()(T a) const {
         if constexpr (OP == DX_INVERT) {
@@ -132,11 +206,29 @@ template <int OP, typename T> struct UnaryFn {
                 if constexpr (OP == DX_SQRT) r = sqrtf(x);  // IEEE (-prec-sqrt=true)
                 else if constexpr (OP == DX_LOG) r = logf(x);
                 else if constexpr (OP == DX_EXP) r = expf(x);
-                else if constexpr (OP == DX_SIN) r = sinf(x);
-                else if constexpr (OP == DX_COS) r = cosf(x);
+                else if constexpr (OP == DX_SIN) {
+                    if constexpr (std::is_same<T, f16>::value || std::is_same<T, bf16>::value) r = trig_of_16bit<0>(x);
+                    else r = sinf(x);
+                } else if constexpr (OP == DX_COS) {
+                    if constexpr (std::is_same<T, f16>::value || std::is_same<T, bf16>::value) r = trig_of_16bit<1>(x);
+                    else r = cosf(x);
+                }
                 else r = tanf(x);
             }
             return from_compute<T>(r);
+        }
+    }
+    // Two elements at once, for the ops that have a packed routine (the streaming kernel uses it when present).
+    static constexpr bool has_pair = (OP == DX_SIN || OP == DX_COS) && (std::is_same<T, f16>::value || std::is_same<T, bf16>::value);
+    __device__ __forceinline__ void pair(T a0, T a1, T &c0, T &c1) const {
+        if constexpr (has_pair) {
+            float y0, y1;
+            trig_of_16bit_x2<OP == DX_COS ? 1 : 0>(to_compute(a0), to_compute(a1), y0, y1);
+            c0 = from_compute<T>(y0);
+            c1 = from_compute<T>(y1);
+        } else {
+            c0 = (*this)(a0);
+            c1 = (*this)(a1);
         }
     }
 };

@@ -8,6 +8,9 @@
   truncation as round-to-nearest of (q·(1 + p) − copysign(0.5, q)) + 1.5·2^23, with q the IEEE quotient
   and p = 2^-17 for int16, q an approximate quotient (up to 2 ulp off) and p = 2^-12 for int8
                                                                      (trunc_pushed, small_int_to_float)
+* sin / cos of a 16-bit float in fp32 (quadrant by the magic number, three-constant reduction, Cephes
+  polynomials): within 1.5 fp32 ulp, and the same f16 as the C library's float routine for every f16 input
+                                                                     (trig_of_16bit, ew_ops.cuh)
 """
 import numpy as np
 
@@ -75,3 +78,54 @@ def test_small_int_to_float_through_the_magic_number():
     v = np.arange(-32768, 32768, dtype=np.int32)
     f = (np.int32(0x4B400000) + v).view(np.float32) - np.float32(12582912.0)
     assert np.array_equal(f, v.astype(np.float32))
+
+
+def _fma(a, b, c):
+    """fp32 fused multiply-add of arrays: the exact product of two floats fits a double."""
+    return (np.asarray(a, np.float32).astype(np.float64) * np.asarray(b, np.float32).astype(np.float64)
+            + np.asarray(c, np.float32).astype(np.float64)).astype(np.float32)
+
+
+def _trig_of_16bit(x, want_cos):
+    """trig_of_16bit (ew_ops.cuh) in numpy, for |x| < 1e5."""
+    f32 = np.float32
+    x = x.astype(f32)
+    magic = f32(12582912.0)
+    j = _fma(x, f32(0.636619747), magic)
+    n = j.view(np.int32).astype(np.int64) + int(want_cos)
+    jf = (j - magic).astype(f32)
+    r = _fma(jf, f32(-1.57079601e+00), x)
+    r = _fma(jf, f32(-3.13916473e-07), r)
+    r = _fma(jf, f32(-5.39030253e-15), r)
+    r2 = (r * r).astype(f32)
+    ps = _fma(r2, f32(-1.9515295891e-4), f32(8.3321608736e-3))
+    ps = _fma(ps, r2, f32(-1.6666654611e-1))
+    s = _fma((r * r2).astype(f32), ps, r)
+    s = np.where(r == 0, r, s)
+    pc = _fma(r2, f32(2.443315711809948e-5), f32(-1.388731625493765e-3))
+    pc = _fma(pc, r2, f32(4.166664568298827e-2))
+    pc = _fma(pc, r2, f32(-0.5))
+    c = _fma(pc, r2, f32(1.0))
+    v = np.where(n & 1, c, s)
+    return np.where(n & 2, -v, v).astype(f32)
+
+
+def test_trig_of_16bit_every_f16_argument():
+    h = np.arange(0, 65536, dtype=np.uint16).view(np.float16)
+    x = h[np.isfinite(h)].astype(np.float32)
+    for want_cos, ref in ((0, np.sin), (1, np.cos)):
+        got = _trig_of_16bit(x, want_cos)
+        exact = ref(x.astype(np.float64))
+        ulp = np.spacing(np.abs(exact).astype(np.float32)).astype(np.float64)
+        assert (np.abs(got.astype(np.float64) - exact) <= 1.5 * ulp).all()
+        assert np.array_equal(got.astype(np.float16).view(np.uint16), ref(x).astype(np.float16).view(np.uint16))  # the float routine, rounded
+
+
+def test_trig_of_16bit_every_bf16_argument_below_1e5():
+    b = (np.arange(0, 65536, dtype=np.uint32) << 16).view(np.float32)
+    x = b[np.isfinite(b) & (np.abs(b) < 1e5)]
+    for want_cos, ref in ((0, np.sin), (1, np.cos)):
+        got = _trig_of_16bit(x, want_cos)
+        exact = ref(x.astype(np.float64))
+        ulp = np.spacing(np.abs(exact).astype(np.float32)).astype(np.float64)
+        assert (np.abs(got.astype(np.float64) - exact) <= 1.5 * ulp).all()

@@ -200,6 +200,33 @@ def test_unary_math(mods, op, dtype):
         _close(got, want, dtype, f"{op}<{dtype}>")
 
 
+@pytest.mark.parametrize("op", ["sin", "cos"])
+def test_trig_of_every_16bit_pattern(mods, op):
+    """sin / cos of 16-bit floats run through the kernel's own fp32 routine: every finite float16 argument must
+    give the float16 the CPU oracle gives (the C library's float routine, rounded), bit for bit; every bfloat16
+    argument — huge ones, infinities and NaNs included, which take the library path — within one bfloat16 ulp
+    near the function's zeros and exactly elsewhere in all but a handful of cases."""
+    TF, O = mods
+    h = np.arange(0, 65536, dtype=np.uint16).view(np.float16)
+    h = h[np.isfinite(h)]
+    out = torch.empty(h.shape, dtype=torch.float16, device="cuda:0")
+    getattr(TF, op)(to_gpu(h), out)
+    assert_bit_exact(to_np(out), getattr(O, op)(h), f"{op}<float16> every finite argument")
+    bits = torch.arange(0, 65536, dtype=torch.int32).to(torch.int16).view(torch.bfloat16).cuda()
+    outb = torch.empty_like(bits)
+    getattr(TF, op)(bits, outb)
+    x = bits.float().cpu().numpy()
+    got = outb.float().cpu().numpy()
+    with np.errstate(invalid="ignore"):
+        exact = getattr(np, op)(x.astype(np.float64))
+    fin = np.isfinite(x)
+    assert np.isnan(got[~fin]).all()                      # sin(inf), sin(nan) are NaN
+    err = np.abs(got[fin].astype(np.float64) - exact[fin])
+    assert (err <= 2.0 ** -8 * np.abs(exact[fin]) + 1e-30).all()   # one bfloat16 ulp (half an ulp is the best possible)
+    want = torch.from_numpy(exact[fin].astype(np.float32)).to(torch.bfloat16).float().numpy()
+    assert (got[fin] != want).sum() <= 32                  # correctly rounded in all but a handful of cases
+
+
 @pytest.mark.parametrize("dtype", INTS + ["bool"])
 def test_invert(mods, dtype):
     TF, O = mods
