@@ -19,6 +19,9 @@ constexpr int EW_UNROLL = 4;
 // Whether a functor offers `pair(a0, a1, c0, c1)`, two elements per call (packed arithmetic inside).
 template <typename F, typename = void> struct functor_has_pair : std::false_type {};
 template <typename F> struct functor_has_pair<F, std::void_t<decltype(F::has_pair)>> : std::integral_constant<bool, F::has_pair> {};
+// ... and a cheap test on a whole input vector (`vector_is_plain`) after which `pair_plain` may replace `pair`.
+template <typename F, typename = void> struct functor_has_vector_check : std::false_type {};
+template <typename F> struct functor_has_vector_check<F, std::void_t<decltype(F::has_vector_check)>> : std::integral_constant<bool, F::has_vector_check> {};
 
 template <int VEC, typename TA, typename TC, typename F>
 __global__ void __launch_bounds__(EW_BLOCK) ew1_kernel(const TA *a, TC *c, int64_t n, F f) {
@@ -32,7 +35,15 @@ __global__ void __launch_bounds__(EW_BLOCK) ew1_kernel(const TA *a, TC *c, int64
 #pragma unroll
         for (int u = 0; u < EW_UNROLL; ++u) {
             Pack<TC, VEC> vc;
-            if constexpr (functor_has_pair<F>::value && VEC % 2 == 0) {
+            if constexpr (functor_has_pair<F>::value && functor_has_vector_check<F>::value && VEC % 2 == 0) {
+                if (F::template vector_is_plain<VEC>(va[u])) {
+#pragma unroll
+                    for (int i = 0; i < VEC; i += 2) f.pair_plain(va[u].v[i], va[u].v[i + 1], vc.v[i], vc.v[i + 1]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VEC; i += 2) f.pair(va[u].v[i], va[u].v[i + 1], vc.v[i], vc.v[i + 1]);
+                }
+            } else if constexpr (functor_has_pair<F>::value && VEC % 2 == 0) {
 #pragma unroll
                 for (int i = 0; i < VEC; i += 2) f.pair(va[u].v[i], va[u].v[i + 1], vc.v[i], vc.v[i + 1]);
             } else {

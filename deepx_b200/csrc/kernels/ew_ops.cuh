@@ -113,15 +113,16 @@ template <typename T> struct DivConstFn {
 };
 
 // ---- unary ---------------------------------------------------------------------
-// sin / cos for arguments that came from a 16-bit float, in fp32 to about 1.4 ulp (every finite f16 argument
+// sin / cos for arguments that came from a 16-bit float, in fp32 to about 1.8 ulp (every finite f16 argument
 // then rounds to the same f16 as the C library's sinf / cosf; checked on the CPU).  The library routine costs
 // about 30 instructions per element, two of them int<->float conversions on the quarter-rate unit, which
 // held these ops at 0.62–0.73 of the copy bandwidth (4 bytes of traffic per element).  Here: quadrant n =
 // nearest integer to x·2/π by adding 1.5·2^23 (its low mantissa bits are n), three-constant Cody–Waite
 // reduction with FMAs, one short polynomial each for sin and cos on [−π/4, π/4] (Cephes single-precision
-// coefficients), select and sign by n.  Beyond 1e5 (bf16 only), inf and nan take the library's full reduction.
-template <int WANT_COS> __device__ __forceinline__ float trig_of_16bit(float x) {
-    if (!(fabsf(x) < 100000.0f)) return WANT_COS ? cosf(x) : sinf(x);
+// coefficients), select and sign by n.  Beyond 1e5 (CHECK: bfloat16 only; float16 ends at 65504, and its
+// infinities and NaNs come out as NaN by themselves) the library's full reduction is used.
+template <int WANT_COS, bool CHECK> __device__ __forceinline__ float trig_of_16bit(float x) {
+    if (CHECK && !(fabsf(x) < 100000.0f)) return WANT_COS ? cosf(x) : sinf(x);
     const float j = __fmaf_rn(x, 0.636619747f, 12582912.0f);
     const int n = __float_as_int(j) + WANT_COS;
     const float jf = j - 12582912.0f;
@@ -131,8 +132,7 @@ template <int WANT_COS> __device__ __forceinline__ float trig_of_16bit(float x) 
     const float r2 = r * r;
     float ps = __fmaf_rn(r2, -1.9515295891e-4f, 8.3321608736e-3f);
     ps = __fmaf_rn(ps, r2, -1.6666654611e-1f);
-    float s = __fmaf_rn(r * r2, ps, r);
-    s = (r == 0.0f) ? r : s;  // sin(-0) is -0: the sum above would give +0
+    const float s = r * __fmaf_rn(r2, ps, 1.0f);  // as a product, so that sin(-0) is -0
     float pc = __fmaf_rn(r2, 2.443315711809948e-5f, -1.388731625493765e-3f);
     pc = __fmaf_rn(pc, r2, 4.166664568298827e-2f);
     pc = __fmaf_rn(pc, r2, -0.5f);
@@ -153,10 +153,10 @@ __device__ __forceinline__ F2 f2_add(F2 a, F2 b) { F2 r; asm("add.rn.f32x2 %0, %
 
 // trig_of_16bit for two arguments at once: the same operations in the same order (same bits), the floating-point
 // ones as packed instructions.
-template <int WANT_COS> __device__ __forceinline__ void trig_of_16bit_x2(float x0, float x1, float &y0, float &y1) {
-    if (!(fabsf(x0) < 100000.0f) || !(fabsf(x1) < 100000.0f)) {
-        y0 = trig_of_16bit<WANT_COS>(x0);
-        y1 = trig_of_16bit<WANT_COS>(x1);
+template <int WANT_COS, bool CHECK> __device__ __forceinline__ void trig_of_16bit_x2(float x0, float x1, float &y0, float &y1) {
+    if (CHECK && (!(fabsf(x0) < 100000.0f) || !(fabsf(x1) < 100000.0f))) {
+        y0 = trig_of_16bit<WANT_COS, CHECK>(x0);
+        y1 = trig_of_16bit<WANT_COS, CHECK>(x1);
         return;
     }
     const F2 x = f2_pack(x0, x1);
@@ -171,17 +171,14 @@ template <int WANT_COS> __device__ __forceinline__ void trig_of_16bit_x2(float x
     const F2 r2 = f2_mul(r, r);
     F2 ps = f2_fma(r2, f2_splat(-1.9515295891e-4f), f2_splat(8.3321608736e-3f));
     ps = f2_fma(ps, r2, f2_splat(-1.6666654611e-1f));
-    const F2 s = f2_fma(f2_mul(r, r2), ps, r);
+    const F2 s = f2_mul(r, f2_fma(r2, ps, f2_splat(1.0f)));
     F2 pc = f2_fma(r2, f2_splat(2.443315711809948e-5f), f2_splat(-1.388731625493765e-3f));
     pc = f2_fma(pc, r2, f2_splat(4.166664568298827e-2f));
     pc = f2_fma(pc, r2, f2_splat(-0.5f));
     const F2 c = f2_fma(pc, r2, f2_splat(1.0f));
-    float s0, s1, c0, c1, r0, r1;
+    float s0, s1, c0, c1;
     f2_unpack(s, s0, s1);
     f2_unpack(c, c0, c1);
-    f2_unpack(r, r0, r1);
-    s0 = (r0 == 0.0f) ? r0 : s0;
-    s1 = (r1 == 0.0f) ? r1 : s1;
     const float v0 = (n0 & 1) ? c0 : s0, v1 = (n1 & 1) ? c1 : s1;
     y0 = (n0 & 2) ? -v0 : v0;
     y1 = (n1 & 2) ? -v1 : v1;
@@ -245,10 +242,10 @@ template <int OP, typename T> struct UnaryFn {
                 }
                 else if constexpr (OP == DX_EXP) r = expf(x);
                 else if constexpr (OP == DX_SIN) {
-                    if constexpr (std::is_same<T, f16>::value || std::is_same<T, bf16>::value) r = trig_of_16bit<0>(x);
+                    if constexpr (std::is_same<T, f16>::value || std::is_same<T, bf16>::value) r = trig_of_16bit<0, std::is_same<T, bf16>::value>(x);
                     else r = sinf(x);
                 } else if constexpr (OP == DX_COS) {
-                    if constexpr (std::is_same<T, f16>::value || std::is_same<T, bf16>::value) r = trig_of_16bit<1>(x);
+                    if constexpr (std::is_same<T, f16>::value || std::is_same<T, bf16>::value) r = trig_of_16bit<1, std::is_same<T, bf16>::value>(x);
                     else r = cosf(x);
                 }
                 else r = tanf(x);
@@ -258,11 +255,28 @@ template <int OP, typename T> struct UnaryFn {
     }
     // Two elements at once, for the ops that have a packed routine (the streaming kernel uses it when present).
     static constexpr bool has_pair = (OP == DX_SIN || OP == DX_COS || OP == DX_LOG) && (std::is_same<T, f16>::value || std::is_same<T, bf16>::value);
-    __device__ __forceinline__ void pair(T a0, T a1, T &c0, T &c1) const {
+    __device__ __forceinline__ void pair(T a0, T a1, T &c0, T &c1) const { pair_impl<true>(a0, a1, c0, c1); }
+    // For a whole vector whose `vector_is_plain` check passed: the same results without the per-pair range check.
+    __device__ __forceinline__ void pair_plain(T a0, T a1, T &c0, T &c1) const { pair_impl<false>(a0, a1, c0, c1); }
+    // bfloat16 sin / cos: true when no element of the vector reaches 65536 in magnitude (nor is inf / NaN), decided
+    // on the raw bit patterns two at a time (adding 0x8000 − 0x4780 to each 15-bit magnitude carries into bit 15
+    // exactly when it is too large).  One test and one branch per vector instead of one per pair.
+    static constexpr bool has_vector_check = (OP == DX_SIN || OP == DX_COS) && std::is_same<T, bf16>::value;
+    template <int VEC> __device__ __forceinline__ static bool vector_is_plain(const Pack<T, VEC> &v) {
+        static_assert(VEC % 2 == 0, "whole 32-bit words");
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(&v);
+        uint32_t o = 0;
+#pragma unroll
+        for (int i = 0; i < VEC / 2; ++i) o |= (w[i] & 0x7fff7fffu) + 0x38803880u;  // bit 15 of a half: |pattern| >= 0x4780 (65536.0)
+        return (o & 0x80008000u) == 0;
+    }
+
+private:
+    template <bool CHECKED> __device__ __forceinline__ void pair_impl(T a0, T a1, T &c0, T &c1) const {
         if constexpr (has_pair) {
             float y0, y1;
             if constexpr (OP == DX_LOG) log_of_16bit_x2(to_compute(a0), to_compute(a1), y0, y1);
-            else trig_of_16bit_x2<OP == DX_COS ? 1 : 0>(to_compute(a0), to_compute(a1), y0, y1);
+            else trig_of_16bit_x2<OP == DX_COS ? 1 : 0, CHECKED && std::is_same<T, bf16>::value>(to_compute(a0), to_compute(a1), y0, y1);
             c0 = from_compute<T>(y0);
             c1 = from_compute<T>(y1);
         } else {
@@ -270,6 +284,8 @@ template <int OP, typename T> struct UnaryFn {
             c1 = (*this)(a1);
         }
     }
+
+public:
 };
 
 // ---- compare → 0/1 byte ------------------------------------------------------------

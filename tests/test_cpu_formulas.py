@@ -9,7 +9,7 @@
   and p = 2^-17 for int16, q an approximate quotient (up to 2 ulp off) and p = 2^-12 for int8
                                                                      (trunc_pushed, small_int_to_float)
 * sin / cos of a 16-bit float in fp32 (quadrant by the magic number, three-constant reduction, Cephes
-  polynomials): within 1.5 fp32 ulp, and the same f16 as the C library's float routine for every f16 input
+  polynomials): within 2 fp32 ulp, and the same f16 as the C library's float routine for every f16 input
                                                                      (trig_of_16bit, ew_ops.cuh)
 * log of a 16-bit float in fp32 (exponent split on the bits, Cephes polynomial): within 0.75 fp32 ulp
                                                                      (log_of_16bit_x2, ew_ops.cuh)
@@ -102,8 +102,7 @@ def _trig_of_16bit(x, want_cos):
     r2 = (r * r).astype(f32)
     ps = _fma(r2, f32(-1.9515295891e-4), f32(8.3321608736e-3))
     ps = _fma(ps, r2, f32(-1.6666654611e-1))
-    s = _fma((r * r2).astype(f32), ps, r)
-    s = np.where(r == 0, r, s)
+    s = (r * _fma(r2, ps, f32(1.0))).astype(f32)
     pc = _fma(r2, f32(2.443315711809948e-5), f32(-1.388731625493765e-3))
     pc = _fma(pc, r2, f32(4.166664568298827e-2))
     pc = _fma(pc, r2, f32(-0.5))
@@ -119,7 +118,7 @@ def test_trig_of_16bit_every_f16_argument():
         got = _trig_of_16bit(x, want_cos)
         exact = ref(x.astype(np.float64))
         ulp = np.spacing(np.abs(exact).astype(np.float32)).astype(np.float64)
-        assert (np.abs(got.astype(np.float64) - exact) <= 1.5 * ulp).all()
+        assert (np.abs(got.astype(np.float64) - exact) <= 2.0 * ulp).all()
         assert np.array_equal(got.astype(np.float16).view(np.uint16), ref(x).astype(np.float16).view(np.uint16))  # the float routine, rounded
 
 
@@ -130,7 +129,7 @@ def test_trig_of_16bit_every_bf16_argument_below_1e5():
         got = _trig_of_16bit(x, want_cos)
         exact = ref(x.astype(np.float64))
         ulp = np.spacing(np.abs(exact).astype(np.float32)).astype(np.float64)
-        assert (np.abs(got.astype(np.float64) - exact) <= 1.5 * ulp).all()
+        assert (np.abs(got.astype(np.float64) - exact) <= 2.0 * ulp).all()
 
 
 def _log_of_16bit(x):
