@@ -55,9 +55,55 @@ template <int K> static int pow_small(int dtype, const void *a, void *c, int64_t
     return launch_ew1((const float *)a, (float *)c, n, PowSmallFn<K, float>(), st, "ew_scalar");
 }
 
+// int8 ∘ scalar through a table: an int8 has 256 values, so division by a scalar (either way round) is one
+// shared-memory byte load per element from a table the host fills with the exact truncated quotients, instead
+// of unpacking, dividing and packing sixteen elements of every 16-byte vector.
+struct Int8Table {
+    int8_t t[256];
+};
+__global__ void __launch_bounds__(EW_BLOCK) i8_table_kernel(const int8_t *a, int8_t *c, int64_t n, const __grid_constant__ Int8Table tab) {
+    __shared__ int8_t sm[256];
+    sm[threadIdx.x] = tab.t[threadIdx.x];
+    static_assert(EW_BLOCK == 256, "one table entry per thread");
+    __syncthreads();
+    constexpr int VEC = 16;
+    constexpr int64_t TILE = int64_t(EW_BLOCK) * EW_UNROLL * VEC;
+    const int64_t base = int64_t(blockIdx.x) * TILE;
+    if (base + TILE <= n) {
+        Pack<int8_t, VEC> va[EW_UNROLL];
+#pragma unroll
+        for (int u = 0; u < EW_UNROLL; ++u) va[u] = ld_stream<int8_t, VEC>(a + base + (int64_t(u) * EW_BLOCK + threadIdx.x) * VEC);
+#pragma unroll
+        for (int u = 0; u < EW_UNROLL; ++u) {
+            Pack<int8_t, VEC> vc;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) vc.v[i] = sm[static_cast<uint8_t>(va[u].v[i])];
+            st_stream<int8_t, VEC>(c + base + (int64_t(u) * EW_BLOCK + threadIdx.x) * VEC, vc);
+        }
+    } else {
+        for (int64_t i = base + threadIdx.x; i < n; i += EW_BLOCK) c[i] = sm[static_cast<uint8_t>(a[i])];
+    }
+}
+// Division of every int8 value by d (reversed: of s by every int8 value); a zero divisor has no defined result in
+// the reference (elementwise_miaobyte.hpp:267, :307 divide without a check) and yields 0 here.
+static int launch_i8_division_table(const void *a, void *c, int64_t n, int scalar, bool reversed, cudaStream_t st) {
+    Int8Table tab;
+    for (int v = -128; v < 128; ++v) {
+        const int num = reversed ? scalar : v, den = reversed ? v : scalar;
+        tab.t[static_cast<uint8_t>(static_cast<int8_t>(v))] = den == 0 ? int8_t(0) : static_cast<int8_t>(num / den);  // -128 / -1 wraps like the kernels
+    }
+    int64_t grid;
+    if (int e = ew_grid(n, 16, &grid)) return e;
+    i8_table_kernel<<<(unsigned)grid, EW_BLOCK, 0, st>>>((const int8_t *)a, (int8_t *)c, n, tab);
+    return check_launch("ew_scalar");
+}
+
 extern "C" int dx_ew_scalar(int op, int dtype, const void *a, double fs, int64_t is, void *c, int64_t n,
                             void *stream) {
     cudaStream_t st = as_stream(stream);
+    if (dtype == DX_I8 && (op == DX_DIVS || op == DX_RDIVS) && n > 0 && a && c && aligned_to(a, 16) && aligned_to(c, 16) &&
+        int8_t(is) != 0)
+        return launch_i8_division_table(a, c, n, int(int8_t(is)), op == DX_RDIVS, st);
     if (op == DX_POWS && (dtype == DX_F32 || dtype == DX_F64)) {
         if (fs == 2.0) return pow_small<2>(dtype, a, c, n, st);
         if (fs == 1.0) return pow_small<1>(dtype, a, c, n, st);

@@ -148,6 +148,28 @@ def test_small_integer_division_is_exact(mods):
     assert_bit_exact(to_np(o16), O.rdivscalar(30000, nz), "rdivscalar<int16>")
 
 
+def test_int8_scalar_division_every_value_and_divisor(mods):
+    """int8 divided by a scalar and a scalar divided by int8 run through a 256-entry table (whole tiles and the
+    guarded tail of the kernel both): every value against every non-zero scalar, bit for bit."""
+    TF, O = mods
+    rng = np.random.default_rng(17)
+    vals = np.concatenate([np.arange(-128, 128, dtype=np.int8), rng.integers(-128, 128, 20000 - 256 + 37).astype(np.int8)])
+    nz = vals[vals != 0]
+    A, NZ = to_gpu(vals), to_gpu(nz)
+    out, outr = torch.empty_like(A), torch.empty_like(NZ)
+    for d in range(-128, 128):
+        if d == 0:
+            continue
+        TF.divscalar(A, d, out)
+        assert_bit_exact(to_np(out), O.divscalar(vals, d), f"divscalar<int8> by {d}")
+        TF.rdivscalar(d, NZ, outr)
+        assert_bit_exact(to_np(outr), O.rdivscalar(d, nz), f"rdivscalar<int8> {d} / x")
+    # in place, as the front end's div_ sends it
+    B = to_gpu(vals)
+    TF.divscalar(B, 7, B)
+    assert_bit_exact(to_np(B), O.divscalar(vals, 7), "divscalar<int8> in place")
+
+
 @pytest.mark.parametrize("dtype", ALL_NUMERIC)
 @pytest.mark.parametrize("op", ["addscalar", "subscalar", "rsubscalar", "mulscalar", "divscalar", "rdivscalar",
                                 "maxscalar", "minscalar"])
