@@ -1952,9 +1952,16 @@ int launch_pair_splitk(const T *A, const T *B, T *C, int64_t batch, int64_t M, i
     if (dev < 0 || dev >= 64) return fail(DX_E_CUDA, "matmul: device index %d out of range", dev);
     // the widest split whose clusters all run at once and whose slices keep at least 48 K blocks: the two
     // cluster barriers, the push and the late start cost about as much as 30 K blocks of main loop
+    // (DX_GEMM_PAIR_SPLITK=2|4 forces that many slices wherever the clusters fit and every slice gets a K block)
+    int forced = 0;
+    if (const char *e = std::getenv("DX_GEMM_PAIR_SPLITK")) forced = (e[0] == '2' || e[0] == '4') ? e[0] - '0' : 0;
     int ks = 0;
-    for (int cand = 4; cand >= 2 && !ks; cand >>= 1)
-        if (k_blocks / cand >= 48 && tiles <= pair_splitk_clusters<T>(dev, cand)) ks = cand;
+    if (forced) {
+        if (k_blocks >= forced && tiles <= pair_splitk_clusters<T>(dev, forced)) ks = forced;
+    } else {
+        for (int cand = 4; cand >= 2 && !ks; cand >>= 1)
+            if (k_blocks / cand >= 48 && tiles <= pair_splitk_clusters<T>(dev, cand)) ks = cand;
+    }
     if (!ks) return DX_E_UNSUPPORTED;
     int *status;
     {
@@ -2157,8 +2164,8 @@ extern "C" int dx_matmul(int dtype, const void *A, const void *B, void *C, int64
                 }
             }
             if (tma_ok && M > BM) {
-                static const bool psplit_on = [] { const char *e = std::getenv("DX_GEMM_PAIR_SPLITK"); return !(e && e[0] == '0'); }();
-                if (psplit_on) {
+                const char *psplit_env = std::getenv("DX_GEMM_PAIR_SPLITK");
+                if (!(psplit_env && psplit_env[0] == '0')) {
                     const int rc = dtype == DX_BF16 ? launch_pair_splitk<bf16>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, st)
                                                     : launch_pair_splitk<f16>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);
                     if (rc != DX_E_UNSUPPORTED) return rc;

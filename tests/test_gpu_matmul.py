@@ -286,12 +286,16 @@ def test_matmul_split_k_is_deterministic(mods):
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
 
 
+@pytest.mark.parametrize("slices", ["auto", "2", "4"])
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 @pytest.mark.parametrize("m", [129, 256, 300, 512, 700])
-def test_matmul_few_tile_rows_pair_split_k(mods, dtype, m):
+def test_matmul_few_tile_rows_pair_split_k(mods, monkeypatch, dtype, m, slices):
     """Two to four rows of 256 x 256 tiles and a long K: the cluster kernel that splits K over CTA pairs
-    (partials combined through distributed shared memory); ragged M, N and K, last K slice short."""
+    (partials combined through distributed shared memory); ragged M, N and K, last K slice short.  By itself the
+    kernel is chosen only for very long K; 2 and 4 slices are also forced on every shape that fits."""
     TF, O, N = mods
+    if slices != "auto":
+        monkeypatch.setenv("DX_GEMM_PAIR_SPLITK", slices)
     rng = np.random.default_rng(seed_of("pairsplitk", dtype, m))
     for Nn, K in [(256, 1024), (520, 2056), (4096, 4096), (1000, 1032), (264, 8192)]:
         a = make(rng, dtype, (m, K), -1.0, 1.0)
@@ -304,6 +308,7 @@ def test_matmul_few_tile_rows_pair_split_k(mods, dtype, m):
 
 def test_matmul_pair_split_k_is_deterministic_and_close_to_the_tile_kernel(mods, monkeypatch):
     TF, O, N = mods
+    monkeypatch.setenv("DX_GEMM_PAIR_SPLITK", "2")
     rng = np.random.default_rng(14)
     a = make(rng, "bfloat16", (512, 4096), -1.0, 1.0)
     b = make(rng, "bfloat16", (4096, 2048), -1.0, 1.0)
