@@ -485,6 +485,17 @@ __global__ void __launch_bounds__(CB) inner_repeat_kernel(const char *__restrict
     st_stream<E, VEC>(reinterpret_cast<E *>(out) + int64_t(v) * VEC, o);
 }
 
+// Byte-permute selector for output word `word` (bytes 4·word .. 4·word+3 of a 16-byte output vector) when elements of
+// ES bytes are each repeated R times: output byte b comes from source byte (b / (R·ES))·ES + b % ES.
+template <int ES, int R> __host__ __device__ constexpr uint32_t repeat_selector(int word) {
+    uint32_t sel = 0;
+    for (int j = 0; j < 4; ++j) {
+        const int b = 4 * word + j;
+        sel |= uint32_t((b / (R * ES)) * ES + b % ES) << (4 * j);
+    }
+    return sel;
+}
+
 // r a power of two: the VEC / R (at least one) source elements of an output vector are one aligned
 // load, expanded in registers.
 template <typename E, int R>
@@ -507,8 +518,19 @@ __global__ void __launch_bounds__(CB) inner_repeat_pow2_kernel(const char *__res
         const uint32_t v = v0 + k * CB;
         if (v < p.units) {
             Pack<E, VEC> o;
+            if constexpr (sizeof(E) <= 2) {
+                // 1- and 2-byte elements: the at most 8 source bytes sit in two words and every output word is one byte
+                // permute of them (left to the compiler this became an extract and an insert per byte: 0.61 of the copy rate)
+                unsigned long long raw = 0;
+                memcpy(&raw, &sv[k], sizeof(E) * M);
+                const uint32_t w0 = static_cast<uint32_t>(raw), w1 = static_cast<uint32_t>(raw >> 32);
+                uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) o.v[j] = sv[k].v[(j / R) < M ? (j / R) : 0];
+                for (int i = 0; i < 4; ++i) ow[i] = __byte_perm(w0, w1, repeat_selector<int(sizeof(E)), R>(i));
+            } else {
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) o.v[j] = sv[k].v[(j / R) < M ? (j / R) : 0];
+            }
             st_stream<E, VEC>(reinterpret_cast<E *>(out) + int64_t(v) * VEC, o);
         }
     }
