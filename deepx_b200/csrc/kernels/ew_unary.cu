@@ -81,7 +81,7 @@ template <typename E> struct SwitchTable {
 // NT > 0: exactly NT sources, all read as vectors up front (every load of a thread is in flight
 // before the first select); NT == 0: any number of sources, each element fetched from the source
 // its case names.  Both read each source sector once when the cases are mixed.
-template <int VEC, typename E, typename CT, int NT>
+template <int VEC, typename E, typename CT, int NT, int EW_UNROLL = dx::EW_UNROLL>
 __global__ void __launch_bounds__(EW_BLOCK)
     switch_kernel(SwitchTable<E> tab, int ntensors, const CT *cases, E *c, int64_t n) {
     constexpr int64_t TILE = int64_t(EW_BLOCK) * EW_UNROLL * VEC;
@@ -148,7 +148,14 @@ static int launch_switch(const void *const *tensors, int ntensors, const void *c
     constexpr int VEC = 16 / (sizeof(E) > sizeof(CT) ? sizeof(E) : sizeof(CT));
     al = al && aligned_to(cases, sizeof(CT) * VEC);
     int64_t grid;
-    if (al) {
+    if (al && sizeof(E) < sizeof(CT) && ntensors == 2) {
+        // narrow elements under wide cases: a thread's vector is only VEC = 16 / sizeof(CT) elements, so it takes
+        // twice as many vectors to keep as many bytes in flight as the other streaming kernels
+        constexpr int U = 2 * dx::EW_UNROLL;
+        grid = (n + int64_t(EW_BLOCK) * U * VEC - 1) / (int64_t(EW_BLOCK) * U * VEC);
+        if (grid > 0x7fffffffLL) return fail(DX_E_SHAPE, "switch: element count %lld too large for one launch", (long long)n);
+        switch_kernel<VEC, E, CT, 2, U><<<(unsigned)grid, EW_BLOCK, 0, st>>>(tab, ntensors, (const CT *)cases, (E *)c, n);
+    } else if (al) {
         if (int e = ew_grid(n, VEC, &grid)) return e;
         const unsigned g = (unsigned)grid;
         switch (ntensors) {
