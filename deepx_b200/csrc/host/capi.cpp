@@ -189,6 +189,27 @@ int dx_ir_parse(const char *ir_line, char *out, size_t cap) {
         return put(std::string("!") + e.what(), out, cap);
     }
 }
+int dx_ir_vector_i64(const char *ir_line, int arg_index, int64_t *out, int cap) {
+    try {
+        TF t;
+        t.parse(ir_line ? ir_line : "");
+        const std::vector<int64_t> v = t.vector_i64(arg_index);
+        if (int(v.size()) > cap) { g_err = "output array too small"; return -1; }
+        for (size_t i = 0; i < v.size(); ++i) out[i] = v[i];
+        return int(v.size());
+    } catch (const std::exception &e) {
+        g_err = e.what();
+        return -1;
+    }
+}
+int dx_ir_check_print_format(const char *format, int dtype, char *out, size_t cap) {
+    std::string fixed, why;
+    if (!checked_print_format(format ? format : "", precision_of_dx(dtype), fixed, why)) {
+        g_err = why;
+        return 1;
+    }
+    return put(fixed, out, cap) < 0 ? -1 : 0;
+}
 int dx_ir_dtype_roundtrip(const char *text, char *out, size_t cap) { return put(typedef_str(typedef_of(text ? text : "")), out, cap); }
 
 int dx_ir_plan_fusion(const char *program, const char *existing, char *out, size_t cap) {

@@ -1,4 +1,7 @@
 // deepxIR host core — see core.hpp.
+#include <cerrno>
+#include <climits>
+
 #include "core.hpp"
 #include "fusion.hpp"
 
@@ -528,9 +531,35 @@ std::vector<std::string> TF::vector_text(int idx, bool from_args) const {
     return out;
 }
 
+// The reference converts every item with to<int> = int(std::stof(text)) (dtype.hpp:15-25), which rounds
+// extents above 2^24 and is undefined from 2^31 on.  Text that is a plain integer is read exactly here
+// (the two agree wherever the reference's result is defined and exact); text with a '.', an exponent or
+// anything else still goes through std::stof.  Values outside the int64 range, or not finite, are refused.
+std::vector<int64_t> TF::vector_i64(int idx, bool from_args) const {
+    std::vector<int64_t> out;
+    for (const auto &item : vector_text(idx, from_args)) {
+        const char *b = item.c_str();
+        char *end = nullptr;
+        errno = 0;
+        const long long v = std::strtoll(b, &end, 10);
+        if (end != b && *end == 0) {
+            if (errno == ERANGE) throw std::invalid_argument("integer out of range: " + item);
+            out.push_back(v);
+            continue;
+        }
+        const float f = std::stof(item);
+        if (!(f > -9.2e18f && f < 9.2e18f)) throw std::invalid_argument("integer out of range: " + item);
+        out.push_back(int64_t(f));
+    }
+    return out;
+}
+
 std::vector<int> TF::vector_int(int idx, bool from_args) const {
     std::vector<int> out;
-    for (const auto &item : vector_text(idx, from_args)) out.push_back(int(std::stof(item)));  // to<int>, dtype.hpp:15-25
+    for (int64_t v : vector_i64(idx, from_args)) {
+        if (v < INT32_MIN || v > INT32_MAX) throw std::invalid_argument("integer out of range: " + std::to_string(v));
+        out.push_back(int(v));
+    }
     return out;
 }
 

@@ -185,7 +185,8 @@ class TF {
     int var_int(int idx, const Mem &mem, bool from_args = true) const { return int(var_f32(idx, mem, from_args)); }
     // getvector<T> (tf.hpp:129-158): strip [], split on single spaces
     std::vector<std::string> vector_text(int idx, bool from_args = true) const;
-    std::vector<int> vector_int(int idx, bool from_args = true) const;
+    std::vector<int> vector_int(int idx, bool from_args = true) const;       // axes, orders: must fit an int
+    std::vector<int64_t> vector_i64(int idx, bool from_args = true) const;   // extents, repeats: 64-bit, read exactly
     bool check_tensors(const std::vector<std::string> &names, const Mem &mem, std::string &error) const;  // tf.hpp:160-171
 
   protected:
@@ -219,6 +220,9 @@ class TfFactory {
     std::vector<std::string> order_;  // op names in registration order
     size_t count_ = 0;
 };
+
+// print's format argument, checked and normalised (ops.cpp); false + `error` when it is refused
+bool checked_print_format(const std::string &fmt, uint16_t dtype, std::string &out, std::string &error);
 
 int register_all(TfFactory &factory);   // the op table of executor/op-cuda/src/client/tfs.cpp
 int register_fused(TfFactory &factory); // rmsnorm / softmax: the single-kernel forms of the front end's op chains

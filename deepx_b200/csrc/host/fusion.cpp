@@ -115,11 +115,11 @@ struct Pass {
                         r.known = dx_code_of(t.returns[0].dtype.precision) >= 0;
                         r.prec = t.returns[0].dtype.precision;
                         if (has_reshape) r.shape = reshaped;
-                        else for (int v : t.vector_int(0)) r.shape.push_back(v);
+                        else for (int64_t v : t.vector_i64(0)) r.shape.push_back(v);
                         return r;
                     }
                     if (t.name == "reshape" && ret0 && !has_reshape && t.args.size() == 2) {
-                        for (int v : t.vector_int(1)) reshaped.push_back(v);
+                        for (int64_t v : t.vector_i64(1)) reshaped.push_back(v);
                         has_reshape = true;
                     }
                 } catch (const std::exception &) {
@@ -162,7 +162,7 @@ struct Pass {
     }
     static bool shape_arg_is(const TF &t, const std::vector<int64_t> &want) {
         try {
-            const std::vector<int> s = t.vector_int(1);
+            const std::vector<int64_t> s = t.vector_i64(1);
             if (s.size() != want.size()) return false;
             for (size_t i = 0; i < s.size(); ++i)
                 if (s[i] != want[i]) return false;

@@ -216,7 +216,17 @@ struct dx_heap {
         }
     }
 
+    // Names, dtypes and node names go into JSON replies and hash keys as they are: refuse the
+    // characters that would need escaping there instead of emitting text a client mis-parses.
+    static bool plain_text(const std::string &s) {
+        for (unsigned char ch : s)
+            if (ch < 0x20 || ch == '"' || ch == '\\' || ch == 0x7f) return false;
+        return true;
+    }
+
     int handle(const Command &c, std::string *reply) {
+        if (!plain_text(c.name) || !plain_text(c.dtype) || !plain_text(c.node))
+            return fail(-3, "name, dtype and node must not contain quotes, backslashes or control characters");
         std::lock_guard<std::mutex> lk(store.mu);
         auto it = store.hashes.find(key(c.name));
         if (c.op == "create") {
@@ -234,18 +244,20 @@ struct dx_heap {
             size_t n = 1;
             for (auto d : c.shape) {
                 if (d < 0) return fail(-2, "create: negative extent");
-                n *= size_t(d);
+                if (__builtin_mul_overflow(n, size_t(d), &n)) return fail(-2, "create: shape " + shape_text(c.shape) + " overflows the address space");
             }
+            size_t nbytes = 0;
+            if (__builtin_mul_overflow(n, size_t(es), &nbytes)) return fail(-2, "create: shape " + shape_text(c.shape) + " overflows the address space");
             void *ptr = nullptr;
             std::string hex;
-            if (int e = allocate(c.device, n * size_t(es), &ptr, &hex)) return e;
+            if (int e = allocate(c.device, nbytes, &ptr, &hex)) return e;
             Hash h;
             h["dtype"] = c.dtype;
             h["shape"] = shape_text(c.shape);
             h["ctime"] = std::to_string(std::chrono::duration_cast<std::chrono::seconds>(std::chrono::system_clock::now().time_since_epoch()).count());
             h["node"] = c.node.empty() ? node : c.node;
             h["device"] = std::to_string(c.device);
-            h["bytes"] = std::to_string(n * size_t(es));
+            h["bytes"] = std::to_string(nbytes);
             h["ipc_handle"] = hex;
             h["refcount"] = "1";
             h["state"] = "ready";
@@ -395,8 +407,11 @@ void *dx_heap_open(const char *ipc_handle_hex, int device) {
         return nullptr;
     }
     void *ptr = nullptr;
+    int prev = -1;
+    cudaGetDevice(&prev);
     cudaError_t e = cudaSetDevice(device);
     if (e == cudaSuccess) e = cudaIpcOpenMemHandle(&ptr, hd, cudaIpcMemLazyEnablePeerAccess);
+    if (prev >= 0 && prev != device) cudaSetDevice(prev);  // the caller's current device is left as it was
     if (e != cudaSuccess) {
         fail(-4, std::string("cudaIpcOpenMemHandle: ") + cudaGetErrorString(e));
         return nullptr;

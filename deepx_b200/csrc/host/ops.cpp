@@ -6,6 +6,7 @@
 // into the kernel C ABI with the tensor's dtype code instead of a 9-way switch over C++ types.
 #include <cuda_runtime.h>
 
+#include <cctype>
 #include <cstdio>
 #include <cstring>
 #include <fstream>
@@ -235,10 +236,9 @@ struct ReshapeTF : TF {  // :17-83; tensorfunc changeshape_miaobyte.hpp:17-42
     DX_TF_BOILERPLATE(ReshapeTF)
     int run(Mem &mem, std::string &error) override {
         auto A = mem.get_tensor(args[0].textvalue);
-        const std::vector<int> shp = vector_int(1);
+        const std::vector<int64_t> ns = vector_i64(1);
         auto B = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != B->shape.dtype) { error = type_mismatch({A->shape.dtype, B->shape.dtype}); return 1; }
-        std::vector<int64_t> ns(shp.begin(), shp.end());
         int64_t prod = 1;
         for (auto v : ns) prod *= v;
         if (A->shape.size != prod) throw std::invalid_argument("Shape size mismatch");
@@ -315,10 +315,9 @@ struct BroadcastToTF : TF {  // :289-353
     DX_TF_BOILERPLATE(BroadcastToTF)
     int run(Mem &mem, std::string &error) override {
         auto A = mem.get_tensor(args[0].textvalue);
-        const std::vector<int> shp = vector_int(1);
+        const std::vector<int64_t> ns = vector_i64(1);
         auto B = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != B->shape.dtype) { error = type_mismatch({A->shape.dtype, B->shape.dtype}); return 1; }
-        const std::vector<int64_t> ns(shp.begin(), shp.end());
         const auto bs = broadcast_shape(A->shape.shape, ns);
         if (bs.empty() || bs != ns || B->shape.shape != ns) throw TensorShapeError("Broadcast shape mismatch");
         Staged st(mem, B, A->data == B->data);
@@ -360,10 +359,9 @@ struct RepeatTF : TF {  // :501-566
     DX_TF_BOILERPLATE(RepeatTF)
     int run(Mem &mem, std::string &error) override {
         auto A = mem.get_tensor(args[0].textvalue);
-        const std::vector<int> rep = vector_int(1);
+        const std::vector<int64_t> r64 = vector_i64(1);
         auto B = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != B->shape.dtype) { error = type_mismatch({A->shape.dtype, B->shape.dtype}); return 1; }
-        const std::vector<int64_t> r64(rep.begin(), rep.end());
         if (repeat_shape(A->shape.shape, r64) != B->shape.shape) throw TensorShapeError("Repeat shape mismatch");
         Staged st(mem, B, A->data == B->data);
         dx_check(dx_repeat(A->dx(), A->data, A->shape.shape.data(), A->shape.dim(), r64.data(), st.dst(), mem.stream()));
@@ -402,7 +400,9 @@ struct NewTensorTF : TF {
     int run(Mem &mem, std::string &error) override {
         const TypeDef type = returns[0].dtype;
         if ((type.category & CAT_TENSOR) == 0) { error = "newtensor: return type must include tensor category"; return 1; }
-        const std::vector<int> shp = vector_int(0);
+        const std::vector<int64_t> shp = vector_i64(0);
+        for (int64_t d : shp)
+            if (d < 0) { error = "newtensor: negative extent"; return 1; }
         switch (type.precision) {
             case P_F8E5M2: error = "newtensor: Float8E5M2 has not been implemented,if you need it, please contact the author"; return 1;
             case P_F8E4M3: error = "newtensor: Float8E4M3 has not been implemented,if you need it, please contact the author"; return 1;
@@ -411,7 +411,7 @@ struct NewTensorTF : TF {
             default: break;
         }
         if (dx_code_of(type.precision) < 0) { error = "newtensor: unsupported precision"; return 1; }
-        mem.new_tensor(returns[0].textvalue, type.precision, std::vector<int64_t>(shp.begin(), shp.end()));  // one allocation, no copy
+        mem.new_tensor(returns[0].textvalue, type.precision, shp);  // one allocation, no copy
         return 0;
     }
 };
@@ -547,13 +547,56 @@ float half_bits_to_float(uint16_t h) {
     return f;
 }
 
+}  // namespace
+
+// The print format arrives in a datagram and would be handed to printf: only a format with exactly one
+// numeric conversion is accepted (flags, width, precision, one of d i u x X o for integer and bool
+// tensors, f F e E g G for floating ones; "%%" is literal text).  %s, %n, %c, %p, '*' widths and a second
+// conversion are refused.  Whatever length modifier the caller wrote is replaced by the one that matches
+// what print_element passes (long long for int64, int otherwise, double for floats), so the argument
+// always has the type the conversion reads.  The reference passes the text through unchecked
+// (executor/deepxcore/src/stdutil/print.hpp:13-57).
+bool checked_print_format(const std::string &fmt, uint16_t dtype, std::string &out, std::string &error) {
+    const bool is_float = (dtype & P_FLOAT) != 0;
+    out.clear();
+    int conversions = 0;
+    for (size_t i = 0; i < fmt.size(); ++i) {
+        if (fmt[i] != '%') { out += fmt[i]; continue; }
+        if (i + 1 < fmt.size() && fmt[i + 1] == '%') { out += "%%"; ++i; continue; }
+        size_t j = i + 1;
+        while (j < fmt.size() && std::strchr("-+ #0", fmt[j])) ++j;
+        while (j < fmt.size() && std::isdigit(static_cast<unsigned char>(fmt[j]))) ++j;
+        if (j < fmt.size() && fmt[j] == '.') {
+            ++j;
+            while (j < fmt.size() && std::isdigit(static_cast<unsigned char>(fmt[j]))) ++j;
+        }
+        const size_t spec_end = j;  // flags, width, precision
+        while (j < fmt.size() && std::strchr("hlLqjzt", fmt[j])) ++j;
+        if (j >= fmt.size()) { error = "print: incomplete conversion in format '" + fmt + "'"; return false; }
+        const char conv = fmt[j];
+        const bool int_conv = std::strchr("diuxXo", conv) != nullptr, float_conv = std::strchr("fFeEgG", conv) != nullptr;
+        if (!int_conv && !float_conv) { error = std::string("print: conversion '%") + conv + "' is not allowed (numeric conversions only)"; return false; }
+        if (int_conv == is_float) { error = std::string("print: conversion '%") + conv + "' does not fit a " + precision_str(dtype) + " tensor"; return false; }
+        if (++conversions > 1) { error = "print: the format must hold exactly one conversion"; return false; }
+        if (spec_end - i > 10) { error = "print: width or precision too long"; return false; }
+        out += fmt.substr(i, spec_end - i);
+        if (int_conv && dtype == P_I64) out += "ll";
+        out += conv;
+        i = j;
+    }
+    if (conversions != 1) { error = "print: the format must hold exactly one conversion"; return false; }
+    return true;
+}
+
+namespace {
+
 void print_element(const char *data, int64_t i, uint16_t dtype, const std::string &fmt) {  // stdutil/print.hpp:13-57
     switch (dtype) {
         case P_BOOL: std::printf(fmt.c_str(), int(reinterpret_cast<const uint8_t *>(data)[i])); break;
         case P_I8: std::printf(fmt.c_str(), int(reinterpret_cast<const int8_t *>(data)[i])); break;
         case P_I16: std::printf(fmt.c_str(), int(reinterpret_cast<const int16_t *>(data)[i])); break;
         case P_I32: std::printf(fmt.c_str(), reinterpret_cast<const int32_t *>(data)[i]); break;
-        case P_I64: std::printf(fmt.c_str(), reinterpret_cast<const int64_t *>(data)[i]); break;
+        case P_I64: std::printf(fmt.c_str(), (long long)reinterpret_cast<const int64_t *>(data)[i]); break;
         case P_F64: std::printf(fmt.c_str(), reinterpret_cast<const double *>(data)[i]); break;
         case P_F32: std::printf(fmt.c_str(), double(reinterpret_cast<const float *>(data)[i])); break;
         case P_F16: std::printf(fmt.c_str(), double(half_bits_to_float(reinterpret_cast<const uint16_t *>(data)[i]))); break;
@@ -575,9 +618,10 @@ struct PrintTF : TF {  // tf/io.hpp:17-99, layout of stdutil/print.hpp:84-129
     int run(Mem &mem, std::string &error) override {
         if (!check_tensors({args[0].textvalue}, mem, error)) return 1;
         auto T = mem.get_tensor(args[0].textvalue);
-        std::string fmt = args.size() > 1 ? args[1].textvalue : "";
-        if (fmt.empty()) fmt = (T->shape.dtype & P_FLOAT) ? "%.4f" : "%d";
-        if (T->shape.dtype == P_I64 && fmt == "%d") fmt = "%ld";
+        std::string asked = args.size() > 1 ? args[1].textvalue : "";
+        if (asked.empty()) asked = (T->shape.dtype & P_FLOAT) ? "%.4f" : "%d";
+        std::string fmt;
+        if (!checked_print_format(asked, T->shape.dtype, fmt, error)) return 1;
         const std::vector<char> host = download(mem, *T);
         const Shape &s = T->shape;
         std::printf("shape:[");

@@ -146,8 +146,10 @@ extern "C" dx_comm *dx_comm_create(int rank, int world, int device) {
         fail(DX_E_ARG, "comm: rank %d of %d (at most %d ranks)", rank, world, COMM_MAX_WORLD);
         return nullptr;
     }
-    if (cudaSetDevice(device) != cudaSuccess) {
-        fail(DX_E_CUDA, "comm: cudaSetDevice(%d): %s", device, cudaGetErrorString(cudaGetLastError()));
+    DeviceGuard guard(device);  // the caller's current device is left as it was
+    int now = -1;
+    if (cudaGetDevice(&now) != cudaSuccess || now != device) {
+        fail(DX_E_CUDA, "comm: cannot make device %d current: %s", device, cudaGetErrorString(cudaGetLastError()));
         return nullptr;
     }
     dx_comm *c = new (std::nothrow) dx_comm();
@@ -177,7 +179,7 @@ extern "C" int dx_comm_handle(dx_comm *c, unsigned char out[64]) {
 
 extern "C" int dx_comm_connect(dx_comm *c, const unsigned char *handles) {
     if (!c || !handles) return fail(DX_E_ARG, "comm: null argument");
-    if (cudaSetDevice(c->device) != cudaSuccess) return fail(DX_E_CUDA, "comm: cudaSetDevice failed");
+    DeviceGuard guard(c->device);
     for (int r = 0; r < c->world; ++r) {
         if (r == c->rank || c->opened[r]) continue;
         cudaIpcMemHandle_t h;
@@ -235,7 +237,7 @@ extern "C" int dx_comm_status(dx_comm *c, void *stream) {
 
 extern "C" void dx_comm_destroy(dx_comm *c) {
     if (!c) return;
-    cudaSetDevice(c->device);
+    DeviceGuard guard(c->device);
     for (int r = 0; r < c->world; ++r)
         if (c->opened[r]) cudaIpcCloseMemHandle(c->peers.box[r]);
     if (c->emulated.empty()) cudaFree(c->mine);
@@ -248,8 +250,10 @@ extern "C" dx_comm *dx_comm_emulate(int world, int device) {
         fail(DX_E_ARG, "comm: %d ranks (at most %d)", world, COMM_MAX_WORLD);
         return nullptr;
     }
-    if (cudaSetDevice(device) != cudaSuccess) {
-        fail(DX_E_CUDA, "comm: cudaSetDevice(%d) failed", device);
+    DeviceGuard guard(device);
+    int now = -1;
+    if (cudaGetDevice(&now) != cudaSuccess || now != device) {
+        fail(DX_E_CUDA, "comm: cannot make device %d current", device);
         return nullptr;
     }
     dx_comm *c = new (std::nothrow) dx_comm();

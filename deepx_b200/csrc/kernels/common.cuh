@@ -113,6 +113,18 @@ template <typename T, int N> __device__ __forceinline__ Pack<T, N> ld_cached(con
     return *reinterpret_cast<const Pack<T, N> *>(p);
 }
 
+// Makes `dev` the current device for a scope and puts the caller's device back afterwards.
+struct DeviceGuard {
+    int prev = -1;
+    bool changed = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) changed = cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() {
+        if (changed) cudaSetDevice(prev);
+    }
+};
+
 inline bool aligned_to(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 // ---- 32-bit fast division by a runtime constant (Granlund–Montgomery) -------------

@@ -31,23 +31,13 @@ struct dx_pool {
 };
 
 namespace {
+using dx::DeviceGuard;
 
 size_t round_size(size_t b) {
     if (b == 0) b = 1;
     if (b <= (1u << 20)) return (b + 511) / 512 * 512;          // small: 512-byte classes
     return (b + (2u << 20) - 1) / (2u << 20) * (2u << 20);      // large: 2 MiB granules
 }
-
-struct DeviceGuard {
-    int prev = -1;
-    bool changed = false;
-    explicit DeviceGuard(int dev) {
-        if (cudaGetDevice(&prev) == cudaSuccess && prev != dev) changed = cudaSetDevice(dev) == cudaSuccess;
-    }
-    ~DeviceGuard() {
-        if (changed) cudaSetDevice(prev);
-    }
-};
 
 void release_cached(dx_pool *p) {
     for (auto &kv : p->free_blocks) {

@@ -767,6 +767,12 @@ extern "C" int dx_reduce_noalloc(int op, int dtype, const void *a, const int64_t
         // First call on a device: resolve where the array lives on THAT device (it must be current).
         std::lock_guard<std::mutex> lk(g_static_mu);
         if (!g_static_ptr[dev]) {
+            // The lookup below is not a stream operation and must not happen while this stream is being
+            // captured into a graph: the first call on a device has to come before any capture.
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(as_stream(stream), &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+                return fail(DX_E_ARG, "reduce (no-alloc): the first call on a device resolves the scratch address and cannot run "
+                                      "inside a stream capture; call it once on this device before capturing");
             void *p = nullptr;
             cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
             if (e != cudaSuccess || !p)

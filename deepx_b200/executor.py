@@ -37,6 +37,8 @@ SIGNATURES = {
     "dx_exec_stats": (None, [_vp, C.POINTER(C.c_size_t)]),
     "dx_ir_parse": (_i, [_cp, C.c_char_p, _sz]),
     "dx_ir_dtype_roundtrip": (_i, [_cp, C.c_char_p, _sz]),
+    "dx_ir_vector_i64": (_i, [_cp, _i, C.POINTER(C.c_int64), _i]),
+    "dx_ir_check_print_format": (_i, [_cp, _i, C.c_char_p, _sz]),
     "dx_ir_plan_fusion": (_i, [_cp, _cp, C.c_char_p, _sz]),
     "dx_registry_new": (_vp, [_i]),
     "dx_registry_free": (None, [_vp]),
@@ -79,6 +81,24 @@ def parse_ir(line: str) -> str:
 def dtype_roundtrip(text: str) -> str:
     buf = C.create_string_buffer(4096)
     lib().dx_ir_dtype_roundtrip(text.encode(), buf, len(buf))
+    return buf.value.decode()
+
+
+def vector_i64(ir_line: str, arg_index: int) -> list[int]:
+    """The integer vector argument `arg_index` of an IR line as the executor reads it (64-bit)."""
+    out = (C.c_int64 * 64)()
+    n = lib().dx_ir_vector_i64(ir_line.encode(), arg_index, out, 64)
+    if n < 0:
+        raise ValueError(lib().dx_exec_last_error().decode())
+    return [int(out[i]) for i in range(n)]
+
+
+def check_print_format(fmt: str, dtype_code: int) -> str:
+    """The format `print` would use for a tensor of that dtype; ValueError when it is refused."""
+    buf = C.create_string_buffer(256)
+    rc = lib().dx_ir_check_print_format(fmt.encode(), dtype_code, buf, len(buf))
+    if rc != 0:
+        raise ValueError(lib().dx_exec_last_error().decode())
     return buf.value.decode()
 
 

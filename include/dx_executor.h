@@ -9,6 +9,12 @@
  * `deepx-op-b200` binary is exactly this behind a UDP socket.  The upload/download calls are the
  * in-process stand-in for the on-disk tensor exchange (save/load IR ops work too).
  * All functions return 0 on success and a negative value on failure unless stated otherwise.
+ *
+ * Threads: an executor handle is for ONE thread at a time, as the reference's executor has one
+ * worker thread (main.cpp:25,74,93).  dx_exec_run serialises itself, but upload / download / bind /
+ * tensor_info / compile touch the tensor store and the compute stream without a lock, and a program
+ * being compiled keeps a stream capture open across several internal runs: do not call into the
+ * same handle from a second thread meanwhile.  Different handles are independent.
  */
 #ifndef DX_EXECUTOR_H
 #define DX_EXECUTOR_H
@@ -93,6 +99,14 @@ void dx_exec_stats(dx_exec *e, size_t stats[5]);
  * "<name>|<arg dtype>:<arg text>,…|<ret dtype>:<ret text>,…|author=<a> id=<n> repeat=<n>", or "!<error>". */
 int dx_ir_parse(const char *ir_line, char *out, size_t cap);
 int dx_ir_dtype_roundtrip(const char *text, char *out, size_t cap);
+/* The integer vector argument `arg_index` of an IR line (extents, repeats) as the executor reads it:
+ * 64-bit, plain integer text exactly, other numeric text through std::stof as the reference's to<int>
+ * does (executor/deepxcore/src/deepx/dtype.hpp:15-25).  Returns the count, or -1 (dx_exec_last_error). */
+int dx_ir_vector_i64(const char *ir_line, int arg_index, int64_t *out, int cap);
+/* print's format argument (executor/deepxcore/src/stdutil/print.hpp:13-57 hands it to printf unchecked):
+ * accepted only with exactly one numeric conversion that fits the tensor's dtype; `out` gets the format
+ * actually used (length modifier normalised).  0 = accepted, 1 = refused (dx_exec_last_error says why). */
+int dx_ir_check_print_format(const char *format, int dtype, char *out, size_t cap);
 /* The fusion pass alone, no GPU needed.  `existing` lists tensors that exist before the program,
  * one per line as "<name> <dtype name> <d0> <d1> …" (may be NULL or empty).  Writes one line per
  * program line: "run", "absorbed <group>" or "fused <group> <the op that runs instead>".

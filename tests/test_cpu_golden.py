@@ -286,3 +286,34 @@ def test_parser_vs_reference_library_fuzz(E):
         line += str(rng.choice(metas))
         ref.ref_parse_ir(line.encode(), buf, len(buf))
         assert E.parse_ir(line) == buf.value.decode(), line
+
+
+def test_integer_vectors_are_read_exactly_up_to_int64():
+    """Extents in IR text: the reference's to<int> (int(std::stof(text)), dtype.hpp:15-25) rounds above 2^24
+    and is undefined from 2^31; plain integer text is read exactly here, float text as the reference does."""
+    from deepx_b200 import executor as E
+    line = "newtensor(vector<int32>:[16777217 3000000000 7 2.0 1e3])->(tensor<float32>:t)"
+    assert E.vector_i64(line, 0) == [16777217, 3000000000, 7, 2, 1000]
+    assert E.vector_i64("reshape(tensor<float32>:a, vector<int32>:[2048 1048576])->(tensor<float32>:b)", 1) == [2048, 1048576]
+    assert E.vector_i64("newtensor(vector<int32>:[-3 4])->(tensor<float32>:t)", 0) == [-3, 4]   # the op, not the parser, refuses it
+    for bad in ("[99999999999999999999]", "[1e30]", "[nan]"):
+        with pytest.raises(ValueError):
+            E.vector_i64(f"newtensor(vector<int32>:{bad})->(tensor<float32>:t)", 0)
+
+
+def test_print_format_is_checked_before_it_reaches_printf():
+    """`print(t, format)` arrives in a datagram; only one numeric conversion that fits the dtype is let through."""
+    from deepx_b200 import executor as E
+    F32, I64, I32, BOOL = 1, 4, 5, 8
+    assert E.check_print_format("%.4f", F32) == "%.4f"
+    assert E.check_print_format("%8.3e", F32) == "%8.3e"
+    assert E.check_print_format("%lf", F32) == "%f"
+    assert E.check_print_format("%d", I32) == "%d"
+    assert E.check_print_format("%d", I64) == "%lld"         # the argument is a long long: the modifier is supplied
+    assert E.check_print_format("%ld", I32) == "%d"          # and removed where the argument is an int
+    assert E.check_print_format("[%5x]", I32) == "[%5x]"
+    assert E.check_print_format("%d%%", BOOL) == "%d%%"
+    for fmt, code in (("%s", F32), ("%n", I32), ("%s%n%n%n", I32), ("%d %d", I32), ("%*d", I32), ("%c", I32), ("%p", I64),
+                      ("%d", F32), ("%f", I32), ("no conversion", F32), ("%", F32), ("%.4", F32), ("%999999999999999999999d", I32)):
+        with pytest.raises(ValueError):
+            E.check_print_format(fmt, code)

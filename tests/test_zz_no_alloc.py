@@ -56,15 +56,53 @@ def test_noalloc_matches_dx_reduce_on_consecutive_calls():
 
 def test_noalloc_rejects_shapes_beyond_its_scratch():
     from deepx_b200 import _native as N
-    # 151424 = 1183 column strips of 128 floats: too few strips to fill the GPU, so the rows are split
-    # in two and the partials (2 x 151424 x 4 bytes) exceed the 1 MiB built-in scratch.
-    a = torch.zeros((1024, 151424), dtype=torch.float32, device="cuda:0")
+    # Which shapes need more than the 1 MiB built-in scratch depends on how many thread blocks of the
+    # kernel fit on this GPU, so the shape is found by asking the planner: column reductions of 1-byte
+    # elements (16 outputs per vector, 4-byte partials) are the ones whose partials grow largest.
+    limit = 1 << 20
+    found = None
+    for rows in (4096, 8192, 16384, 65536):
+        for strips in (37, 55, 74, 111, 148, 222, 296):
+            cols = strips * 512
+            shape, cd = N.i64_array((rows, cols)), N.i32_array([0])
+            for op in (N.SUM, N.RMAX):
+                need = N.lib.dx_reduce_workspace_bytes(op, N.I8, shape, 2, cd, 1)
+                if need > limit and found is None:
+                    found = (op, rows, cols, need)
+    assert found is not None, "no candidate shape needs more than the built-in scratch on this device"
+    op, rows, cols, need = found
+    a = torch.zeros((rows, cols), dtype=torch.int8, device="cuda:0")
+    out = torch.full((cols,), 5, dtype=torch.int8, device="cuda:0")
     shape, cd = N.i64_array(a.shape), N.i32_array([0])
-    need = N.lib.dx_reduce_workspace_bytes(N.SUM, N.F32, shape, 2, cd, 1)
-    if need <= (1 << 20):
-        pytest.skip(f"this device's plan needs only {need} bytes here")
-    out = torch.empty(151424, dtype=torch.float32, device="cuda:0")
-    rc = N.lib.dx_reduce_noalloc(N.SUM, N.F32, a.data_ptr(), shape, 2, cd, 1, out.data_ptr(), None)
+    rc = N.lib.dx_reduce_noalloc(op, N.I8, a.data_ptr(), shape, 2, cd, 1, out.data_ptr(), None)
     assert rc == N.E_WORKSPACE
     msg = N.lib.dx_last_error().decode()
     assert "1048576" in msg and "scratch" in msg, msg
+    torch.cuda.synchronize()
+    assert bool((out == 5).all()), "a refused call must not touch the output"
+    # the same shape through dx_reduce with a caller workspace works
+    ws = torch.empty(int(need), dtype=torch.uint8, device="cuda:0")
+    N.check(N.lib.dx_reduce(op, N.I8, a.data_ptr(), shape, 2, cd, 1, out.data_ptr(), ws.data_ptr(), ws.numel(), None))
+    torch.cuda.synchronize()
+    assert bool((out == 0).all())
+
+
+def test_noalloc_first_call_inside_a_capture_is_refused_cleanly():
+    """The set-up of the first call per device is not a stream operation.  Whether this process has
+    already made that call depends on test order, so only the contract is checked: inside a capture the
+    entry point either works (set-up already done) or returns an argument error, and the capture survives."""
+    from deepx_b200 import _native as N
+    a = torch.ones((4, 1 << 16), dtype=torch.float32, device="cuda:0")
+    out = torch.empty(4, dtype=torch.float32, device="cuda:0")
+    shape, cd = N.i64_array(a.shape), N.i32_array([1])
+    N.check(N.lib.dx_reduce_noalloc(N.SUM, N.F32, a.data_ptr(), shape, 2, cd, 1, out.data_ptr(), None))  # set-up done here
+    torch.cuda.synchronize()
+    st = torch.cuda.Stream()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=st):
+        rc = N.lib.dx_reduce_noalloc(N.SUM, N.F32, a.data_ptr(), shape, 2, cd, 1, out.data_ptr(), st.cuda_stream)
+    assert rc == N.OK
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert to_np(out).tolist() == [65536.0] * 4
