@@ -599,7 +599,7 @@ def run_ours(args) -> None:
 
     from deepx_b200 import _native as N
     from deepx_b200.sharded import RowPartition, ShardedOps
-    ops = ShardedOps()
+    ops = ShardedOps(defer=True)  # the combine of the global sum runs after the row max: the skew between ranks is hidden
     part = RowPartition(ROWS, world)
     my_rows = part.count(rank)
     row0 = part.start(rank)
@@ -650,6 +650,7 @@ def run_ours(args) -> None:
         ops.add(t, x, z)
         ops.sum(z, [0, 1], False, s)
         ops.reducemax(z, [1], False, m)
+        ops.flush()  # wait for the peers' partial sums and combine them: part of the step
 
     def barrier():
         if world > 1:
@@ -740,14 +741,24 @@ def run_ours(args) -> None:
     achieved = mul_bytes / mul_ms / 1e6
 
     # ---- end-to-end number: through the deepxIR executor (the reference-facing boundary), host buffers
-    # in, results out, every step.  The device-resident tensors above are released first.
+    # in, results out, every step.  The device-resident tensors above are released first.  Every rank is one
+    # executor of a world-of-N (dx_exec_set_shard): it gets the SAME IR lines with the GLOBAL shapes, holds its
+    # rows of the partitioned tensors, and the global sum is combined by the executor itself over peer memory —
+    # no torch.distributed call inside a step.
     del x, y, t, z
     torch.cuda.empty_cache()
     from deepx_b200.executor import Executor
     ex = Executor(local_rank)
+    ex_comm = None
+    if world > 1:
+        from deepx_b200.comm import PeerComm
+        ex_comm = PeerComm()  # set-up only: the IPC handles of the mailboxes travel through the process group
+        ex.set_shard(rank, world, ex_comm._h, min_bytes=4096)
     f32 = "tensor<float32>"
-    for nm, shp in (("x", (my_rows, COLS)), ("y", (my_rows, COLS)), ("t", (my_rows, COLS)), ("z", (my_rows, COLS)), ("s", (1,)), ("m", (my_rows,))):
+    for nm, shp in (("x", (ROWS, COLS)), ("y", (ROWS, COLS)), ("t", (ROWS, COLS)), ("z", (ROWS, COLS)), ("s", (1,)), ("m", (ROWS,))):
         ex.new(nm, "float32", shp)
+    if world > 1:
+        assert ex.shard("x") == (True, row0, my_rows, ROWS) and ex.shard("m") == (True, row0, my_rows, ROWS) and not ex.shard("s")[0]
     ir = [f"exp({f32}:x)->({f32}:t) // author=miaobyte",
           f"mul({f32}:t, {f32}:y)->({f32}:t) // author=miaobyte",
           f"add({f32}:t, {f32}:x)->({f32}:z) // author=miaobyte",
@@ -756,44 +767,49 @@ def run_ours(args) -> None:
     hx_np, hy_np, hs_np, hm_np = hx.numpy(), hy.numpy(), hs.numpy(), hm.numpy()  # views of the pinned buffers
     ex_stream = torch.cuda.ExternalStream(ctypes_ptr(ex), device=dev)
 
-    class _DevView:  # the executor's `s` tensor as a torch tensor, for the NCCL combine
-        def __init__(self, ptr, n):
-            self.__cuda_array_interface__ = {"shape": (n,), "typestr": "<f4", "data": (ptr, False), "version": 2}
-    s_view = torch.as_tensor(_DevView(ex.ptr("s"), 1), device=dev) if world > 1 else None
-
     def e2e_step():
-        ex.upload("x", hx_np)
-        ex.upload("y", hy_np)
+        ex.upload_async("x", hx_np)   # copy stream; exp waits for x only, so it runs while y is still on its way
+        ex.upload_async("y", hy_np)
         for line in ir:
             ex.run(line)
-        if world > 1:  # partial sums of the row blocks → global sum (the one exchange step of the chain)
-            ex.sync()
-            dist.all_reduce(s_view, op=dist.ReduceOp.SUM)
-            torch.cuda.current_stream().synchronize()
-        download_into(ex, "s", hs_np)
+        download_into(ex, "s", hs_np)  # completes the deferred combine of the partial sums first
         download_into(ex, "m", hm_np)
+
+    def copies_only():
+        ex.upload_async("x", hx_np)
+        ex.upload_async("y", hy_np)
+        ex.sync()
 
     def timed_ex(fn, steps):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(ex_stream):
             e0.record()
+        t0 = time.perf_counter()
         for _ in range(steps):
             fn()
+        ex.sync()
+        wall_ms = (time.perf_counter() - t0) * 1e3
         with torch.cuda.stream(ex_stream):
             e1.record()
         ex.sync()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        # the uploads run on the executor's copy stream: the step ends when the compute stream has consumed them, which
+        # the events on the compute stream see; the host clock around the same region must agree with them
+        ms = torch.tensor([max(e0.elapsed_time(e1), 0.0), wall_ms], dtype=torch.float64, device=dev)
         if world > 1:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        return float(ms[0].item()), float(ms[1].item())
 
     e2e_steps = max(2, min(args.steps, 5))
     e2e_step()
-    e2e_ms = timed_ex(e2e_step, e2e_steps) / e2e_steps
+    e2e_ms, e2e_wall_ms = (v / e2e_steps for v in timed_ex(e2e_step, e2e_steps))
     if abs(float(hs_np[0]) - got_sum) > 1e-4 * abs(got_sum) + 1e-3 or not np.array_equal(hm_np, got_m):
         raise SystemExit("bench: the executor path and the direct path disagree — refusing to report a number")
+    # what the host can deliver: the same two uploads from the same pinned buffers and nothing else
+    copies_only()
+    h2d_ms, _ = (v / e2e_steps for v in timed_ex(copies_only, e2e_steps))
+    h2d_bytes = 2 * my_rows * COLS * 4 * world
     executor_us = compiled_us = None
     tiny_ir = "addscalar(tensor<float32>:tiny, var<float32>:1)->(tensor<float32>:tiny) // author=miaobyte id=7"
     if world == 1:
@@ -820,6 +836,8 @@ def run_ours(args) -> None:
         compiled_us = (time.perf_counter() - t0) / (50 * 200) * 1e6
         prog.free()
     ex.close()
+    if ex_comm is not None:
+        ex_comm.close()
     udp_us = udp_round_trip_us(tiny_ir) if world == 1 else None
     e2e_value = total_bytes / e2e_ms / 1e6
 
@@ -838,8 +856,14 @@ def run_ours(args) -> None:
                      "(profiles/ew2_mul_f32_chain_256x1048576.md), scaled by rows",
                      "bytes_per_launch": mul_bytes, "us_per_launch": round(mul_ms * 1e3, 2)},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": 2 * my_rows * COLS * 4 * world,
-                "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
-                "path": "deepxIR text -> libdeepx_exec.so (dx_exec_upload / dx_exec_run / dx_exec_download), pinned host buffers"},
+                "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "ms_per_step_host_clock": round(e2e_wall_ms, 3),
+                "steps": e2e_steps,
+                "h2d_bound_gbs": round(total_bytes / h2d_ms / 1e6, 1), "h2d_gbs_per_gpu": round(h2d_bytes / world / h2d_ms / 1e6, 1),
+                "frac_of_h2d_bound": round(h2d_ms / e2e_ms, 3),
+                "h2d_bound": "the same metric if a step were nothing but its two uploads (same pinned buffers, same copy stream, all ranks at once)",
+                "path": "executor only: deepxIR text -> libdeepx_exec.so (dx_exec_upload_async / dx_exec_run / dx_exec_download), pinned host buffers; "
+                        + ("one executor" if world == 1 else f"one executor per GPU as ranks of a world of {world} (dx_exec_set_shard): global shapes in the IR, "
+                           "rows partitioned by the executor, partial sums combined by its own peer-memory exchange")},
         "executor": {"us_per_ir_line": None if executor_us is None else round(executor_us, 2),
                      "us_per_ir_line_compiled": None if compiled_us is None else round(compiled_us, 2),
                      "us_per_udp_round_trip": None if udp_us is None else round(udp_us, 2),

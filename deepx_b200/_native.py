@@ -64,6 +64,17 @@ SIGNATURES = {
     "dx_reduce_allreduce": (_i, [_vp, _i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp, _sz, _vp]),
     "dx_comm_emulate": (_vp, [_i, _i]),
     "dx_comm_emulated_allreduce": (_i, [_vp, _i, _i, _pvp, _i, _i64, _vp]),
+    "dx_comm_rank": (_i, [_vp]),
+    "dx_comm_world": (_i, [_vp]),
+    "dx_comm_allreduce_begin": (_i, [_vp, _i, _i, _vp, _i64, _vp]),
+    "dx_comm_allreduce_finish": (_i, [_vp, _vp]),
+    "dx_comm_pending": (_i, [_vp, _pvp]),
+    "dx_shard_rows": (None, [_i64, _i, _i, _pi64, _pi64]),
+    "dx_comm_allgather_rows": (_i, [_vp, _vp, _i64, _i64, _vp]),
+    "dx_reduce_allreduce_begin": (_i, [_vp, _i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp, _sz, _vp]),
+    "dx_comm_emulated_publish": (_i, [_vp, _i, _i, _pvp, _i, _i64, _vp]),
+    "dx_comm_emulated_combine": (_i, [_vp, _i, _i, _pvp, _i, _i64, _vp]),
+    "dx_comm_emulated_allgather_rows": (_i, [_vp, _pvp, _i64, _i64, _vp]),
     "dx_rmsnorm": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _d, _d, _vp]),
     "dx_softmax": (_i, [_i, _vp, _vp, _i64, _i64, _vp]),
     "dx_transpose": (_i, [_i, _vp, _pi64, _i, _pi32, _vp, _vp]),

@@ -74,11 +74,36 @@ class PeerComm:
             N.check(N.lib.dx_comm_allreduce(self._h, OPS[op], _dtype_code(t), t.data_ptr(), t.numel(), st))
         return t
 
-    def reduce_allreduce(self, op: str, A: torch.Tensor, dims, keepdims: bool, B: torch.Tensor) -> None:
+    def reduce_allreduce(self, op: str, A: torch.Tensor, dims, keepdims: bool, B: torch.Tensor, defer: bool = False) -> None:
         """sum / prod / reducemax / reducemin of this rank's block into B, combined over the ranks; where
-        the local reduction ends in a one-CTA finish step, that kernel also does the exchange."""
+        the local reduction ends in a one-CTA finish step, that kernel also does the exchange.  With
+        `defer` the call stops once this rank's result is on its way to the peers: B is complete only
+        after :meth:`finish` (or the next call on this communicator), and what the stream runs in
+        between hides the skew between the ranks."""
         from . import tensorfunc as TF
-        TF._reduce(OPS[op], A, dims, keepdims, B, comm_handle=self._h)
+        TF._reduce(OPS[op], A, dims, keepdims, B, comm_handle=self._h, defer=defer)
+
+    def pending(self) -> int:
+        """Address of the buffer whose exchange has been begun and not finished, or 0."""
+        p = C.c_void_p()
+        return int(p.value or 0) if N.lib.dx_comm_pending(self._h, C.byref(p)) else 0
+
+    def finish(self, stream: int | None = None) -> None:
+        """Completes a deferred exchange on the current stream of this communicator's device."""
+        with torch.cuda.device(self.device):
+            st = torch.cuda.current_stream().cuda_stream if stream is None else stream
+            N.check(N.lib.dx_comm_allreduce_finish(self._h, st))
+
+    def allgather_rows(self, t: torch.Tensor) -> torch.Tensor:
+        """In place: every rank holds all of `t` and has filled its own block of leading-axis rows
+        (``dx_shard_rows``); afterwards every rank holds every block."""
+        if not (t.is_cuda and t.is_contiguous() and t.dim() >= 1):
+            raise ValueError("allgather_rows needs a contiguous CUDA tensor with a leading axis")
+        rows = t.shape[0]
+        row_bytes = (t.numel() // rows if rows else 0) * t.element_size()
+        with torch.cuda.device(t.device):
+            N.check(N.lib.dx_comm_allgather_rows(self._h, t.data_ptr(), rows, row_bytes, torch.cuda.current_stream().cuda_stream))
+        return t
 
     def set_timeout_ms(self, ms: int) -> None:
         N.check(N.lib.dx_comm_set_timeout_ms(self._h, ms))
@@ -88,7 +113,7 @@ class PeerComm:
         N.check(N.lib.dx_comm_status(self._h, None))
 
     def close(self) -> None:
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and N is not None and getattr(N, "lib", None) is not None:  # the module may be gone at interpreter exit
             N.lib.dx_comm_destroy(self._h)
             self._h = None
 
@@ -110,6 +135,30 @@ class EmulatedComm:
         N.check(N.lib.dx_comm_emulated_allreduce(self._h, OPS[op], _dtype_code(bufs[0]), ptrs, self.world if active is None else active,
                                                  bufs[0].numel(), st))
 
+    def _ptrs(self, bufs):
+        assert len(bufs) == self.world
+        return (C.c_void_p * self.world)(*[b.data_ptr() for b in bufs])
+
+    def publish(self, bufs: Sequence[torch.Tensor], op: str = "sum", active: int | None = None) -> None:
+        """First half of the exchange for all ranks (one launch): stores and flags, no waiting."""
+        st = torch.cuda.current_stream(bufs[0].device).cuda_stream
+        N.check(N.lib.dx_comm_emulated_publish(self._h, OPS[op], _dtype_code(bufs[0]), self._ptrs(bufs), self.world if active is None else active,
+                                               bufs[0].numel(), st))
+
+    def combine(self, bufs: Sequence[torch.Tensor], op: str = "sum", active: int | None = None) -> None:
+        """Second half for all ranks (one launch): bounded wait for the flags, combine in rank order."""
+        st = torch.cuda.current_stream(bufs[0].device).cuda_stream
+        N.check(N.lib.dx_comm_emulated_combine(self._h, OPS[op], _dtype_code(bufs[0]), self._ptrs(bufs), self.world if active is None else active,
+                                               bufs[0].numel(), st))
+
+    def allgather_rows(self, bufs: Sequence[torch.Tensor]) -> None:
+        """bufs[r] is rank r's copy of the whole tensor with rank r's row block filled in."""
+        t = bufs[0]
+        rows = t.shape[0]
+        row_bytes = (t.numel() // rows if rows else 0) * t.element_size()
+        st = torch.cuda.current_stream(t.device).cuda_stream
+        N.check(N.lib.dx_comm_emulated_allgather_rows(self._h, self._ptrs(bufs), rows, row_bytes, st))
+
     def set_timeout_ms(self, ms: int) -> None:
         N.check(N.lib.dx_comm_set_timeout_ms(self._h, ms))
 
@@ -117,9 +166,16 @@ class EmulatedComm:
         N.check(N.lib.dx_comm_status(self._h, None))
 
     def close(self) -> None:
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and N is not None and getattr(N, "lib", None) is not None:  # the module may be gone at interpreter exit
             N.lib.dx_comm_destroy(self._h)
             self._h = None
 
     def __del__(self):
         self.close()
+
+
+def shard_rows(global_rows: int, rank: int, world: int) -> tuple[int, int]:
+    """(first row, row count) of `rank`'s block: the split every part of the library uses."""
+    r0, n = C.c_int64(), C.c_int64()
+    N.lib.dx_shard_rows(global_rows, rank, world, C.byref(r0), C.byref(n))
+    return int(r0.value), int(n.value)

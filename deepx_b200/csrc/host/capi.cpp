@@ -1,6 +1,7 @@
 // C ABI of the executor (include/dx_executor.h).
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstring>
 #include <sstream>
 #include <unordered_map>
@@ -127,7 +128,38 @@ int dx_exec_tensor_info(dx_exec *e, const char *name, int *dtype, int64_t *shape
 
 void *dx_exec_tensor_ptr(dx_exec *e, const char *name) {
     if (!e || !name || !e->ex.mem().exists_tensor(name)) return nullptr;
-    return e->ex.mem().get_tensor(name)->data;
+    auto t = e->ex.mem().get_tensor(name);
+    if (t->upload_in_flight) {
+        e->ex.mem().wait_ready(*t);
+        --e->ex.mem().uploads_in_flight;
+    }
+    try {  // the caller is about to look at the memory: a combine still owed to this tensor runs first
+        if (e->ex.mem().comm_pending_in(t->data, size_t(std::max<int64_t>(t->shape.bytes(), 0)))) e->ex.mem().flush_comm();
+    } catch (const std::exception &ex) {
+        g_err = ex.what();
+        return nullptr;
+    }
+    return t->data;
+}
+
+int dx_exec_set_shard(dx_exec *e, int rank, int world, size_t min_bytes, dx_comm *comm) {
+    if (!e) { g_err = "null executor"; return -1; }
+    try {
+        e->ex.set_shard(rank, world, min_bytes, comm);
+        return 0;
+    } catch (const std::exception &ex) {
+        g_err = ex.what();
+        return -1;
+    }
+}
+
+int dx_exec_tensor_shard(dx_exec *e, const char *name, int64_t *row0, int64_t *rows, int64_t *global_rows) {
+    if (!e || !name || !e->ex.mem().exists_tensor(name)) return -1;
+    auto t = e->ex.mem().get_tensor(name);
+    if (row0) *row0 = t->row0;
+    if (rows) *rows = t->shape.dim() ? t->shape.shape[0] : 0;
+    if (global_rows) *global_rows = t->partitioned() ? t->global_rows : (t->shape.dim() ? t->shape.shape[0] : 0);
+    return t->partitioned() ? 1 : 0;
 }
 
 static int copy(dx_exec *e, const char *name, void *host, size_t bytes, bool up) {
@@ -139,6 +171,16 @@ static int copy(dx_exec *e, const char *name, void *host, size_t bytes, bool up)
     }
     if (bytes == 0) return 0;
     cudaSetDevice(e->ex.mem().device());
+    try {
+        if (e->ex.mem().comm_pending_in(t->data, bytes)) e->ex.mem().flush_comm();  // a combine still owed to this tensor
+    } catch (const std::exception &ex) {
+        g_err = ex.what();
+        return -4;
+    }
+    if (t->upload_in_flight) {  // an asynchronous upload into this tensor comes first
+        e->ex.mem().wait_ready(*t);
+        --e->ex.mem().uploads_in_flight;
+    }
     cudaStream_t st = static_cast<cudaStream_t>(e->ex.mem().stream());
     cudaError_t err = up ? cudaMemcpyAsync(t->data, host, bytes, cudaMemcpyHostToDevice, st)
                          : cudaMemcpyAsync(host, t->data, bytes, cudaMemcpyDeviceToHost, st);
@@ -147,12 +189,40 @@ static int copy(dx_exec *e, const char *name, void *host, size_t bytes, bool up)
     return 0;
 }
 int dx_exec_upload(dx_exec *e, const char *name, const void *host, size_t bytes) { return copy(e, name, const_cast<void *>(host), bytes, true); }
+
+int dx_exec_upload_async(dx_exec *e, const char *name, const void *host, size_t bytes) {
+    if (!e || !name || !e->ex.mem().exists_tensor(name)) { g_err = std::string("tensor not found: ") + (name ? name : ""); return -1; }
+    auto t = e->ex.mem().get_tensor(name);
+    if (size_t(t->shape.bytes()) != bytes) {
+        g_err = "size mismatch: tensor holds " + std::to_string(t->shape.bytes()) + " bytes, caller gave " + std::to_string(bytes);
+        return -2;
+    }
+    if (bytes == 0) return 0;
+    cudaSetDevice(e->ex.mem().device());
+    try {
+        Mem &m = e->ex.mem();
+        if (m.comm_pending_in(t->data, bytes)) m.flush_comm();
+        if (!t->upload_in_flight) ++m.uploads_in_flight;
+        m.upload_async(*t, host, bytes);
+    } catch (const std::exception &ex) {
+        g_err = ex.what();
+        return -4;
+    }
+    return 0;
+}
 int dx_exec_download(dx_exec *e, const char *name, void *host, size_t bytes) { return copy(e, name, host, bytes, false); }
 
 int dx_exec_sync(dx_exec *e) {
     if (!e) return -1;
     cudaSetDevice(e->ex.mem().device());
+    try {
+        e->ex.mem().flush_comm();
+    } catch (const std::exception &ex) {
+        g_err = ex.what();
+        return -4;
+    }
     cudaError_t err = cudaStreamSynchronize(static_cast<cudaStream_t>(e->ex.mem().stream()));
+    if (err == cudaSuccess && e->ex.mem().uploads_in_flight > 0) err = cudaStreamSynchronize(static_cast<cudaStream_t>(e->ex.mem().copy_stream()));
     if (err != cudaSuccess) { g_err = cudaGetErrorString(err); return -4; }
     return 0;
 }
@@ -246,6 +316,84 @@ int dx_ir_plan_fusion(const char *program, const char *existing, char *out, size
         }
         if (put(text, out, cap) < 0) return -1;
         return int(st.rmsnorm_groups + st.softmax_groups);
+    } catch (const std::exception &ex) {
+        g_err = ex.what();
+        return -1;
+    }
+}
+
+// The partition decisions for a program, with tensors that are records only (no device).  Lines are classified by
+// the same plan_rowwise / plan_reduce / should_partition the ops use; ops without a row-wise form are reported as
+// the executor would treat them when an operand is partitioned.
+int dx_ir_shard_plan(const char *program, int world, size_t min_bytes, char *out, size_t cap) {
+    try {
+        ShardCtx ctx;
+        ctx.world = world;
+        ctx.min_bytes = min_bytes;
+        std::unordered_map<std::string, Layout> known;
+        std::istringstream ps(program ? program : "");
+        std::string line, text;
+        int lines = 0;
+        auto names_of = [](const Param &q) {
+            std::vector<std::string> v;
+            std::string names = q.textvalue;
+            for (char &c : names) if (c == '[' || c == ']') c = ' ';
+            std::istringstream ns(names);
+            std::string nm;
+            while (ns >> nm) v.push_back(nm);
+            return v;
+        };
+        while (std::getline(ps, line)) {
+            if (line.find_first_not_of(" \t\r") == std::string::npos) continue;
+            TF t(line);
+            std::string verdict;
+            auto layout_of = [&](const std::string &n) -> const Layout & {
+                auto it = known.find(n);
+                if (it == known.end()) throw std::runtime_error("tensor not found: " + n);
+                return it->second;
+            };
+            static const char *rowwise_ops[] = {"add", "sub", "mul", "div", "max", "min", "pow", "addscalar", "subscalar", "rsubscalar", "mulscalar",
+                                                "divscalar", "rdivscalar", "maxscalar", "minscalar", "powscalar", "rpowscalar", "sqrt", "log", "exp",
+                                                "sin", "cos", "tan", "invert", "equal", "notequal", "less", "greater", "equalscalar", "notequalscalar",
+                                                "lessscalar", "greaterscalar", "switch", "todtype", "copytensor"};
+            bool is_rowwise = false;
+            for (const char *o : rowwise_ops) is_rowwise = is_rowwise || t.name == o;
+            if (t.name == "newtensor") {
+                Layout l;
+                l.global = t.vector_i64(0);
+                l.elem_bytes = precision_bits(t.returns[0].dtype.precision) / 8;
+                l.partitioned = should_partition(l.global, l.elem_bytes, ctx);
+                known[t.returns[0].textvalue] = l;
+                verdict = "newtensor " + t.returns[0].textvalue + (l.partitioned ? ": partitioned " + std::to_string(l.global[0]) + " rows" : ": whole");
+            } else if (t.name == "deltensor") {
+                known.erase(t.returns[0].textvalue);
+                verdict = "whole";
+            } else if (is_rowwise) {
+                std::vector<Layout> in;
+                for (const auto &q : t.args)
+                    if (q.dtype.category & (CAT_TENSOR | CAT_LISTTENSOR))
+                        for (const auto &n : names_of(q))
+                            if (known.count(n)) in.push_back(known[n]);
+                const RowwisePlan p = plan_rowwise(in, layout_of(t.returns[0].textvalue));
+                verdict = !p.error.empty() ? "refuse: " + p.error : (!p.by_rows ? "whole" : (p.gather_output ? "rows+allgather" : "rows"));
+            } else if (t.name == "sum" || t.name == "prod" || t.name == "reducemax" || t.name == "reducemin") {
+                const Layout &a = layout_of(t.args[0].textvalue);
+                const ReducePlan p = plan_reduce(a, checked_dims(a.global, t.vector_int(1)), t.var_bool(2), layout_of(t.returns[0].textvalue), dx_comm_max_bytes());
+                verdict = p.kind == ReducePlan::REFUSE ? "refuse: " + p.error : reduce_plan_name(p.kind);
+            } else {
+                bool any = false;
+                for (const auto &q : t.args)
+                    if (q.dtype.category & (CAT_TENSOR | CAT_LISTTENSOR))
+                        for (const auto &n : names_of(q)) any = any || (known.count(n) && known[n].partitioned);
+                for (const auto &q : t.returns)
+                    for (const auto &n : names_of(q)) any = any || (known.count(n) && known[n].partitioned);
+                verdict = any ? "rows-if-aligned" : "whole";
+            }
+            if (lines++) text += "\n";
+            text += verdict;
+        }
+        if (put(text, out, cap) < 0) { g_err = "output buffer too small"; return -1; }
+        return lines;
     } catch (const std::exception &ex) {
         g_err = ex.what();
         return -1;

@@ -298,6 +298,10 @@ bool check_matmul_shape(const std::vector<int64_t> &a, const std::vector<int64_t
 // tensors and the store
 // ============================================================================================
 Tensor::~Tensor() {
+    if (ready_event) {
+        cudaEventSynchronize(static_cast<cudaEvent_t>(ready_event));  // a copy into this storage may still be running
+        cudaEventDestroy(static_cast<cudaEvent_t>(ready_event));
+    }
     if (data && pool) dx_pool_free(pool, data);
     data = nullptr;
 }
@@ -314,8 +318,47 @@ Mem::Mem(int device, size_t pool_limit_bytes) : device_(device) {
     stream_ = s;
 }
 
+void *Mem::copy_stream() {
+    if (!copy_stream_) {
+        cudaStream_t s = nullptr;
+        if (cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking) != cudaSuccess) throw std::runtime_error("cannot create the copy stream");
+        copy_stream_ = s;
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) throw std::runtime_error("cannot create an event");
+        order_event_ = e;
+    }
+    return copy_stream_;
+}
+
+void Mem::upload_async(Tensor &t, const void *host, size_t bytes) {
+    cudaStream_t cs = static_cast<cudaStream_t>(copy_stream()), st = static_cast<cudaStream_t>(stream_);
+    // the copy must not overtake earlier ops that still read or write this storage
+    cudaEventRecord(static_cast<cudaEvent_t>(order_event_), st);
+    cudaStreamWaitEvent(cs, static_cast<cudaEvent_t>(order_event_), 0);
+    const cudaError_t e = cudaMemcpyAsync(t.data, host, bytes, cudaMemcpyHostToDevice, cs);
+    if (e != cudaSuccess) throw std::runtime_error(std::string("host to device copy failed: ") + cudaGetErrorString(e));
+    if (!t.ready_event) {
+        cudaEvent_t ev = nullptr;
+        if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) throw std::runtime_error("cannot create an event");
+        t.ready_event = ev;
+    }
+    cudaEventRecord(static_cast<cudaEvent_t>(t.ready_event), cs);
+    t.upload_in_flight = true;
+}
+
+void Mem::wait_ready(Tensor &t) {
+    if (!t.upload_in_flight) return;
+    cudaStreamWaitEvent(static_cast<cudaStream_t>(stream_), static_cast<cudaEvent_t>(t.ready_event), 0);
+    t.upload_in_flight = false;
+}
+
 Mem::~Mem() {
     tensors_.clear();
+    if (copy_stream_) {
+        cudaStreamSynchronize(static_cast<cudaStream_t>(copy_stream_));
+        cudaStreamDestroy(static_cast<cudaStream_t>(copy_stream_));
+        cudaEventDestroy(static_cast<cudaEvent_t>(order_event_));
+    }
     if (scratch_) dx_pool_free(pool_, scratch_);
     if (stream_) {
         cudaStreamSynchronize(static_cast<cudaStream_t>(stream_));
@@ -329,7 +372,16 @@ TensorPtr Mem::new_tensor(const std::string &name, uint16_t precision, const std
     for (auto d : shape)
         if (d < 0) throw std::invalid_argument("newtensor: negative extent");
     auto t = std::make_shared<Tensor>();
-    t->shape.set(shape);
+    if (should_partition(shape, precision_bits(precision) / 8, shard)) {
+        const RowBlock b = row_block(shape[0], shard.rank, shard.world);
+        std::vector<int64_t> local = shape;
+        local[0] = b.rows;
+        t->shape.set(local);
+        t->global_rows = shape[0];
+        t->row0 = b.row0;
+    } else {
+        t->shape.set(shape);
+    }
     t->shape.dtype = precision;
     t->pool = pool_;
     t->device = device_;
@@ -369,6 +421,18 @@ const ArgValue *Mem::get_arg(const std::string &name) const {
         return nullptr;
     }
     return &it->second;
+}
+
+void Mem::flush_comm() {
+    if (!shard.comm) return;
+    if (dx_comm_allreduce_finish(shard.comm, stream_) != DX_OK) throw std::runtime_error(dx_last_error());
+}
+
+bool Mem::comm_pending_in(const void *p, size_t bytes) const {
+    void *buf = nullptr;
+    if (!shard.comm || !dx_comm_pending(shard.comm, &buf)) return false;
+    const char *lo = static_cast<const char *>(p);
+    return static_cast<const char *>(buf) >= lo && static_cast<const char *>(buf) < lo + (bytes ? bytes : 1);
 }
 
 void *Mem::scratch(size_t bytes) {
@@ -712,10 +776,56 @@ OpResp Executor::run(const TF &call) {
     std::string message;
     int rc = 0;
     try {
+        if (mem_.uploads_in_flight > 0) {  // tensors still being filled by dx_exec_upload_async: this op waits for those it names
+            auto wait = [&](const Param &q) {
+                if ((q.dtype.category & (CAT_TENSOR | CAT_LISTTENSOR)) == 0) return;
+                std::string names = q.textvalue;
+                trim_chars(names, "[]");
+                std::istringstream ns(names);
+                std::string nm;
+                while (ns >> nm)
+                    if (mem_.exists_tensor(nm)) {
+                        Tensor &t = *mem_.get_tensor(nm);
+                        if (t.upload_in_flight) {
+                            mem_.wait_ready(t);
+                            --mem_.uploads_in_flight;
+                        }
+                    }
+            };
+            for (const auto &q : tf->args) wait(q);
+            for (const auto &q : tf->returns) wait(q);
+        }
+        if (mem_.shard.comm && dx_comm_pending(mem_.shard.comm, nullptr)) {
+            // A cross-rank reduction left its combine for later.  Compute ops that do not touch its output go ahead
+            // (they are what hides the skew between the ranks); anything that reads or writes that tensor, and every
+            // op that is not plain compute (lifetime, io, args), waits for it.
+            static const char *compute[] = {"elementwise", "reduce", "changeshape", "matmul", "fused", "init"};
+            bool plain = false;
+            for (const char *c : compute) plain = plain || tf->tftype == c;
+            bool touches = !plain;
+            auto look = [&](const Param &q) {
+                if (touches || (q.dtype.category & (CAT_TENSOR | CAT_LISTTENSOR)) == 0) return;
+                std::string names = q.textvalue;
+                trim_chars(names, "[]");
+                std::istringstream ns(names);
+                std::string nm;
+                while (ns >> nm)
+                    if (mem_.exists_tensor(nm)) {
+                        const TensorPtr t = mem_.get_tensor(nm);
+                        touches = touches || mem_.comm_pending_in(t->data, size_t(std::max<int64_t>(t->shape.bytes(), 0)));
+                    }
+            };
+            for (const auto &q : tf->args) look(q);
+            for (const auto &q : tf->returns) look(q);
+            if (touches) mem_.flush_comm();
+        }
         const int repeat = tf->metadata.benchmark_repeat > 1 ? tf->metadata.benchmark_repeat : 1;
         for (int i = 0; i < repeat && rc == 0; ++i) rc = tf->run(mem_, message);
         // a timed request wants the device to have finished before finish_at is taken
-        if (tf->metadata.benchmark_repeat > 0) cudaStreamSynchronize(static_cast<cudaStream_t>(mem_.stream()));
+        if (tf->metadata.benchmark_repeat > 0) {
+            mem_.flush_comm();
+            cudaStreamSynchronize(static_cast<cudaStream_t>(mem_.stream()));
+        }
     } catch (const std::exception &e) {
         rc = 1;
         message = e.what();
@@ -727,6 +837,17 @@ OpResp Executor::run(const TF &call) {
     if (rc != 0) resp.error(message);
     else resp.finish("");
     return resp;
+}
+
+void Executor::set_shard(int rank, int world, size_t min_bytes, dx_comm *comm) {
+    if (world < 1 || rank < 0 || rank >= world) throw std::invalid_argument("set_shard: rank " + std::to_string(rank) + " of " + std::to_string(world));
+    if (world > 1 && !comm) throw std::invalid_argument("set_shard: more than one rank needs a connected communicator");
+    if (comm && (dx_comm_rank(comm) != rank || dx_comm_world(comm) != world)) throw std::invalid_argument("set_shard: the communicator was created for another rank or world size");
+    std::lock_guard<std::mutex> lk(mu_);
+    mem_.shard.rank = rank;
+    mem_.shard.world = world;
+    mem_.shard.min_bytes = min_bytes;
+    mem_.shard.comm = world > 1 ? comm : nullptr;
 }
 
 OpResp Executor::run_line(const std::string &ir) {
@@ -832,6 +953,11 @@ std::shared_ptr<CompiledProgram> Executor::compile(const std::string &text, std:
     }
     cudaStream_t st = static_cast<cudaStream_t>(mem_.stream());
     cudaSetDevice(mem_.device());
+    try {
+        mem_.flush_comm();
+    } catch (const std::exception &e) {
+        return failed(e.what());
+    }
     if (cudaStreamSynchronize(st) != cudaSuccess) return failed(std::string("stream: ") + cudaGetErrorString(cudaGetLastError()));
     // pass 2: the same ops, captured instead of executed
     auto out = std::make_shared<CompiledProgram>();
@@ -842,6 +968,13 @@ std::shared_ptr<CompiledProgram> Executor::compile(const std::string &text, std:
     for (size_t i = 0; i < ops.size() && why.empty(); ++i) {
         const OpResp r = run(ops[i]);
         if (r.result != "ok") why = ops[i].name + ": " + r.message;
+    }
+    if (why.empty()) {
+        try {
+            mem_.flush_comm();  // a combine left open by the last cross-rank reduction belongs to the program
+        } catch (const std::exception &e) {
+            why = e.what();
+        }
     }
     mem_.capturing = false;
     cudaGraph_t graph = nullptr;
@@ -899,6 +1032,15 @@ int Executor::replay(CompiledProgram &program, std::string *error) {
         const TensorPtr p = mem_.get_tensor(r.name);
         if (p->data != r.data || p->shape.dtype != r.precision || p->shape.shape != r.shape)
             return failed("stale program: tensor " + r.name + " changed storage, dtype or shape; compile it again");
+        if (p->upload_in_flight) {  // an asynchronous upload into a tensor the program uses: the graph launch waits for it
+            mem_.wait_ready(*p);
+            --mem_.uploads_in_flight;
+        }
+    }
+    try {
+        mem_.flush_comm();
+    } catch (const std::exception &e) {
+        return failed(e.what());
     }
     cudaSetDevice(mem_.device());
     const cudaError_t e = cudaGraphLaunch(static_cast<cudaGraphExec_t>(program.exec), static_cast<cudaStream_t>(mem_.stream()));

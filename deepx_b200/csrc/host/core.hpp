@@ -16,6 +16,7 @@
 #include <vector>
 
 #include "dx_kernels.h"
+#include "shard.hpp"
 
 namespace dxh {
 
@@ -91,10 +92,25 @@ bool check_matmul_shape(const std::vector<int64_t> &a, const std::vector<int64_t
 
 // ---- tensors and the store (tensor.hpp:17-171, mem/mem.hpp:15-175, op-cuda mem_cuda.hpp) ------------
 struct Tensor {
-    Shape shape;
+    Shape shape;              // what `data` holds: the LOCAL rows of a row-partitioned tensor
     void *data = nullptr;
     dx_pool *pool = nullptr;  // owner of `data`
     int device = 0;
+    // Row partitioning over the ranks of a multi-GPU executor (shard.hpp): global_rows >= 0 means this rank
+    // holds rows [row0, row0 + shape[0]) of a tensor whose leading axis has global_rows indices.
+    int64_t global_rows = -1, row0 = 0;
+    // Set while an asynchronous upload into this tensor is in flight on the copy stream: the compute stream waits
+    // for it before the first op that names the tensor (dx_exec_upload_async).
+    void *ready_event = nullptr;
+    bool upload_in_flight = false;
+    bool partitioned() const { return global_rows >= 0; }
+    std::vector<int64_t> global_shape() const {
+        std::vector<int64_t> g = shape.shape;
+        if (partitioned() && !g.empty()) g[0] = global_rows;
+        return g;
+    }
+    Layout layout() const { return Layout{partitioned(), global_shape(), precision_bits(shape.dtype) / 8}; }
+    int64_t row_bytes() const { return shape.dim() == 0 || shape.shape[0] == 0 ? 0 : shape.bytes() / shape.shape[0]; }
     Tensor() = default;
     Tensor(const Tensor &) = delete;
     Tensor &operator=(const Tensor &) = delete;
@@ -126,6 +142,12 @@ class Mem {
     dx_pool *pool() const { return pool_; }
     int device() const { return device_; }
     void *stream() const { return stream_; }
+    void *copy_stream();  // created on first use: host-to-device copies that overlap with compute
+    // Host bytes into a tensor without waiting: the copy is ordered behind everything already submitted to the compute
+    // stream, and ops that name the tensor afterwards are ordered behind the copy (wait_ready).
+    void upload_async(Tensor &t, const void *host, size_t bytes);
+    void wait_ready(Tensor &t);
+    int uploads_in_flight = 0;  // tensors whose asynchronous upload no op has waited for yet
     void *scratch(size_t bytes);  // grow-only workspace for reductions, from the pool
     // While a program is being captured into a CUDA graph nothing may be allocated: the graph keeps
     // the pointers it saw.  `capturing` makes scratch growth and staging temporaries throw instead;
@@ -134,11 +156,19 @@ class Mem {
     uint64_t scratch_generation() const { return scratch_generation_; }
     size_t tensor_count() const { return tensors_.size(); }
     std::vector<std::string> tensor_names() const;
+    // One of several ranks (shard.hpp).  new_tensor partitions large tensors by rows when shard.active().
+    ShardCtx shard;
+    // A cross-rank reduction may leave its combine for later (dx_comm_allreduce_finish): flush_comm completes it
+    // on the compute stream; comm_pending_in says whether the outstanding exchange writes into [p, p + bytes).
+    void flush_comm();
+    bool comm_pending_in(const void *p, size_t bytes) const;
 
   private:
     int device_;
     dx_pool *pool_ = nullptr;
     void *stream_ = nullptr;
+    void *copy_stream_ = nullptr;
+    void *order_event_ = nullptr;
     void *scratch_ = nullptr;
     size_t scratch_bytes_ = 0;
     uint64_t scratch_generation_ = 0;
@@ -274,6 +304,10 @@ class Executor {
     std::shared_ptr<CompiledProgram> compile(const std::string &text, std::string *error);
     int replay(CompiledProgram &program, std::string *error);
     bool fuse = true;
+    // Makes this executor rank `rank` of `world` (one process per GPU, the same IR lines to every rank); `comm`
+    // must be connected and outlive the executor.  Tensors created afterwards are partitioned by rows when
+    // they hold at least `min_bytes`; existing tensors stay as they are.
+    void set_shard(int rank, int world, size_t min_bytes, dx_comm *comm);
     Mem &mem() { return mem_; }
     const TfFactory &factory() const { return factory_; }
     uint64_t ops_run() const { return ops_run_; }

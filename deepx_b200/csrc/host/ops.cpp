@@ -5,6 +5,8 @@
 // are new: tensors are type-erased, so an op validates names/dtypes/shapes and makes ONE call
 // into the kernel C ABI with the tensor's dtype code instead of a 9-way switch over C++ types.
 #include <cuda_runtime.h>
+#include <fcntl.h>
+#include <unistd.h>
 
 #include <cctype>
 #include <cstdio>
@@ -41,6 +43,66 @@ std::string type_mismatch(std::initializer_list<uint16_t> ps) {
     return s;
 }
 
+// ---- operands of an op that works row by row (shard.hpp) ------------------------------------------------------
+// With a single rank, or when nothing is partitioned, this is the whole tensors and the checks the reference makes.
+// Otherwise every operand is taken by this rank's rows: a partitioned tensor as it is, a replicated one of the same
+// global shape through the rows [row0, row0 + rows) of its full copy.  A replicated OUTPUT computed that way is
+// completed by finish(): an all-gather of the row blocks over the communicator.
+struct Rowwise {
+    Mem &mem;
+    bool by_rows = false;
+    int64_t n = 0;           // elements this rank computes
+    int64_t rows = 0;        // local rows (by_rows)
+    TensorPtr gather;        // replicated output to complete
+    std::vector<void *> ptr; // inputs in order, then the output
+    std::vector<int64_t> local_shape;  // of the output, as computed here
+
+    Rowwise(Mem &m, const std::vector<TensorPtr> &inputs, const TensorPtr &out) : mem(m) {
+        std::vector<Layout> in;
+        for (const auto &t : inputs) in.push_back(t->layout());
+        const RowwisePlan plan = plan_rowwise(in, out->layout());
+        if (!plan.error.empty()) throw std::invalid_argument(plan.error);
+        by_rows = plan.by_rows;
+        if (!by_rows) {
+            for (const auto &t : inputs) ptr.push_back(t->data);
+            ptr.push_back(out->data);
+            n = out->shape.size;
+            local_shape = out->shape.shape;
+            return;
+        }
+        const std::vector<int64_t> g = out->global_shape();
+        const RowBlock b = row_block(g[0], mem.shard.rank, mem.shard.world);
+        auto rows_of = [&](const TensorPtr &t) -> void * {
+            if (t->partitioned()) {
+                if (t->row0 != b.row0 || t->shape.shape[0] != b.rows) throw std::runtime_error("tensors are partitioned differently");
+                return t->data;
+            }
+            return static_cast<char *>(t->data) + b.row0 * t->row_bytes();
+        };
+        for (const auto &t : inputs) ptr.push_back(rows_of(t));
+        ptr.push_back(rows_of(out));
+        rows = b.rows;
+        local_shape = g;
+        local_shape[0] = b.rows;
+        n = 1;
+        for (auto d : local_shape) n *= d;
+        if (plan.gather_output) gather = out;
+    }
+    void finish() {
+        if (!gather) return;
+        if (mem.capturing && !mem.shard.comm) return;
+        dx_check(dx_comm_allgather_rows(mem.shard.comm, gather->data, gather->shape.shape[0], gather->row_bytes(), mem.stream()));
+    }
+};
+
+// Ops that have no row-wise form: refuse partitioned operands with a reply that says what to do.
+void refuse_partitioned(const std::string &op, std::initializer_list<TensorPtr> ts) {
+    for (const auto &t : ts)
+        if (t && t->partitioned())
+            throw std::runtime_error(op + ": this form of the op does not work on row-partitioned tensors (a tensor of " +
+                                     std::to_string(t->global_rows) + " rows is split over the GPUs); keep its operands below the partition threshold");
+}
+
 #define DX_TF_BOILERPLATE(Class)                                              \
     std::shared_ptr<TF> clone() const override { return std::make_shared<Class>(*this); } \
     std::string math_formula() const override { return formula; }
@@ -59,8 +121,9 @@ struct BinaryTF : TF {  // add sub mul div max min pow  (tf/elementwise_basic.hp
             error = type_mismatch({A->shape.dtype, B->shape.dtype, C->shape.dtype});
             return 1;
         }
-        if (A->shape.shape != B->shape.shape || A->shape.shape != C->shape.shape) throw std::invalid_argument("shape mismatch");
-        dx_check(dx_ew_binary(op, A->dx(), A->data, B->data, C->data, A->shape.size, mem.stream()));
+        Rowwise rw(mem, {A, B}, C);
+        dx_check(dx_ew_binary(op, A->dx(), rw.ptr[0], rw.ptr[1], rw.ptr[2], rw.n, mem.stream()));
+        rw.finish();
         return 0;
     }
 };
@@ -77,9 +140,10 @@ struct ScalarTF : TF {  // addscalar … rpowscalar; `reversed` ops take (scalar
         if (!check_tensors({args[ti].textvalue, returns[0].textvalue}, mem, error)) return 1;
         auto A = mem.get_tensor(args[ti].textvalue), C = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != C->shape.dtype) { error = type_mismatch({A->shape.dtype, C->shape.dtype}); return 1; }
-        if (A->shape.shape != C->shape.shape) throw std::invalid_argument("shape mismatch");
+        Rowwise rw(mem, {A}, C);
         const Scalar s = scalar_for(*this, si, mem);
-        dx_check(dx_ew_scalar(op, A->dx(), A->data, s.f, s.i, C->data, A->shape.size, mem.stream()));
+        dx_check(dx_ew_scalar(op, A->dx(), rw.ptr[0], s.f, s.i, rw.ptr[1], rw.n, mem.stream()));
+        rw.finish();
         return 0;
     }
 };
@@ -94,8 +158,9 @@ struct UnaryTF : TF {  // sqrt log exp sin cos tan invert
         if (!check_tensors({args[0].textvalue, returns[0].textvalue}, mem, error)) return 1;
         auto A = mem.get_tensor(args[0].textvalue), C = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != C->shape.dtype) { error = type_mismatch({A->shape.dtype, C->shape.dtype}); return 1; }
-        if (A->shape.shape != C->shape.shape) throw std::invalid_argument("shape mismatch");
-        dx_check(dx_ew_unary(op, A->dx(), A->data, C->data, A->shape.size, mem.stream()));
+        Rowwise rw(mem, {A}, C);
+        dx_check(dx_ew_unary(op, A->dx(), rw.ptr[0], rw.ptr[1], rw.n, mem.stream()));
+        rw.finish();
         return 0;
     }
 };
@@ -115,8 +180,9 @@ struct CompareTF : TF {  // equal notequal (with epsilon) less greater
             error = type_mismatch({A->shape.dtype, B->shape.dtype}) + " or " + type_mismatch({A->shape.dtype, M->shape.dtype});
             return 1;
         }
-        if (A->shape.shape != B->shape.shape || A->shape.shape != M->shape.shape) throw std::invalid_argument("shape mismatch");
-        dx_check(dx_ew_compare(op, A->dx(), A->data, B->data, eps, M->data, A->shape.size, mem.stream()));
+        Rowwise rw(mem, {A, B}, M);
+        dx_check(dx_ew_compare(op, A->dx(), rw.ptr[0], rw.ptr[1], eps, rw.ptr[2], rw.n, mem.stream()));
+        rw.finish();
         return 0;
     }
 };
@@ -133,9 +199,10 @@ struct CompareScalarTF : TF {
         auto A = mem.get_tensor(args[0].textvalue), M = mem.get_tensor(returns[0].textvalue);
         const float eps = (has_eps && args.size() > 2) ? var_f32(2, mem) : 0.f;
         if (M->shape.dtype != P_BOOL) { error = type_mismatch({A->shape.dtype, M->shape.dtype}); return 1; }
-        if (A->shape.shape != M->shape.shape) throw std::invalid_argument("shape mismatch");
+        Rowwise rw(mem, {A}, M);
         const Scalar s = scalar_for(*this, 1, mem);
-        dx_check(dx_ew_compare_scalar(op, A->dx(), A->data, s.f, s.i, eps, M->data, A->shape.size, mem.stream()));
+        dx_check(dx_ew_compare_scalar(op, A->dx(), rw.ptr[0], s.f, s.i, eps, rw.ptr[1], rw.n, mem.stream()));
+        rw.finish();
         return 0;
     }
 };
@@ -147,17 +214,34 @@ struct SwitchTF : TF {  // tf/elementwise_compare.hpp:813-939
     int run(Mem &mem, std::string &error) override {
         auto C = mem.get_tensor(returns[0].textvalue);
         auto cases = mem.get_tensor(args[1].textvalue);
-        std::vector<const void *> ptrs;
+        std::vector<TensorPtr> sources;
         for (const auto &n : vector_text(0)) {
             if (!mem.exists_tensor(n)) { std::cerr << "tensor not found: " << n << std::endl; continue; }  // gettensors, mem.hpp:134-151
             auto t = mem.get_tensor(n);
             if (t->shape.dtype != C->shape.dtype) { error = type_mismatch({t->shape.dtype, C->shape.dtype}); return 1; }
-            if (t->shape.size != C->shape.size) throw std::invalid_argument("shape mismatch");
-            ptrs.push_back(t->data);
+            if (!mem.shard.active() && t->shape.size != C->shape.size) throw std::invalid_argument("shape mismatch");
+            sources.push_back(t);
         }
-        if (cases->shape.shape != C->shape.shape) throw std::invalid_argument("shape mismatch");
-        if (cases->shape.dtype == P_BOOL && ptrs.size() != 2) throw std::invalid_argument("For bool cases, tensors size must be 2");
-        dx_check(dx_switch(C->dx(), ptrs.data(), int(ptrs.size()), cases->dx(), cases->data, C->data, C->shape.size, mem.stream()));
+        if (cases->shape.dtype == P_BOOL && sources.size() != 2) throw std::invalid_argument("For bool cases, tensors size must be 2");
+        std::vector<const void *> ptrs;
+        const void *cases_ptr;
+        void *out_ptr;
+        int64_t count;
+        if (!mem.shard.active()) {  // the reference compares element counts only for the sources, shapes for the cases
+            if (cases->shape.shape != C->shape.shape) throw std::invalid_argument("shape mismatch");
+            for (const auto &t : sources) ptrs.push_back(t->data);
+            cases_ptr = cases->data;
+            out_ptr = C->data;
+            count = C->shape.size;
+            dx_check(dx_switch(C->dx(), ptrs.data(), int(ptrs.size()), cases->dx(), cases_ptr, out_ptr, count, mem.stream()));
+            return 0;
+        }
+        std::vector<TensorPtr> inputs = sources;
+        inputs.push_back(cases);
+        Rowwise rw(mem, inputs, C);
+        for (size_t i = 0; i < sources.size(); ++i) ptrs.push_back(rw.ptr[i]);
+        dx_check(dx_switch(C->dx(), ptrs.data(), int(ptrs.size()), cases->dx(), rw.ptr[sources.size()], rw.ptr.back(), rw.n, mem.stream()));
+        rw.finish();
         return 0;
     }
 };
@@ -169,11 +253,17 @@ struct TodtypeTF : TF {  // tf/elementwise_basic.hpp:13-362
     int run(Mem &mem, std::string &error) override {
         if (!check_tensors({args[0].textvalue, returns[0].textvalue}, mem, error)) return 1;
         auto A = mem.get_tensor(args[0].textvalue), C = mem.get_tensor(returns[0].textvalue);
-        if (A->shape.size != C->shape.size) {
-            error = "Shape mismatch: " + std::to_string(A->shape.size) + " != " + std::to_string(C->shape.size);
-            return 1;
+        if (!A->partitioned() && !C->partitioned()) {
+            if (A->shape.size != C->shape.size) {
+                error = "Shape mismatch: " + std::to_string(A->shape.size) + " != " + std::to_string(C->shape.size);
+                return 1;
+            }
+            dx_check(dx_cast(A->dx(), A->data, C->dx(), C->data, A->shape.size, mem.stream()));
+            return 0;
         }
-        dx_check(dx_cast(A->dx(), A->data, C->dx(), C->data, A->shape.size, mem.stream()));
+        Rowwise rw(mem, {A}, C);  // a cast changes the bytes per element: one side can be partitioned and the other not
+        dx_check(dx_cast(A->dx(), rw.ptr[0], C->dx(), rw.ptr[1], rw.n, mem.stream()));
+        rw.finish();
         return 0;
     }
 };
@@ -191,19 +281,58 @@ struct ReduceTF : TF {
         const bool keepdims = var_bool(2);
         auto B = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != B->shape.dtype) { error = type_mismatch({A->shape.dtype, B->shape.dtype}); return 1; }
-        const std::vector<int> cd = checked_dims(A->shape.shape, dims);
-        const std::vector<int64_t> want = reduced_shape(A->shape.shape, cd, keepdims);
-        int64_t n = 1;
-        for (auto v : want) n *= v;
-        if (n != B->shape.size) throw TensorShapeError(name + ": output has " + std::to_string(B->shape.size) + " elements, expected " + std::to_string(n));
-        const int nd = A->shape.dim();
-        const size_t need = dx_reduce_workspace_bytes(op, A->dx(), A->shape.shape.data(), nd, cd.data(), int(cd.size()));
-        void *ws = need ? mem.scratch(need) : nullptr;
+        const std::vector<int64_t> ag = A->global_shape();
+        const std::vector<int> cd = checked_dims(ag, dims);
+        const ReducePlan plan = plan_reduce(A->layout(), cd, keepdims, B->layout(), dx_comm_max_bytes());
+        if (plan.kind == ReducePlan::REFUSE) throw TensorShapeError(name + ": " + plan.error);
         if (A->data == B->data && A->shape.size != B->shape.size) {
             error = name + ": output tensor is the input tensor";
             return 1;
         }
-        dx_check(dx_reduce(op, A->dx(), A->data, A->shape.shape.data(), nd, cd.data(), int(cd.size()), B->data, ws, need, mem.stream()));
+        const int nd = A->shape.dim();
+        const int64_t *shp = A->shape.shape.data();  // the local rows of a partitioned input
+        const size_t need = dx_reduce_workspace_bytes(op, A->dx(), shp, nd, cd.data(), int(cd.size()));
+        void *ws = need ? mem.scratch(need) : nullptr;
+        void *st = mem.stream();
+        dx_comm *comm = mem.shard.comm;
+        switch (plan.kind) {
+            case ReducePlan::WHOLE:
+            case ReducePlan::ROWS:  // the output's rows follow the input's partition: nothing to exchange
+                dx_check(dx_reduce(op, A->dx(), A->data, shp, nd, cd.data(), int(cd.size()), B->data, ws, need, st));
+                break;
+            case ReducePlan::ROWS_GATHER: {  // replicated output: this rank's rows of it, then the other ranks' blocks
+                void *mine = static_cast<char *>(B->data) + A->row0 * B->row_bytes();
+                dx_check(dx_reduce(op, A->dx(), A->data, shp, nd, cd.data(), int(cd.size()), mine, ws, need, st));
+                dx_check(dx_comm_allgather_rows(comm, B->data, B->shape.shape[0], B->row_bytes(), st));
+                break;
+            }
+            case ReducePlan::COMBINE_DEFERRED:
+                // reduce + publish in one go; the wait for the peers and the combine run when B is next needed
+                dx_check(dx_reduce_allreduce_begin(comm, op, A->dx(), A->data, shp, nd, cd.data(), int(cd.size()), B->data, ws, need, st));
+                break;
+            case ReducePlan::COMBINE_ROUNDS:
+                dx_check(dx_reduce(op, A->dx(), A->data, shp, nd, cd.data(), int(cd.size()), B->data, ws, need, st));
+                dx_check(dx_comm_allreduce(comm, op, A->dx(), B->data, B->shape.size, st));
+                break;
+            case ReducePlan::COMBINE_SCATTER: {
+                // the result is itself partitioned: combine the whole partial in a temporary, keep this rank's rows
+                if (mem.capturing) throw std::runtime_error("a reduction into a row-partitioned output needs a temporary, which a captured program cannot hold");
+                int64_t total = 1;
+                for (auto v : plan.out_global) total *= v;
+                const size_t es = size_t(precision_bits(A->shape.dtype) / 8);
+                void *tmp = dx_pool_alloc(mem.pool(), std::max<size_t>(size_t(total) * es, 1));
+                if (!tmp) throw std::runtime_error(dx_last_error());
+                int rc = dx_reduce(op, A->dx(), A->data, shp, nd, cd.data(), int(cd.size()), tmp, ws, need, st);
+                if (rc == DX_OK) rc = dx_comm_allreduce(comm, op, A->dx(), tmp, total, st);
+                if (rc == DX_OK && B->shape.bytes() > 0)
+                    cudaMemcpyAsync(B->data, static_cast<char *>(tmp) + B->row0 * B->row_bytes(), size_t(B->shape.bytes()), cudaMemcpyDeviceToDevice,
+                                    static_cast<cudaStream_t>(st));
+                dx_pool_free(mem.pool(), tmp);  // reuse is ordered behind the copy on the one compute stream
+                dx_check(rc);
+                break;
+            }
+            default: break;
+        }
         return 0;
     }
 };
@@ -236,9 +365,16 @@ struct ReshapeTF : TF {  // :17-83; tensorfunc changeshape_miaobyte.hpp:17-42
     DX_TF_BOILERPLATE(ReshapeTF)
     int run(Mem &mem, std::string &error) override {
         auto A = mem.get_tensor(args[0].textvalue);
-        const std::vector<int64_t> ns = vector_i64(1);
+        std::vector<int64_t> ns = vector_i64(1);
         auto B = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != B->shape.dtype) { error = type_mismatch({A->shape.dtype, B->shape.dtype}); return 1; }
+        if (A->partitioned() || B->partitioned()) {
+            // the rows stay where they are only if the new shape keeps the leading axis
+            if (!A->partitioned() || !B->partitioned() || A->global_rows != B->global_rows || ns.empty() || ns[0] != A->global_rows)
+                throw std::runtime_error("reshape: a row-partitioned tensor can only be reshaped to a shape with the same leading axis (" +
+                                         std::to_string(A->partitioned() ? A->global_rows : B->global_rows) + " rows)");
+            ns[0] = A->shape.shape[0];  // the local rows
+        }
         int64_t prod = 1;
         for (auto v : ns) prod *= v;
         if (A->shape.size != prod) throw std::invalid_argument("Shape size mismatch");
@@ -263,6 +399,9 @@ struct TransposeTF : TF {  // :85-152
         auto C = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != C->shape.dtype) { error = type_mismatch({A->shape.dtype, C->shape.dtype}); return 1; }
         if (int(order.size()) != A->shape.dim()) throw std::invalid_argument("dimOrder size does not match the number of dimensions in the TensorCPU.");
+        if (A->partitioned() || C->partitioned()) {
+            if (!(A->partitioned() && C->partitioned() && A->global_rows == C->global_rows && order[0] == 0)) refuse_partitioned("transpose (an order that moves axis 0)", {A, C});
+        }
         if (C->shape.size != A->shape.size) throw std::runtime_error("transpose error!shape");
         Staged st(mem, C, A->data == C->data);
         dx_check(dx_transpose(A->dx(), A->data, A->shape.shape.data(), A->shape.dim(), order.data(), st.dst(), mem.stream()));
@@ -290,6 +429,8 @@ struct ConcatTF : TF {  // :154-287
         int64_t total = 0;
         for (const auto &n : names) {
             auto t = mem.get_tensor(n);
+            if (t->partitioned() != C->partitioned() || (C->partitioned() && (axis == 0 || t->global_rows != C->global_rows)))
+                refuse_partitioned("concat (along axis 0, or of tensors that are not all partitioned alike)", {t->partitioned() ? t : C});
             if (t->shape.dtype != C->shape.dtype) { error = type_mismatch({t->shape.dtype, C->shape.dtype}); return 1; }
             if (t->shape.dim() != nd) throw TensorShapeError("All input tensors must have the same dimension size for concat");
             for (int j = 0; j < nd; ++j)
@@ -315,9 +456,16 @@ struct BroadcastToTF : TF {  // :289-353
     DX_TF_BOILERPLATE(BroadcastToTF)
     int run(Mem &mem, std::string &error) override {
         auto A = mem.get_tensor(args[0].textvalue);
-        const std::vector<int64_t> ns = vector_i64(1);
+        std::vector<int64_t> ns = vector_i64(1);
         auto B = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != B->shape.dtype) { error = type_mismatch({A->shape.dtype, B->shape.dtype}); return 1; }
+        if (A->partitioned() || B->partitioned()) {
+            // rows of the output come from the same rows of a partitioned source, or from a source that has no axis 0 of its own
+            const bool source_ok = A->partitioned() ? (A->shape.dim() == int(ns.size()) && !ns.empty() && A->global_rows == ns[0])
+                                                    : (A->shape.dim() < int(ns.size()) || (A->shape.dim() > 0 && A->shape.shape[0] == 1));
+            if (!B->partitioned() || ns.empty() || B->global_rows != ns[0] || !source_ok) refuse_partitioned("broadcastTo (source and output rows do not line up)", {A, B});
+            ns[0] = B->shape.shape[0];
+        }
         const auto bs = broadcast_shape(A->shape.shape, ns);
         if (bs.empty() || bs != ns || B->shape.shape != ns) throw TensorShapeError("Broadcast shape mismatch");
         Staged st(mem, B, A->data == B->data);
@@ -344,6 +492,12 @@ struct IndexSelectTF : TF {  // :355-499
         }
         const int axis = axis_in < 0 ? axis_in + A->shape.dim() : axis_in;
         if (axis < 0 || axis >= A->shape.dim()) throw std::invalid_argument("Axis is out of bounds");
+        if (A->partitioned() || I->partitioned() || B->partitioned()) {
+            // rows of a replicated table picked by a partitioned index, or positions along an inner axis of a partitioned table
+            const bool by_index_rows = axis == 0 && !A->partitioned() && I->partitioned() && B->partitioned() && I->global_rows == B->global_rows;
+            const bool by_table_rows = axis > 0 && A->partitioned() && !I->partitioned() && B->partitioned() && A->global_rows == B->global_rows;
+            if (!by_index_rows && !by_table_rows) refuse_partitioned("indexselect (operands whose rows do not line up)", {A, I, B});
+        }
         if (indexselect_shape(A->shape.shape, I->shape.shape, axis) != B->shape.shape) throw TensorShapeError("Indexselect shape mismatch");
         Staged st(mem, B, A->data == B->data);
         dx_check(dx_indexselect(A->dx(), A->data, A->shape.shape.data(), A->shape.dim(), I->dx(), I->data, I->shape.shape.data(),
@@ -362,6 +516,9 @@ struct RepeatTF : TF {  // :501-566
         const std::vector<int64_t> r64 = vector_i64(1);
         auto B = mem.get_tensor(returns[0].textvalue);
         if (A->shape.dtype != B->shape.dtype) { error = type_mismatch({A->shape.dtype, B->shape.dtype}); return 1; }
+        if (A->partitioned() || B->partitioned()) {
+            if (!(A->partitioned() && B->partitioned() && !r64.empty() && r64[0] == 1 && A->global_rows == B->global_rows)) refuse_partitioned("repeat (along axis 0)", {A, B});
+        }
         if (repeat_shape(A->shape.shape, r64) != B->shape.shape) throw TensorShapeError("Repeat shape mismatch");
         Staged st(mem, B, A->data == B->data);
         dx_check(dx_repeat(A->dx(), A->data, A->shape.shape.data(), A->shape.dim(), r64.data(), st.dst(), mem.stream()));
@@ -381,6 +538,13 @@ struct MatMulTF : TF {
         if (A->shape.dtype != B->shape.dtype || A->shape.dtype != C->shape.dtype) {
             error = type_mismatch({A->shape.dtype, B->shape.dtype, C->shape.dtype});
             return 1;
+        }
+        if (A->partitioned() || B->partitioned() || C->partitioned()) {
+            // rows of A against a replicated B (2-D), or whole matrices of a batch partitioned along its leading axis
+            const bool by_rows = A->shape.dim() == 2 && A->partitioned() && !B->partitioned() && C->partitioned() && A->global_rows == C->global_rows;
+            const bool by_batch = A->shape.dim() > 2 && A->partitioned() && B->partitioned() && C->partitioned() && A->global_rows == B->global_rows &&
+                                  A->global_rows == C->global_rows;
+            if (!by_rows && !by_batch) refuse_partitioned("matmul (operands whose rows do not line up)", {A, B, C});
         }
         if (!check_matmul_shape(A->shape.shape, B->shape.shape)) throw std::invalid_argument("A.shape could matmul with B.shape");
         const int64_t m = A->shape.at(-2), k = A->shape.at(-1), n = B->shape.at(-1);
@@ -424,6 +588,13 @@ struct CopyTensorTF : TF {
         if (!check_tensors({args[0].textvalue, returns[0].textvalue}, mem, error)) return 1;
         auto S = mem.get_tensor(args[0].textvalue), D = mem.get_tensor(returns[0].textvalue);
         if (S->shape.dtype != D->shape.dtype) { error = "copytensor: input type and return type must be the same"; return 1; }
+        if (S->partitioned() || D->partitioned()) {
+            Rowwise rw(mem, {S}, D);
+            if (rw.ptr[0] != rw.ptr[1] && rw.n > 0)
+                cudaMemcpyAsync(rw.ptr[1], rw.ptr[0], size_t(rw.n) * size_t(precision_bits(S->shape.dtype) / 8), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(mem.stream()));
+            rw.finish();
+            return 0;
+        }
         if (D->shape.size < S->shape.size) { error = "copytensor: destination is smaller than the source"; return 1; }
         if (S->data != D->data)
             cudaMemcpyAsync(D->data, S->data, size_t(S->shape.bytes()), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(mem.stream()));
@@ -508,10 +679,16 @@ struct InitTF : TF {
                 }
                 break;
             }
-            case ARANGE: dx_check(dx_arange(T->dx(), T->data, var_f32(0, mem), var_f32(1, mem), T->shape.size, st)); break;
-            case UNIFORM: dx_check(dx_uniform(T->dx(), T->data, var_f32(0, mem), var_f32(1, mem), uint64_t(uint32_t(var_int(2, mem))), T->shape.size, st)); break;
-            case NORMAL: dx_check(dx_normal(T->dx(), T->data, var_f32(0, mem), var_f32(1, mem), uint64_t(uint32_t(var_int(2, mem))), T->shape.size, st)); break;
-            case DROPOUT: dx_check(dx_dropout(T->dx(), T->data, var_f32(0, mem), uint64_t(uint32_t(var_int(1, mem))), T->shape.size, st)); break;
+            case ARANGE: {
+                // a partitioned tensor continues the sequence where its first local element sits
+                const double start = var_f32(0, mem), step = var_f32(1, mem);
+                const double first = T->partitioned() && T->shape.shape[0] > 0 ? double(T->row0) * double(T->shape.size / T->shape.shape[0]) : 0.0;
+                dx_check(dx_arange(T->dx(), T->data, start + step * first, step, T->shape.size, st));
+                break;
+            }
+            case UNIFORM: refuse_partitioned(name + " (the random stream is per tensor, not per row block)", {T}); dx_check(dx_uniform(T->dx(), T->data, var_f32(0, mem), var_f32(1, mem), uint64_t(uint32_t(var_int(2, mem))), T->shape.size, st)); break;
+            case NORMAL: refuse_partitioned(name + " (the random stream is per tensor, not per row block)", {T}); dx_check(dx_normal(T->dx(), T->data, var_f32(0, mem), var_f32(1, mem), uint64_t(uint32_t(var_int(2, mem))), T->shape.size, st)); break;
+            case DROPOUT: refuse_partitioned(name + " (the random stream is per tensor, not per row block)", {T}); dx_check(dx_dropout(T->dx(), T->data, var_f32(0, mem), uint64_t(uint32_t(var_int(1, mem))), T->shape.size, st)); break;
         }
         return 0;
     }
@@ -624,6 +801,9 @@ struct PrintTF : TF {  // tf/io.hpp:17-99, layout of stdutil/print.hpp:84-129
         if (!checked_print_format(asked, T->shape.dtype, fmt, error)) return 1;
         const std::vector<char> host = download(mem, *T);
         const Shape &s = T->shape;
+        if (T->partitioned())
+            std::printf("rows %lld..%lld of %lld (rank %d of %d)\n", (long long)T->row0, (long long)(T->row0 + (s.dim() ? s.shape[0] : 0)),
+                        (long long)T->global_rows, mem.shard.rank, mem.shard.world);
         std::printf("shape:[");
         for (int i = 0; i < s.dim(); ++i) std::printf("%s%lld", i ? ", " : "", (long long)s.shape[i]);
         std::printf("]\n");
@@ -663,6 +843,7 @@ void load_data_into(Mem &mem, const std::string &path, Tensor &t) {
     std::ifstream in(path + ".data", std::ios::binary);
     if (!in.is_open()) throw std::runtime_error("Failed to open file: " + path + ".data");
     std::vector<char> host(size_t(t.shape.bytes()));
+    if (t.partitioned()) in.seekg(std::streamoff(t.row0 * t.row_bytes()));  // this rank's rows of the file a single GPU would read whole
     in.read(host.data(), std::streamsize(host.size()));
     if (size_t(in.gcount()) != host.size()) throw std::runtime_error("file size mismatch: " + path + ".data");
     cudaStream_t st = static_cast<cudaStream_t>(mem.stream());
@@ -680,6 +861,34 @@ struct SaveTF : TF {
         if (!mem.exists_tensor(n)) { error = "save " + n + " not found"; return 1; }
         auto T = mem.get_tensor(n);
         const std::vector<char> host = download(mem, *T);
+        if (mem.shard.active()) {
+            // Every rank runs the same line on a file system they share: the files must come out as a single GPU would
+            // write them.  Rank 0 writes the description (of the GLOBAL shape) and sets the data file's size; each rank
+            // writes its own rows at their offset (a replicated tensor is written by rank 0 alone).
+            Shape g = T->shape;
+            if (T->partitioned()) { g.set(T->global_shape()); g.dtype = T->shape.dtype; }
+            const int fd = ::open((path + ".data").c_str(), O_WRONLY | O_CREAT, 0644);
+            if (fd < 0) { error = "save: cannot write " + path; return 1; }
+            bool ok = true;
+            if (mem.shard.rank == 0) {
+                std::ofstream sf(path + ".shape", std::ios::binary);
+                const std::string y = g.to_yaml();
+                sf.write(y.data(), std::streamsize(y.size()));
+                ok = sf.good() && ::ftruncate(fd, off_t(g.bytes())) == 0;
+            }
+            if (ok && (T->partitioned() || mem.shard.rank == 0)) {
+                const off_t at = T->partitioned() ? off_t(T->row0 * T->row_bytes()) : 0;
+                size_t done = 0;
+                while (ok && done < host.size()) {
+                    const ssize_t w = ::pwrite(fd, host.data() + done, host.size() - done, at + off_t(done));
+                    ok = w > 0;
+                    done += ok ? size_t(w) : 0;
+                }
+            }
+            ::close(fd);
+            if (!ok) { error = "save: cannot write " + path; return 1; }
+            return 0;
+        }
         std::ofstream sf(path + ".shape", std::ios::binary);
         const std::string y = T->shape.to_yaml();
         sf.write(y.data(), std::streamsize(y.size()));
@@ -748,7 +957,9 @@ struct RmsNormTF : TF {
             error = W ? type_mismatch({X->shape.dtype, W->shape.dtype, O->shape.dtype}) : type_mismatch({X->shape.dtype, O->shape.dtype});
             return 1;
         }
-        if (X->shape.dim() < 1 || X->shape.shape != O->shape.shape) throw std::invalid_argument("shape mismatch");
+        if (X->shape.dim() < 1 || X->shape.shape != O->shape.shape || X->global_rows != O->global_rows) throw std::invalid_argument("shape mismatch");
+        if (X->shape.dim() == 1) refuse_partitioned("rmsnorm (over the partitioned axis)", {X});
+        if (W) refuse_partitioned("rmsnorm (weight)", {W});
         const int64_t cols = X->shape.shape.back();
         if (W && (W->shape.size != cols || W->shape.dim() < 1 || W->shape.shape.back() != cols))
             throw TensorShapeError("rmsnorm: weight must hold one row of " + std::to_string(cols) + " elements");
@@ -766,7 +977,8 @@ struct SoftmaxTF : TF {
         if (!check_tensors({args[0].textvalue, returns[0].textvalue}, mem, error)) return 1;
         auto X = mem.get_tensor(args[0].textvalue), O = mem.get_tensor(returns[0].textvalue);
         if (X->shape.dtype != O->shape.dtype) { error = type_mismatch({X->shape.dtype, O->shape.dtype}); return 1; }
-        if (X->shape.dim() < 1 || X->shape.shape != O->shape.shape) throw std::invalid_argument("shape mismatch");
+        if (X->shape.dim() < 1 || X->shape.shape != O->shape.shape || X->global_rows != O->global_rows) throw std::invalid_argument("shape mismatch");
+        if (X->shape.dim() == 1) refuse_partitioned("softmax (over the partitioned axis)", {X});
         const int64_t cols = X->shape.shape.back();
         dx_check(dx_softmax(X->dx(), X->data, O->data, cols ? X->shape.size / cols : 0, cols, mem.stream()));
         return 0;

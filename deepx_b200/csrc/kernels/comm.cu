@@ -18,6 +18,13 @@
 // reading e.  The epoch of a chunk lives in the mailbox and is advanced by the kernel itself, so a
 // captured launch can be replayed.
 //
+// The exchange comes in two halves (comm.cuh): publish (steps 1–2) and combine (steps 3–4).  One kernel can
+// do both, or a reduction can end with the publish (dx_reduce_allreduce_begin) and the combine runs as a
+// kernel of its own later on the stream (dx_comm_allreduce_finish): the kernels in between hide the skew
+// between the ranks, which otherwise shows up as a wait in every step.  Buffers larger than a slot take
+// several rounds of the same kernel.  dx_comm_allgather_rows moves row blocks instead of combining values:
+// every rank fills its own rows of a buffer that all ranks hold, and fetches the others'.
+//
 // Every wait is bounded (default 2 s, dx_comm_set_timeout_ms); when one expires the kernel records
 // which (chunk, peer) it gave up on, skips the combine and returns, and dx_comm_status reports it.
 // The reference has no multi-GPU code at all; the alternative here is an NCCL all-reduce of the
@@ -38,6 +45,18 @@ __global__ void __launch_bounds__(COMM_THREADS) peer_allreduce_kernel(Peers peer
     exchange_chunk<OP, T>(peers, rank, blockIdx.x, buf, n, wait_cycles);
 }
 
+template <typename T>
+__global__ void __launch_bounds__(COMM_THREADS) peer_publish_kernel(Peers peers, int rank, const T *buf, int64_t n, T pad) {
+    exchange_publish<T>(peers, rank, blockIdx.x, buf, n, pad);
+}
+template <int OP, typename T>
+__global__ void __launch_bounds__(COMM_THREADS) peer_combine_kernel(Peers peers, int rank, T *buf, int64_t n, long long wait_cycles) {
+    exchange_combine<OP, T>(peers, rank, blockIdx.x, buf, n, wait_cycles);
+}
+__global__ void __launch_bounds__(COMM_THREADS) peer_gather_kernel(Peers peers, int rank, unsigned char *buf, GatherPlan plan, long long wait_cycles) {
+    gather_chunk(peers, rank, blockIdx.x, buf, plan, wait_cycles);
+}
+
 // All ranks in ONE launch on one GPU (blockIdx.y = rank), every mailbox local: the same protocol
 // where there are fewer GPUs than ranks.  Ranks >= `active` are left out, so that the others'
 // waits run into their limit (the failure path, without a second process that misbehaves).
@@ -48,6 +67,20 @@ template <int OP, typename T>
 __global__ void __launch_bounds__(COMM_THREADS) emulated_allreduce_kernel(Peers peers, Bufs bufs, int active, int64_t n, long long wait_cycles) {
     if (int(blockIdx.y) >= active) return;
     exchange_chunk<OP, T>(peers, blockIdx.y, blockIdx.x, static_cast<T *>(bufs.buf[blockIdx.y]), n, wait_cycles);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(COMM_THREADS) emulated_publish_kernel(Peers peers, Bufs bufs, int active, int64_t n, T pad) {
+    if (int(blockIdx.y) >= active) return;
+    exchange_publish<T>(peers, blockIdx.y, blockIdx.x, static_cast<const T *>(bufs.buf[blockIdx.y]), n, pad);
+}
+template <int OP, typename T>
+__global__ void __launch_bounds__(COMM_THREADS) emulated_combine_kernel(Peers peers, Bufs bufs, int active, int64_t n, long long wait_cycles) {
+    if (int(blockIdx.y) >= active) return;
+    exchange_combine<OP, T>(peers, blockIdx.y, blockIdx.x, static_cast<T *>(bufs.buf[blockIdx.y]), n, wait_cycles);
+}
+__global__ void __launch_bounds__(COMM_THREADS) emulated_gather_kernel(Peers peers, Bufs bufs, GatherPlan plan, long long wait_cycles) {
+    gather_chunk(peers, blockIdx.y, blockIdx.x, static_cast<unsigned char *>(bufs.buf[blockIdx.y]), plan, wait_cycles);
 }
 
 }  // namespace
@@ -61,6 +94,11 @@ struct dx_comm {
     bool connected = false;
     long long wait_cycles = 4000000000ll;
     std::vector<dx::Mailbox *> emulated;  // dx_comm_emulate: all mailboxes local
+    // an exchange that has been published and still waits for its combine
+    bool pending = false;
+    int pending_op = 0, pending_dtype = 0;
+    void *pending_buf = nullptr;
+    int64_t pending_n = 0;
 };
 
 namespace dx {
@@ -79,6 +117,35 @@ template <int OP, typename T> int launch_emulated(dx_comm *c, void *const *bufs,
     for (int r = 0; r < c->world; ++r) b.buf[r] = bufs[r];
     emulated_allreduce_kernel<OP, T><<<dim3(chunks, c->world), COMM_THREADS, 0, st>>>(c->peers, b, active, n, c->wait_cycles);
     return check_launch("comm allreduce (emulated ranks)");
+}
+
+template <int OP, typename T> int launch_publish(dx_comm *c, void *buf, int64_t n, cudaStream_t st) {
+    constexpr int PER = COMM_CHUNK / int(sizeof(T));
+    const int chunks = int((n + PER - 1) / PER);
+    peer_publish_kernel<T><<<chunks, COMM_THREADS, 0, st>>>(c->peers, c->rank, static_cast<const T *>(buf), n, narrow<T>(identity<OP, T>()));
+    return check_launch("comm publish");
+}
+template <int OP, typename T> int launch_combine(dx_comm *c, void *buf, int64_t n, cudaStream_t st) {
+    constexpr int PER = COMM_CHUNK / int(sizeof(T));
+    const int chunks = int((n + PER - 1) / PER);
+    peer_combine_kernel<OP, T><<<chunks, COMM_THREADS, 0, st>>>(c->peers, c->rank, static_cast<T *>(buf), n, c->wait_cycles);
+    return check_launch("comm combine");
+}
+template <int OP, typename T> int launch_emulated_publish(dx_comm *c, void *const *bufs, int active, int64_t n, cudaStream_t st) {
+    constexpr int PER = COMM_CHUNK / int(sizeof(T));
+    const int chunks = int((n + PER - 1) / PER);
+    Bufs b{};
+    for (int r = 0; r < c->world; ++r) b.buf[r] = bufs[r];
+    emulated_publish_kernel<T><<<dim3(chunks, c->world), COMM_THREADS, 0, st>>>(c->peers, b, active, n, narrow<T>(identity<OP, T>()));
+    return check_launch("comm publish (emulated ranks)");
+}
+template <int OP, typename T> int launch_emulated_combine(dx_comm *c, void *const *bufs, int active, int64_t n, cudaStream_t st) {
+    constexpr int PER = COMM_CHUNK / int(sizeof(T));
+    const int chunks = int((n + PER - 1) / PER);
+    Bufs b{};
+    for (int r = 0; r < c->world; ++r) b.buf[r] = bufs[r];
+    emulated_combine_kernel<OP, T><<<dim3(chunks, c->world), COMM_THREADS, 0, st>>>(c->peers, b, active, n, c->wait_cycles);
+    return check_launch("comm combine (emulated ranks)");
 }
 
 #define DX_COMM_BY_OP(FN, T, ...)                                             \
@@ -105,6 +172,15 @@ template <int OP, typename T> int launch_emulated(dx_comm *c, void *const *bufs,
 int real_dispatch(dx_comm *c, int op, int dtype, void *buf, int64_t n, cudaStream_t st) { DX_COMM_DISPATCH(launch_real, c, buf, n, st) }
 int emulated_dispatch(dx_comm *c, int op, int dtype, void *const *bufs, int active, int64_t n, cudaStream_t st) {
     DX_COMM_DISPATCH(launch_emulated, c, bufs, active, n, st)
+}
+
+int publish_dispatch(dx_comm *c, int op, int dtype, void *buf, int64_t n, cudaStream_t st) { DX_COMM_DISPATCH(launch_publish, c, buf, n, st) }
+int combine_dispatch(dx_comm *c, int op, int dtype, void *buf, int64_t n, cudaStream_t st) { DX_COMM_DISPATCH(launch_combine, c, buf, n, st) }
+int emulated_publish_dispatch(dx_comm *c, int op, int dtype, void *const *bufs, int active, int64_t n, cudaStream_t st) {
+    DX_COMM_DISPATCH(launch_emulated_publish, c, bufs, active, n, st)
+}
+int emulated_combine_dispatch(dx_comm *c, int op, int dtype, void *const *bufs, int active, int64_t n, cudaStream_t st) {
+    DX_COMM_DISPATCH(launch_emulated_combine, c, bufs, active, n, st)
 }
 
 int check_size(int dtype, int64_t n) {
@@ -134,6 +210,18 @@ bool comm_device_view(dx_comm *c, Peers *peers, int *rank, long long *wait_cycle
     *rank = c->rank;
     *wait_cycles = c->wait_cycles;
     return true;
+}
+void comm_set_pending(dx_comm *c, int op, int dtype, void *buf, int64_t n) {
+    c->pending = true;
+    c->pending_op = op;
+    c->pending_dtype = dtype;
+    c->pending_buf = buf;
+    c->pending_n = n;
+}
+int comm_flush_pending(dx_comm *c, cudaStream_t st) {
+    if (!c || !c->pending) return DX_OK;
+    c->pending = false;
+    return combine_dispatch(c, c->pending_op, c->pending_dtype, c->pending_buf, c->pending_n, st);
 }
 }  // namespace dx
 
@@ -206,9 +294,85 @@ extern "C" int dx_comm_allreduce(dx_comm *c, int op, int dtype, void *buf, int64
     if (!c || !buf) return fail(DX_E_ARG, "comm: null argument");
     if (!c->connected) return fail(DX_E_ARG, "comm: dx_comm_connect has not been called");
     if (!c->emulated.empty()) return fail(DX_E_ARG, "comm: this communicator emulates its ranks on one GPU; use dx_comm_emulated_allreduce");
-    if (int e = check_size(dtype, n)) return e;
+    const int es = dx_dtype_size(dtype);
+    if (es == 0 || dtype == DX_BOOL) return fail(DX_E_DTYPE, "comm: unsupported dtype code %d", dtype);
+    if (n < 0) return fail(DX_E_SHAPE, "comm: negative count");
     if (n == 0) return DX_OK;
-    return real_dispatch(c, op, dtype, buf, n, as_stream(stream));
+    if (int e = comm_flush_pending(c, as_stream(stream))) return e;
+    // a buffer larger than a slot goes in rounds of one slot each (the parity double-buffering lets round k+1
+    // start while a peer still reads round k, and nobody can get two rounds ahead)
+    const int64_t per_round = COMM_SLOT / es;
+    for (int64_t first = 0; first < n; first += per_round) {
+        const int64_t count = n - first < per_round ? n - first : per_round;
+        if (int e = real_dispatch(c, op, dtype, static_cast<unsigned char *>(buf) + first * es, count, as_stream(stream))) return e;
+    }
+    return DX_OK;
+}
+
+extern "C" int dx_comm_rank(dx_comm *c) { return c ? c->rank : -1; }
+extern "C" int dx_comm_world(dx_comm *c) { return c ? c->world : 0; }
+
+extern "C" void dx_shard_rows(int64_t global_rows, int rank, int world, int64_t *row0, int64_t *rows) {
+    if (world < 1) world = 1;
+    const int64_t base = global_rows / world, extra = global_rows % world;
+    if (rows) *rows = base + (rank < extra ? 1 : 0);
+    if (row0) *row0 = rank * base + (rank < extra ? rank : extra);
+}
+
+extern "C" int dx_comm_allreduce_begin(dx_comm *c, int op, int dtype, void *buf, int64_t n, void *stream) {
+    if (!c || !buf) return fail(DX_E_ARG, "comm: null argument");
+    if (!c->connected) return fail(DX_E_ARG, "comm: dx_comm_connect has not been called");
+    if (!c->emulated.empty()) return fail(DX_E_ARG, "comm: this communicator emulates its ranks on one GPU");
+    if (int e = check_size(dtype, n)) return e;
+    if (int e = comm_flush_pending(c, as_stream(stream))) return e;
+    if (n == 0) return DX_OK;
+    if (int e = publish_dispatch(c, op, dtype, buf, n, as_stream(stream))) return e;
+    comm_set_pending(c, op, dtype, buf, n);
+    return DX_OK;
+}
+
+extern "C" int dx_comm_allreduce_finish(dx_comm *c, void *stream) {
+    if (!c) return fail(DX_E_ARG, "comm: null argument");
+    return comm_flush_pending(c, as_stream(stream));
+}
+
+extern "C" int dx_comm_pending(dx_comm *c, void **buf) {
+    if (!c || !c->pending) return 0;
+    if (buf) *buf = c->pending_buf;
+    return 1;
+}
+
+namespace {
+// the per-round byte ranges of an all-gather of row blocks; false when nothing is left to move
+bool gather_round(int world, int64_t global_rows, int64_t row_bytes, int64_t round, GatherPlan *g, int *chunks) {
+    int64_t longest = 0;
+    for (int r = 0; r < world; ++r) {
+        int64_t row0, rows;
+        dx_shard_rows(global_rows, r, world, &row0, &rows);
+        const int64_t len = rows * row_bytes - round * COMM_SLOT;
+        g->off[r] = row0 * row_bytes + round * COMM_SLOT;
+        g->len[r] = len <= 0 ? 0 : (len < COMM_SLOT ? len : COMM_SLOT);
+        longest = g->len[r] > longest ? g->len[r] : longest;
+    }
+    *chunks = int((longest + COMM_CHUNK - 1) / COMM_CHUNK);
+    return longest > 0;
+}
+}  // namespace
+
+extern "C" int dx_comm_allgather_rows(dx_comm *c, void *buf, int64_t global_rows, int64_t row_bytes, void *stream) {
+    if (!c || !buf) return fail(DX_E_ARG, "comm: null argument");
+    if (!c->connected) return fail(DX_E_ARG, "comm: dx_comm_connect has not been called");
+    if (!c->emulated.empty()) return fail(DX_E_ARG, "comm: this communicator emulates its ranks on one GPU; use dx_comm_emulated_allgather_rows");
+    if (global_rows < 0 || row_bytes < 0) return fail(DX_E_SHAPE, "comm: negative extent");
+    if (c->world == 1) return DX_OK;
+    if (int e = comm_flush_pending(c, as_stream(stream))) return e;
+    GatherPlan g;
+    int chunks;
+    for (int64_t round = 0; gather_round(c->world, global_rows, row_bytes, round, &g, &chunks); ++round) {
+        peer_gather_kernel<<<chunks, COMM_THREADS, 0, as_stream(stream)>>>(c->peers, c->rank, static_cast<unsigned char *>(buf), g, c->wait_cycles);
+        if (int e = check_launch("comm allgather")) return e;
+    }
+    return DX_OK;
 }
 
 extern "C" int dx_comm_status(dx_comm *c, void *stream) {
@@ -287,4 +451,38 @@ extern "C" int dx_comm_emulated_allreduce(dx_comm *c, int op, int dtype, void *c
     const int64_t chunks = (n * es + COMM_CHUNK - 1) / COMM_CHUNK;
     if (chunks * c->world > sm_count()) return fail(DX_E_UNSUPPORTED, "comm: %lld CTAs would not all be resident", (long long)(chunks * c->world));
     return emulated_dispatch(c, op, dtype, bufs, active_ranks, n, as_stream(stream));
+}
+
+// The two halves as separate launches (what dx_reduce_allreduce_begin / dx_comm_allreduce_finish do on real ranks).
+extern "C" int dx_comm_emulated_publish(dx_comm *c, int op, int dtype, void *const *bufs, int active_ranks, int64_t n, void *stream) {
+    if (!c || !bufs) return fail(DX_E_ARG, "comm: null argument");
+    if (c->emulated.empty()) return fail(DX_E_ARG, "comm: not an emulating communicator (dx_comm_emulate)");
+    if (active_ranks < 1 || active_ranks > c->world) return fail(DX_E_ARG, "comm: %d active ranks of %d", active_ranks, c->world);
+    if (int e = check_size(dtype, n)) return e;
+    if (n == 0) return DX_OK;
+    return emulated_publish_dispatch(c, op, dtype, bufs, active_ranks, n, as_stream(stream));
+}
+extern "C" int dx_comm_emulated_combine(dx_comm *c, int op, int dtype, void *const *bufs, int active_ranks, int64_t n, void *stream) {
+    if (!c || !bufs) return fail(DX_E_ARG, "comm: null argument");
+    if (c->emulated.empty()) return fail(DX_E_ARG, "comm: not an emulating communicator (dx_comm_emulate)");
+    if (active_ranks < 1 || active_ranks > c->world) return fail(DX_E_ARG, "comm: %d active ranks of %d", active_ranks, c->world);
+    if (int e = check_size(dtype, n)) return e;
+    if (n == 0) return DX_OK;
+    return emulated_combine_dispatch(c, op, dtype, bufs, active_ranks, n, as_stream(stream));
+}
+// All ranks' row blocks gathered in one launch per round (every CTA of a round must be resident at once).
+extern "C" int dx_comm_emulated_allgather_rows(dx_comm *c, void *const *bufs, int64_t global_rows, int64_t row_bytes, void *stream) {
+    if (!c || !bufs) return fail(DX_E_ARG, "comm: null argument");
+    if (c->emulated.empty()) return fail(DX_E_ARG, "comm: not an emulating communicator (dx_comm_emulate)");
+    if (global_rows < 0 || row_bytes < 0) return fail(DX_E_SHAPE, "comm: negative extent");
+    Bufs b{};
+    for (int r = 0; r < c->world; ++r) b.buf[r] = bufs[r];
+    GatherPlan g;
+    int chunks;
+    for (int64_t round = 0; gather_round(c->world, global_rows, row_bytes, round, &g, &chunks); ++round) {
+        if (int64_t(chunks) * c->world > sm_count()) return fail(DX_E_UNSUPPORTED, "comm: %lld CTAs would not all be resident", (long long)chunks * c->world);
+        emulated_gather_kernel<<<dim3(chunks, c->world), COMM_THREADS, 0, as_stream(stream)>>>(c->peers, b, g, c->wait_cycles);
+        if (int e = check_launch("comm allgather (emulated ranks)")) return e;
+    }
+    return DX_OK;
 }

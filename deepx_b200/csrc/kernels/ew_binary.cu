@@ -1,4 +1,6 @@
 // dx_ew_binary / dx_ew_scalar: C = A ∘ B and C = A ∘ s.
+#include <cmath>
+
 #include "ew_launch.cuh"
 #include "ew_ops.cuh"
 
@@ -109,6 +111,15 @@ extern "C" int dx_ew_scalar(int op, int dtype, const void *a, double fs, int64_t
         if (fs == 1.0) return pow_small<1>(dtype, a, c, n, st);
         if (fs == 3.0) return pow_small<3>(dtype, a, c, n, st);
         if (fs == -1.0) return pow_small<-1>(dtype, a, c, n, st);
+    }
+    if (op == DX_RPOWS && dtype == DX_F32) {
+        // constant base: log2 of it once, in double, as a sum of two floats (positive normal bases; others take the general path)
+        const float base = static_cast<float>(fs);
+        if (base >= 1.17549435e-38f && base <= 3.40282347e+38f) {
+            const double l = std::log2(static_cast<double>(base));
+            const float l_hi = static_cast<float>(l);
+            return launch_ew1((const float *)a, (float *)c, n, RPowConstFn{base, l_hi, static_cast<float>(l - static_cast<double>(l_hi))}, st, "ew_scalar");
+        }
     }
     if (op == DX_DIVS && (dtype == DX_I8 || dtype == DX_I16)) {
         const int64_t d = dtype == DX_I8 ? int64_t(int8_t(is)) : int64_t(int16_t(is));  // the scalar as the element type holds it

@@ -74,8 +74,13 @@ __global__ void __launch_bounds__(EW_BLOCK)
 #pragma unroll
         for (int u = 0; u < EW_UNROLL; ++u) {
             Pack<TC, VEC> vc;
+            if constexpr (functor_has_pair<F>::value && VEC % 2 == 0) {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) vc.v[i] = f(va[u].v[i], vb[u].v[i]);
+                for (int i = 0; i < VEC; i += 2) f.pair(va[u].v[i], va[u].v[i + 1], vb[u].v[i], vb[u].v[i + 1], vc.v[i], vc.v[i + 1]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) vc.v[i] = f(va[u].v[i], vb[u].v[i]);
+            }
             st_stream<TC, VEC>(c + base + (int64_t(u) * EW_BLOCK + threadIdx.x) * VEC, vc);
         }
     } else {

@@ -15,6 +15,107 @@ __device__ __forceinline__ int trunc_pushed(float q, float push) {
     return __float_as_int(__fadd_rn(u, 12582912.0f)) - 0x4B400000;
 }
 
+// Two fp32 values in one 64-bit register and the packed fp32 instructions of sm_100 (one instruction, two
+// results): the routines below are bound by how many instructions a warp can issue, not by the FMA pipe.
+struct F2 { unsigned long long v; };
+__device__ __forceinline__ F2 f2_pack(float lo, float hi) { F2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(lo), "f"(hi)); return r; }
+__device__ __forceinline__ void f2_unpack(F2 a, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a.v)); }
+__device__ __forceinline__ F2 f2_splat(float c) { return f2_pack(c, c); }
+__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) { F2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v)); return r; }
+__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) { F2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
+__device__ __forceinline__ F2 f2_add(F2 a, F2 b) { F2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
+
+__device__ __forceinline__ float ex2_approx(float t) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+    return r;
+}
+
+// powf for two (x, y) pairs at once, within 3e-6 relative of the correctly rounded result (the bound every float32
+// pow test here uses is 1e-5): x^y = 2^(y·log2 x) with log2 x carried as a sum of two floats.
+//   x = m·2^e, m in [sqrt(1/2), sqrt(2)), by integer arithmetic on the bits; f = m − 1 is exact.
+//   log2 m = f/ln2 + f²·Q(f): Q a degree-8 polynomial (weighted minimax fit, 1.1e-9 absolute on log2 m); the
+//   leading term with 1/ln2 split in two floats and the product's rounding error recovered by an FMA.
+//   L = e + log2 m as hi + lo by two error-free additions; t = y·L as hi + lo the same way.
+//   2^t_hi by the hardware approximation (2^-22 relative), times 1 + ln2·t_lo.
+// The library routine costs 60–80 issue slots per element and held pow at 0.53–0.75 of the copy bandwidth; this is
+// about 36 floating-point operations, issued as packed instructions two elements at a time.  An element whose x is
+// not a positive normal number (zero, negative, subnormal, inf, NaN), whose y is not finite, or whose result would
+// leave [2^-125, 2^125] goes to powf on its own, so a result never depends on which element shares the pair.
+constexpr float POW_Q0 = -7.213471532e-01f, POW_Q1 = 4.808981419e-01f, POW_Q2 = -3.607088029e-01f, POW_Q3 = 2.885792851e-01f,
+                POW_Q4 = -2.393930554e-01f, POW_Q5 = 2.042880207e-01f, POW_Q6 = -1.923508048e-01f, POW_Q7 = 1.883963346e-01f,
+                POW_Q8 = -1.097617820e-01f;
+constexpr float POW_INVLN2_HI = 1.4426950216293335f, POW_INVLN2_LO = 1.925963033500011e-08f, POW_LN2 = 0.693147182f;
+
+// the rare elements the fast path hands back: one copy of the library routine, not one per call site
+static __device__ __noinline__ float powf_library(float x, float y) { return powf(x, y); }
+
+__device__ __forceinline__ void pow_f32_x2(float x0, float x1, float y0, float y1, float &r0, float &r1) {
+    const uint32_t b0 = __float_as_uint(x0), b1 = __float_as_uint(x1);
+    const uint32_t e0 = (b0 - 0x3f3504f3u) & 0xff800000u, e1 = (b1 - 0x3f3504f3u) & 0xff800000u;
+    const F2 one = f2_splat(-1.0f);
+    const F2 f = f2_add(f2_pack(__uint_as_float(b0 - e0), __uint_as_float(b1 - e1)), one);
+    const F2 e = f2_add(f2_pack(__int_as_float(0x4B400000 + (static_cast<int>(e0) >> 23)), __int_as_float(0x4B400000 + (static_cast<int>(e1) >> 23))),
+                        f2_splat(-12582912.0f));
+    F2 q = f2_fma(f2_splat(POW_Q8), f, f2_splat(POW_Q7));
+    q = f2_fma(q, f, f2_splat(POW_Q6));
+    q = f2_fma(q, f, f2_splat(POW_Q5));
+    q = f2_fma(q, f, f2_splat(POW_Q4));
+    q = f2_fma(q, f, f2_splat(POW_Q3));
+    q = f2_fma(q, f, f2_splat(POW_Q2));
+    q = f2_fma(q, f, f2_splat(POW_Q1));
+    q = f2_fma(q, f, f2_splat(POW_Q0));
+    const F2 neg1 = f2_splat(-1.0f);
+    const F2 ff = f2_mul(f, f);
+    const F2 chi = f2_splat(POW_INVLN2_HI);
+    const F2 p_hi = f2_mul(f, chi);
+    F2 p_lo = f2_fma(f, chi, f2_mul(p_hi, neg1));
+    p_lo = f2_fma(f, f2_splat(POW_INVLN2_LO), p_lo);
+    const F2 u = f2_fma(ff, q, p_lo);
+    const F2 s1 = f2_add(p_hi, u);                                  // |p_hi| >= |u|: the two sums below lose nothing
+    const F2 c1 = f2_add(f2_fma(s1, neg1, p_hi), u);
+    const F2 s = f2_add(e, s1);                                     // e is 0 or |e| >= 1 > |s1|
+    const F2 c2 = f2_add(f2_fma(s, neg1, e), s1);
+    const F2 l = f2_add(c1, c2);
+    const F2 y = f2_pack(y0, y1);
+    const F2 t_hi = f2_mul(y, s);
+    F2 t_lo = f2_fma(y, s, f2_mul(t_hi, neg1));
+    t_lo = f2_fma(y, l, t_lo);
+    float th0, th1;
+    f2_unpack(t_hi, th0, th1);
+    const F2 p = f2_pack(ex2_approx(th0), ex2_approx(th1));
+    const F2 r = f2_fma(p, f2_mul(t_lo, f2_splat(POW_LN2)), p);
+    f2_unpack(r, r0, r1);
+    // positive normal x (biased exponent 1..254, sign clear) and a moderate, non-NaN y·log2 x
+    if (!(b0 - 0x00800000u < 0x7f000000u && fabsf(th0) < 125.0f)) r0 = powf_library(x0, y0);
+    if (!(b1 - 0x00800000u < 0x7f000000u && fabsf(th1) < 125.0f)) r1 = powf_library(x1, y1);
+}
+
+// pow(s, a) for a constant positive base: log2 s is computed once on the host in double precision and handed over as
+// hi + lo; per element that leaves the product, the hardware 2^t and one correction.
+struct RPowConstFn {
+    float s, l_hi, l_lo;
+    static constexpr bool has_pair = true;
+    __device__ __forceinline__ void pair(float a0, float a1, float &c0, float &c1) const {
+        const F2 y = f2_pack(a0, a1), lh = f2_splat(l_hi);
+        const F2 t_hi = f2_mul(y, lh);
+        F2 t_lo = f2_fma(y, lh, f2_mul(t_hi, f2_splat(-1.0f)));
+        t_lo = f2_fma(y, f2_splat(l_lo), t_lo);
+        float th0, th1;
+        f2_unpack(t_hi, th0, th1);
+        const F2 p = f2_pack(ex2_approx(th0), ex2_approx(th1));
+        const F2 r = f2_fma(p, f2_mul(t_lo, f2_splat(POW_LN2)), p);
+        f2_unpack(r, c0, c1);
+        if (!(fabsf(th0) < 125.0f)) c0 = powf_library(s, a0);
+        if (!(fabsf(th1) < 125.0f)) c1 = powf_library(s, a1);
+    }
+    __device__ __forceinline__ float operator()(float a) const {
+        float c, unused;
+        pair(a, a, c, unused);
+        return c;
+    }
+};
+
 template <int OP, typename T> struct BinaryFn {
     __device__ __forceinline__ T operator()(T a, T b) const {
         using C = compute_t<T>;
@@ -57,9 +158,21 @@ template <int OP, typename T> struct BinaryFn {
         } else {
             static_assert(OP == DX_POW, "binary op");
             if constexpr (std::is_same<C, double>::value) r = pow(x, y);  // std::pow, :441
-            else r = powf(x, y);
+            else {
+                float unused;
+                pow_f32_x2(x, x, y, y, r, unused);  // the arithmetic of the paired path: the same bits wherever an element sits
+            }
         }
         return from_compute<T>(r);
+    }
+    // Two elements per call on the packed instructions (the streaming kernel uses it when present).
+    static constexpr bool has_pair = OP == DX_POW && std::is_same<T, float>::value;
+    __device__ __forceinline__ void pair(T a0, T a1, T b0, T b1, T &c0, T &c1) const {
+        if constexpr (has_pair) pow_f32_x2(a0, a1, b0, b1, c0, c1);
+        else {
+            c0 = (*this)(a0, b0);
+            c1 = (*this)(a1, b1);
+        }
     }
 };
 
@@ -79,6 +192,15 @@ template <int OP, typename T> struct ScalarFn {
         else {
             static_assert(OP == DX_RPOWS, "scalar op");
             return BinaryFn<DX_POW, T>()(s, a);  // :482
+        }
+    }
+    static constexpr bool has_pair = (OP == DX_POWS || OP == DX_RPOWS) && std::is_same<T, float>::value;
+    __device__ __forceinline__ void pair(T a0, T a1, T &c0, T &c1) const {
+        if constexpr (has_pair && OP == DX_POWS) pow_f32_x2(a0, a1, s, s, c0, c1);
+        else if constexpr (has_pair) pow_f32_x2(s, s, a0, a1, c0, c1);
+        else {
+            c0 = (*this)(a0);
+            c1 = (*this)(a1);
         }
     }
 };
@@ -140,16 +262,6 @@ template <int WANT_COS, bool CHECK> __device__ __forceinline__ float trig_of_16b
     const float v = (n & 1) ? c : s;
     return (n & 2) ? -v : v;
 }
-
-// Two fp32 values in one 64-bit register and the packed fp32 instructions of sm_100 (one instruction, two
-// results): the routines below are bound by how many instructions a warp can issue, not by the FMA pipe.
-struct F2 { unsigned long long v; };
-__device__ __forceinline__ F2 f2_pack(float lo, float hi) { F2 r; asm("mov.b64 %0, {%1, %2};" : "=l"(r.v) : "f"(lo), "f"(hi)); return r; }
-__device__ __forceinline__ void f2_unpack(F2 a, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(a.v)); }
-__device__ __forceinline__ F2 f2_splat(float c) { return f2_pack(c, c); }
-__device__ __forceinline__ F2 f2_fma(F2 a, F2 b, F2 c) { F2 r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r.v) : "l"(a.v), "l"(b.v), "l"(c.v)); return r; }
-__device__ __forceinline__ F2 f2_mul(F2 a, F2 b) { F2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
-__device__ __forceinline__ F2 f2_add(F2 a, F2 b) { F2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
 
 // trig_of_16bit for two arguments at once: the same operations in the same order (same bits), the floating-point
 // ones as packed instructions.

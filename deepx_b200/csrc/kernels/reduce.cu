@@ -330,6 +330,7 @@ struct PeerTail {
     Peers peers;
     int rank;
     long long wait_cycles;
+    int combine_now;  // 0: the kernel ends after publishing; the combine runs later on the stream (dx_comm_allreduce_finish)
 };
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) rows_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, uint32_t nout, uint32_t split,
@@ -345,7 +346,8 @@ __global__ void __launch_bounds__(RB) rows_finish_peer_kernel(const acc_t<T> *__
         if (lane == 0) out[o] = narrow<T>(r);
     }
     __syncthreads();  // this CTA's own stores to `out` are visible to all its threads
-    exchange_chunk<OP, T>(tail.peers, tail.rank, 0, out, nout, tail.wait_cycles);
+    exchange_publish<T>(tail.peers, tail.rank, 0, out, nout, narrow<T>(identity<OP, T>()));
+    if (tail.combine_now) exchange_combine<OP, T>(tail.peers, tail.rank, 0, out, nout, tail.wait_cycles);
 }
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) cols_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, int64_t nout, uint32_t split,
@@ -358,7 +360,8 @@ __global__ void __launch_bounds__(RB) cols_finish_peer_kernel(const acc_t<T> *__
         out[o] = narrow<T>(r);
     }
     __syncthreads();
-    exchange_chunk<OP, T>(tail.peers, tail.rank, 0, out, nout, tail.wait_cycles);
+    exchange_publish<T>(tail.peers, tail.rank, 0, out, nout, narrow<T>(identity<OP, T>()));
+    if (tail.combine_now) exchange_combine<OP, T>(tail.peers, tail.rank, 0, out, nout, tail.wait_cycles);
 }
 
 template <typename T> __global__ void fill_kernel(T *out, int64_t n, T v) {
@@ -691,25 +694,29 @@ extern "C" int dx_reduce(int op, int dtype, const void *a, const int64_t *shape,
 }
 
 // Local reduction followed by the combine over the ranks of `comm`, result on every rank.  When the
-// local reduction ends in a one-CTA finish step that CTA also does the exchange (one launch less,
-// and the collective is part of the reduce kernel); otherwise the exchange kernel follows on the
-// same stream.  The combined output must fit a mailbox slot (dx_comm_max_bytes).
-extern "C" int dx_reduce_allreduce(dx_comm *comm, int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
-                                   int ndims, void *out, void *workspace, size_t workspace_bytes, void *stream) {
+// local reduction ends in a one-CTA finish step that CTA also publishes this rank's result to the peers
+// (one launch less, and the collective is part of the reduce kernel); otherwise a publish kernel follows on
+// the same stream.  `combine_now` = 0 stops there: the wait for the peers and the combine are left to
+// dx_comm_allreduce_finish (or to the next call on the communicator), so that whatever the stream runs in
+// between hides the skew between the ranks.  The combined output must fit a mailbox slot (dx_comm_max_bytes).
+static int reduce_allreduce(dx_comm *comm, int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims, int ndims,
+                            void *out, void *workspace, size_t workspace_bytes, void *stream, int combine_now) {
     cudaStream_t st = as_stream(stream);
     if (dx_dtype_size(dtype) == 0 || dtype == DX_BOOL)
         return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
     PeerTail tail;
     if (!comm_device_view(comm, &tail.peers, &tail.rank, &tail.wait_cycles))
         return fail(DX_E_ARG, "reduce+allreduce: the communicator is not connected (or emulates its ranks)");
+    tail.combine_now = combine_now;
     Plan pl;
     if (int e = make_plan(dtype, shape, ndim, dims, ndims, sm_count(), residency(op, dtype), &pl)) return e;
     if (pl.nout > 0 && !out) return fail(DX_E_ARG, "reduce: null output");
     if (pl.nin > 0 && !a) return fail(DX_E_ARG, "reduce: null input");
     if (a == out && pl.nin > 0 && pl.kind != PLAN_COPY) return fail(DX_E_ALIAS, "reduce: output aliases input");
     if (size_t(pl.nout) * dx_dtype_size(dtype) > dx_comm_max_bytes())
-        return fail(DX_E_WORKSPACE, "reduce+allreduce: %lld output bytes exceed the mailbox slot; reduce locally and use a library all-reduce",
+        return fail(DX_E_WORKSPACE, "reduce+allreduce: %lld output bytes exceed the mailbox slot; reduce locally and use dx_comm_allreduce",
                     (long long)(pl.nout * dx_dtype_size(dtype)));
+    if (int e = comm_flush_pending(comm, st)) return e;  // an earlier exchange still waiting for its combine goes first
     bool exchanged = false;
     int rc;
     switch (dtype) {
@@ -723,8 +730,22 @@ extern "C" int dx_reduce_allreduce(dx_comm *comm, int op, int dtype, const void 
         case DX_I8: rc = run_op<int8_t>(op, pl, a, out, workspace, workspace_bytes, st, &tail, &exchanged); break;
         default: return fail(DX_E_DTYPE, "reduce: unsupported dtype code %d", dtype);
     }
-    if (rc != DX_OK || exchanged || pl.nout == 0) return rc;
-    return dx_comm_allreduce(comm, op, dtype, out, pl.nout, stream);
+    if (rc != DX_OK || pl.nout == 0) return rc;
+    if (exchanged) {
+        if (!combine_now) comm_set_pending(comm, op, dtype, out, pl.nout);  // published by the finish kernel
+        return DX_OK;
+    }
+    if (combine_now) return dx_comm_allreduce(comm, op, dtype, out, pl.nout, stream);
+    return dx_comm_allreduce_begin(comm, op, dtype, out, pl.nout, stream);
+}
+
+extern "C" int dx_reduce_allreduce(dx_comm *comm, int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
+                                   int ndims, void *out, void *workspace, size_t workspace_bytes, void *stream) {
+    return reduce_allreduce(comm, op, dtype, a, shape, ndim, dims, ndims, out, workspace, workspace_bytes, stream, 1);
+}
+extern "C" int dx_reduce_allreduce_begin(dx_comm *comm, int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims,
+                                         int ndims, void *out, void *workspace, size_t workspace_bytes, void *stream) {
+    return reduce_allreduce(comm, op, dtype, a, shape, ndim, dims, ndims, out, workspace, workspace_bytes, stream, 0);
 }
 
 // ---- reduce without any device allocation ---------------------------------------------------------

@@ -29,7 +29,11 @@ SIGNATURES = {
     "dx_exec_bind_tensor": (_i, [_vp, _cp, _i, C.POINTER(C.c_int64), _i, _vp]),
     "dx_exec_tensor_info": (_i, [_vp, _cp, C.POINTER(C.c_int), C.POINTER(C.c_int64), _i]),
     "dx_exec_tensor_ptr": (_vp, [_vp, _cp]),
+    "dx_exec_set_shard": (_i, [_vp, _i, _i, _sz, _vp]),
+    "dx_exec_tensor_shard": (_i, [_vp, _cp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "dx_ir_shard_plan": (_i, [_cp, _i, _sz, C.c_char_p, _sz]),
     "dx_exec_upload": (_i, [_vp, _cp, _vp, _sz]),
+    "dx_exec_upload_async": (_i, [_vp, _cp, _vp, _sz]),
     "dx_exec_download": (_i, [_vp, _cp, _vp, _sz]),
     "dx_exec_sync": (_i, [_vp]),
     "dx_exec_stream": (_vp, [_vp]),
@@ -100,6 +104,16 @@ def check_print_format(fmt: str, dtype_code: int) -> str:
     if rc != 0:
         raise ValueError(lib().dx_exec_last_error().decode())
     return buf.value.decode()
+
+
+def shard_plan(program: str, world: int, min_bytes: int = 1 << 20) -> list[str]:
+    """What a rank of a `world`-GPU executor does with each line of `program` (no GPU needed): see
+    ``dx_ir_shard_plan`` in include/dx_executor.h."""
+    buf = C.create_string_buffer(max(1 << 16, 64 * (program.count("\n") + 2)))
+    n = lib().dx_ir_shard_plan(program.encode(), world, min_bytes, buf, len(buf))
+    if n < 0:
+        raise ValueError("shard_plan: " + lib().dx_exec_last_error().decode())
+    return buf.value.decode().split("\n") if n else []
 
 
 def plan_fusion(program: str, existing: str = "") -> tuple[int, list[str]]:
@@ -236,9 +250,31 @@ class Executor:
         if lib().dx_exec_bind_tensor(self._h, name.encode(), dtype_code, shp, len(shape), device_ptr) != 0:
             raise RuntimeError(lib().dx_exec_last_error().decode())
 
+    def set_shard(self, rank: int, world: int, comm_handle, min_bytes: int = 1 << 20) -> None:
+        """Makes this executor rank `rank` of `world` (one process per GPU, the same IR lines to every rank).
+        `comm_handle` is a connected dx_comm (e.g. ``PeerComm(...)._h``) that must outlive the executor."""
+        if lib().dx_exec_set_shard(self._h, rank, world, min_bytes, comm_handle) != 0:
+            raise RuntimeError(lib().dx_exec_last_error().decode())
+
+    def shard(self, name: str) -> tuple[bool, int, int, int]:
+        """(partitioned, first row, rows held here, global rows) of a tensor."""
+        r0, n, g = C.c_int64(), C.c_int64(), C.c_int64()
+        rc = lib().dx_exec_tensor_shard(self._h, name.encode(), C.byref(r0), C.byref(n), C.byref(g))
+        if rc < 0:
+            raise KeyError(name)
+        return bool(rc), int(r0.value), int(n.value), int(g.value)
+
     def upload(self, name: str, array: np.ndarray) -> None:
         a = np.ascontiguousarray(array)
         rc = lib().dx_exec_upload(self._h, name.encode(), a.ctypes.data, a.nbytes)
+        if rc != 0:
+            raise RuntimeError(lib().dx_exec_last_error().decode())
+
+    def upload_async(self, name: str, array: np.ndarray) -> None:
+        """Starts the copy and returns; `array` (contiguous, ideally page-locked) must stay alive until sync()."""
+        if not array.flags["C_CONTIGUOUS"]:
+            raise ValueError("upload_async needs a contiguous array (it is read after the call returns)")
+        rc = lib().dx_exec_upload_async(self._h, name.encode(), array.ctypes.data, array.nbytes)
         if rc != 0:
             raise RuntimeError(lib().dx_exec_last_error().decode())
 

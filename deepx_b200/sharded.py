@@ -8,6 +8,11 @@ block first and then combines the per-rank partials with ONE all-reduce (sum / p
 max / min) — 4 bytes for a global sum, one row for an axis-0 reduce.  Partials that fit a
 mailbox slot (64 KiB) are combined by the GPUs themselves over NVLink peer memory
 (:mod:`deepx_b200.comm`, one kernel per rank, no library collective); larger ones go to NCCL.
+With ``defer=True`` the peer exchange is split: the reduction ends by publishing this rank's partial,
+and the wait for the peers plus the combine run as a kernel of their own when ``flush()`` is called (or
+just before the next op given to this object that touches the result, or the next cross-rank
+reduction) — the ops issued in between hide the skew between the ranks.  Code that reads the output
+tensor by other means must call ``flush()`` first, which is why it is off unless asked for.
 Ops that do not shard this way (matmul, general transposes) stay single-GPU.
 
 The reference has no multi-GPU code at all (no cudaSetDevice, streams or NCCL anywhere
@@ -72,7 +77,7 @@ class ShardedOps:
     reduced the output holds the global result on every rank after the call.
     """
 
-    def __init__(self, group=None, peer_combine: bool | None = None):
+    def __init__(self, group=None, peer_combine: bool | None = None, defer: bool | None = None):
         """``peer_combine``: combine small partials with the peer-memory kernel instead of NCCL
         (default: on when there is more than one rank, off with ``DX_PEER_COMBINE=0``).  Building
         it is collective: every rank of the group constructs its ShardedOps at the same point."""
@@ -84,6 +89,8 @@ class ShardedOps:
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         if peer_combine is None:
             peer_combine = os.environ.get("DX_PEER_COMBINE", "1") != "0"
+        self.defer = (os.environ.get("DX_PEER_DEFER", "0") == "1") if defer is None else bool(defer)
+        self._pending = None
         self.peer = None
         if peer_combine and self.world > 1 and torch.cuda.is_available():
             from .comm import PeerComm
@@ -96,17 +103,47 @@ class ShardedOps:
                     print(f"deepx_b200.sharded: peer-memory combine unavailable ({e}); using the group's all-reduce", file=sys.stderr)
                 self.peer = None
 
+    def flush(self) -> None:
+        """Completes a deferred exchange: after it the last cross-rank reduction's output is final."""
+        if self.peer is not None and self._pending is not None:
+            self._pending = None
+            self.peer.finish()
+
+    def _touches_pending(self, tensors) -> bool:
+        if self._pending is None:
+            return False
+        lo, hi = self._pending
+        for t in tensors:
+            for u in (t if isinstance(t, (list, tuple)) else (t,)):
+                if isinstance(u, torch.Tensor) and u.is_cuda and u.numel() and u.data_ptr() < hi and u.data_ptr() + u.numel() * u.element_size() > lo:
+                    return True
+        return False
+
     def __getattr__(self, name):
-        return getattr(self.tf, name)
+        fn = getattr(self.tf, name)
+        if not callable(fn):
+            return fn
+
+        def call(*args, **kwargs):
+            # an op that reads or writes the tensor whose exchange is still open waits for it first
+            if self._touches_pending(args) or self._touches_pending(kwargs.values()):
+                self.flush()
+            return fn(*args, **kwargs)
+        return call
 
     def _reduce(self, op: str, A: torch.Tensor, dims, keepdims: bool, B: torch.Tensor) -> None:
         cd = self.tf.checked_dims(A.shape, dims)
         crosses = shards_axis0(cd, A.dim())
+        if self._touches_pending((A, B)):
+            self.flush()
         if crosses and self.peer is not None and self.world > 1 and self.peer.fits(B):
-            self.peer.reduce_allreduce(op, A, dims, keepdims, B)  # reduce and exchange, fused where the plan allows
+            # reduce, publish (fused into the finish kernel where the plan allows); the combine is deferred
+            self.peer.reduce_allreduce(op, A, dims, keepdims, B, defer=self.defer)
+            self._pending = (B.data_ptr(), B.data_ptr() + B.numel() * B.element_size()) if self.defer and self.peer.pending() else None
             return
         getattr(self.tf, op)(A, dims, keepdims, B)
         if crosses:
+            self.flush()
             combine_partials(B, op, self.group, self.peer)
 
     def sum(self, A, dims, keepdims, B): self._reduce("sum", A, dims, keepdims, B)  # noqa: A003

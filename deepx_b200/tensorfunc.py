@@ -239,9 +239,10 @@ def _get_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     return ws
 
 
-def _reduce(op: int, A: torch.Tensor, dims: Sequence[int], keepdims: bool, B: torch.Tensor, comm_handle=None) -> None:
+def _reduce(op: int, A: torch.Tensor, dims: Sequence[int], keepdims: bool, B: torch.Tensor, comm_handle=None, defer: bool = False) -> None:
     """`comm_handle` (a dx_comm): the local reduction is followed by the combine over its ranks, fused
-    into the reduction's finish kernel where that is a single CTA."""
+    into the reduction's finish kernel where that is a single CTA.  `defer`: stop after this rank's result
+    has been published to the peers; dx_comm_allreduce_finish completes the exchange later on the stream."""
     _dev(A, B)
     _same_dtype(A, B)
     cd = checked_dims(A.shape, dims)
@@ -258,9 +259,9 @@ def _reduce(op: int, A: torch.Tensor, dims: Sequence[int], keepdims: bool, B: to
         need = N.lib.dx_reduce_workspace_bytes(op, code, shape, A.dim(), cdims, len(cd))
         ws = _get_workspace(A.device, need) if need else None
         if comm_handle is not None:
-            N.check(N.lib.dx_reduce_allreduce(comm_handle, op, code, A.data_ptr(), shape, A.dim(), cdims, len(cd), B.data_ptr(),
-                                              ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
-                                              _stream(A)))
+            fn = N.lib.dx_reduce_allreduce_begin if defer else N.lib.dx_reduce_allreduce
+            N.check(fn(comm_handle, op, code, A.data_ptr(), shape, A.dim(), cdims, len(cd), B.data_ptr(),
+                     ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0, _stream(A)))
             return
         N.check(N.lib.dx_reduce(op, code, A.data_ptr(), shape, A.dim(), cdims, len(cd), B.data_ptr(),
                                 ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,

@@ -77,14 +77,42 @@ void dx_program_free(dx_program *p);
  * executor's device, while the name is registered.  Fails if the name exists. */
 int dx_exec_bind_tensor(dx_exec *e, const char *name, int dtype, const int64_t *shape, int ndim, void *device_ptr);
 
-/* Tensor metadata: dtype is a dx_dtype code; shape receives up to cap extents; returns the rank,
- * or -1 if there is no such tensor. */
+/* ---- one executor per GPU, several GPUs (no reference counterpart: the reference has one Mem and one device,
+ * executor/op-cuda/src/client/main.cpp:22-105, executor/heapmem-cuda/README.md:19,29) ----
+ * Makes this executor rank `rank` of `world`: one process per GPU, every rank is given the SAME IR lines, `comm`
+ * is a connected dx_comm (dx_kernels.h) for this rank and must outlive the executor.  From then on newtensor
+ * partitions a tensor by rows (contiguous blocks of its leading axis, dx_shard_rows) when it holds at least
+ * `min_bytes` and has at least `world` rows; smaller tensors are replicated on every rank.  Ops that work row
+ * by row run on the local rows without communication; a reduction that removes axis 0 combines the ranks'
+ * partials over NVLink peer memory (its wait for the peers is left until the result is next needed, so the ops
+ * in between hide the skew between ranks); ops with no row-wise form refuse partitioned operands with an
+ * error reply.  save writes, and load / loadtensordata read, the very files a single GPU would (each rank its
+ * rows).  Upload, download, tensor_info and tensor_ptr see the LOCAL rows of a partitioned tensor. */
+typedef struct dx_comm dx_comm;
+int dx_exec_set_shard(dx_exec *e, int rank, int world, size_t min_bytes, dx_comm *comm);
+/* Where a tensor's rows sit: first row and number of rows held by this rank, and the global row count.
+ * Returns 1 if the tensor is partitioned, 0 if it is whole (replicated), -1 if there is no such tensor. */
+int dx_exec_tensor_shard(dx_exec *e, const char *name, int64_t *row0, int64_t *rows, int64_t *global_rows);
+/* The partition decisions alone, without a GPU: for every line of `program` what a rank of `world` would do with
+ * it — "newtensor <name>: partitioned <rows> rows" / "whole", "rows", "rows+allgather", "whole",
+ * "allreduce(deferred)", "allreduce(rounds)", "allreduce(rounds)+keep-own-rows", "rows-if-aligned" (changeshape,
+ * matmul and fused ops: by rows where the operands' rows line up, refused otherwise) or "refuse: <why>" — one per
+ * line, '\n'-separated.  Returns the number of lines, -1 on a parse error (dx_exec_last_error). */
+int dx_ir_shard_plan(const char *program, int world, size_t min_bytes, char *out, size_t cap);
+
+/* Tensor metadata: dtype is a dx_dtype code; shape receives up to cap extents (the local rows of a
+ * partitioned tensor); returns the rank, or -1 if there is no such tensor. */
 int dx_exec_tensor_info(dx_exec *e, const char *name, int *dtype, int64_t *shape, int cap);
 /* Device pointer of a tensor's storage (NULL if absent). */
 void *dx_exec_tensor_ptr(dx_exec *e, const char *name);
 /* Copies host bytes into / out of an existing tensor (exactly its size in bytes). Synchronous. */
 int dx_exec_upload(dx_exec *e, const char *name, const void *host, size_t bytes);
 int dx_exec_download(dx_exec *e, const char *name, void *host, size_t bytes);
+/* Upload without waiting: the copy runs on a stream of its own, ordered behind everything submitted so far; the
+ * first op (or download) that names the tensor afterwards waits for it on the device, other ops do not.  `host`
+ * must stay valid, and should be page-locked for the copy to overlap with compute, until dx_exec_sync or a
+ * download of a result that depends on it. */
+int dx_exec_upload_async(dx_exec *e, const char *name, const void *host, size_t bytes);
 /* Waits for everything submitted so far. */
 int dx_exec_sync(dx_exec *e);
 /* The executor's CUDA stream (cudaStream_t as void*). */

@@ -192,8 +192,8 @@ int dx_reduce_noalloc(int op, int dtype, const void *a, const int64_t *shape, in
  * One process per GPU.  A reduction over the axis a tensor is sharded along leaves one partial
  * per rank; dx_comm_allreduce combines them IN PLACE with one kernel per rank that stores its
  * partial into every peer's mailbox over NVLink peer memory and combines the W partials in rank
- * order (identical bits on every rank).  Buffers up to dx_comm_max_bytes(); larger ones belong to
- * a library all-reduce.  Set-up: every rank calls dx_comm_create, exchanges the 64-byte handles
+ * order (identical bits on every rank).  A buffer larger than dx_comm_max_bytes() (one mailbox slot)
+ * goes in several rounds of the same kernel.  Set-up: every rank calls dx_comm_create, exchanges the 64-byte handles
  * of dx_comm_handle by any host channel, and gives all of them (world x 64 bytes, rank order) to
  * dx_comm_connect.  All ranks must issue the same sequence of dx_comm_allreduce calls.
  * Waits on a peer are bounded (2 s unless dx_comm_set_timeout_ms): when one expires the kernel
@@ -208,6 +208,26 @@ int dx_comm_set_timeout_ms(dx_comm *c, int ms);
 int dx_comm_allreduce(dx_comm *c, int op, int dtype, void *buf, int64_t n, void *stream);
 int dx_comm_status(dx_comm *c, void *stream);
 void dx_comm_destroy(dx_comm *c);
+int dx_comm_rank(dx_comm *c);
+int dx_comm_world(dx_comm *c);
+/* The all-reduce in two halves.  _begin stores this rank's buffer (at most dx_comm_max_bytes()) into the
+ * peers' mailboxes and raises its flags, without waiting for anybody; _finish waits (bounded) for the
+ * peers' flags and combines in place.  Kernels launched on the stream between the two run while the
+ * slower ranks catch up, so the per-step skew between ranks is hidden instead of waited out.  One
+ * exchange can be outstanding per communicator: a second _begin, dx_comm_allreduce,
+ * dx_comm_allgather_rows or dx_reduce_allreduce* first finishes the one before (on ITS stream argument).
+ * The buffer must not be read or written between _begin and _finish.  dx_comm_pending returns 1 and the
+ * buffer while an exchange is outstanding. */
+int dx_comm_allreduce_begin(dx_comm *c, int op, int dtype, void *buf, int64_t n, void *stream);
+int dx_comm_allreduce_finish(dx_comm *c, void *stream);
+int dx_comm_pending(dx_comm *c, void **buf);
+/* Contiguous split of `global_rows` leading-axis indices over `world` ranks (the first
+ * global_rows % world ranks get one row more): where rank's block starts and how many rows it has. */
+void dx_shard_rows(int64_t global_rows, int rank, int world, int64_t *row0, int64_t *rows);
+/* All-gather of row blocks, in place: every rank holds the whole [global_rows x row_bytes] buffer and has
+ * filled its own block (dx_shard_rows); afterwards every rank holds every block.  Peer stores and the
+ * same bounded flag waits as the all-reduce; blocks larger than a mailbox slot go in rounds. */
+int dx_comm_allgather_rows(dx_comm *c, void *buf, int64_t global_rows, int64_t row_bytes, void *stream);
 /* dx_reduce on this rank's shard followed by the combine over the ranks, result on every rank.
  * Where the local reduction ends in a one-CTA finish step (few outputs — the global sum of a sharded
  * tensor is one) that CTA also performs the exchange, so a single launch is the tail of the
@@ -215,12 +235,20 @@ void dx_comm_destroy(dx_comm *c);
  * output must fit dx_comm_max_bytes(); workspace as for dx_reduce. */
 int dx_reduce_allreduce(dx_comm *c, int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims, int ndims,
                         void *out, void *workspace, size_t workspace_bytes, void *stream);
+/* The same, stopping after this rank's result has been published to the peers (by the reduction's own
+ * finish kernel where it has one): dx_comm_allreduce_finish completes it. */
+int dx_reduce_allreduce_begin(dx_comm *c, int op, int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims, int ndims,
+                              void *out, void *workspace, size_t workspace_bytes, void *stream);
 /* The same protocol with every rank on ONE GPU (all mailboxes local, all ranks' CTAs in one
  * launch, which is the only safe way to run kernels that wait on each other on one device):
  * bufs[r] is rank r's buffer.  Ranks >= active_ranks are left out, so the others' waits expire
  * and dx_comm_status reports it — the failure path without a misbehaving process. */
 dx_comm *dx_comm_emulate(int world, int device);
 int dx_comm_emulated_allreduce(dx_comm *c, int op, int dtype, void *const *bufs, int active_ranks, int64_t n, void *stream);
+/* The two halves of the exchange as separate launches, and the row-block all-gather, on emulated ranks. */
+int dx_comm_emulated_publish(dx_comm *c, int op, int dtype, void *const *bufs, int active_ranks, int64_t n, void *stream);
+int dx_comm_emulated_combine(dx_comm *c, int op, int dtype, void *const *bufs, int active_ranks, int64_t n, void *stream);
+int dx_comm_emulated_allgather_rows(dx_comm *c, void *const *bufs, int64_t global_rows, int64_t row_bytes, void *stream);
 
 /* ---- fused row chains --------------------------------------------------------
  * The reference has no single function for these: its front end builds RMSNorm

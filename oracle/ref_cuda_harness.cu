@@ -264,11 +264,13 @@ int refcu_switch(int dtype, const void *const *srcs, int k, int cases_dtype, con
 int refcu_cast(int src_dtype, const void *a, int dst_dtype, void *c, int n) {
     return guarded([&] { BY_DTYPE(src_dtype, cast_from, a, dst_dtype, c, n) });
 }
-// float32 / float64 / int32 only (see the header comment)
+// float32 / float64 / int32 only (see the header comment).  Refused: every axis reduced without keepdims — the
+// kernel then fills no output index and reads an uninitialised one (reduce_miaobyte.cu:33-46).
 int refcu_sum(int dtype, const void *a, const int64_t *shape, int ndim, const int32_t *dims, int ndims, int keepdims, void *out) {
     return guarded([&] {
         const Shape in(as_int(shape, ndim));
         const std::vector<int> d(dims, dims + ndims);
+        if (!keepdims && (ndims == 0 || ndims == ndim)) unsupported("full reduction without keepdims (undefined in the reference's kernel)");
         if (dtype == F32) sum_t<float>(a, in, d, keepdims != 0, out);
         else if (dtype == F64) sum_t<double>(a, in, d, keepdims != 0, out);
         else if (dtype == I32) sum_t<int32_t>(a, in, d, keepdims != 0, out);

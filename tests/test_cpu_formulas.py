@@ -13,6 +13,8 @@
                                                                      (trig_of_16bit, ew_ops.cuh)
 * log of a 16-bit float in fp32 (exponent split on the bits, Cephes polynomial): within 0.75 fp32 ulp
                                                                      (log_of_16bit_x2, ew_ops.cuh)
+* float32 pow as 2^(y·log2 x) with log2 x and the product carried as sums of two floats: within 4e-6
+  relative of the exact power wherever the fast path applies              (pow_f32_x2, ew_ops.cuh)
 """
 import numpy as np
 
@@ -161,3 +163,76 @@ def test_log_of_16bit_every_positive_argument():
         exact = np.log(x.astype(np.float64))
         ulp = np.spacing(np.abs(exact).astype(np.float32)).astype(np.float64)
         assert (np.abs(got.astype(np.float64) - exact) <= 0.75 * np.maximum(ulp, 1e-45)).all()
+
+
+# ---- pow_f32_x2 (ew_ops.cuh) in numpy: the same operations in the same order, FMAs through float64 ----------
+_POW_Q = np.array([-7.213471532e-01, 4.808981419e-01, -3.607088029e-01, 2.885792851e-01, -2.393930554e-01, 2.042880207e-01,
+                   -1.923508048e-01, 1.883963346e-01, -1.097617820e-01], dtype=np.float32)
+_INVLN2_HI, _INVLN2_LO, _LN2 = np.float32(1.4426950216293335), np.float32(1.925963033500011e-08), np.float32(0.693147182)
+
+
+def _fma(a, b, c):
+    return (np.asarray(a, np.float32).astype(np.float64) * np.asarray(b, np.float32).astype(np.float64)
+            + np.asarray(c, np.float32).astype(np.float64)).astype(np.float32)
+
+
+def _pow_fast(x, y):
+    """(result, fast) — `fast` marks the elements the kernel keeps; the others go to the library powf."""
+    F = np.float32
+    x, y = x.astype(F), y.astype(F)
+    b = x.view(np.uint32)
+    eb = (b - np.uint32(0x3f3504f3)) & np.uint32(0xff800000)
+    f = (b - eb).view(F) - F(1)
+    e = (eb.view(np.int32) >> 23).astype(F)
+    q = np.full_like(f, _POW_Q[8])
+    for i in range(7, -1, -1):
+        q = _fma(q, f, np.full_like(f, _POW_Q[i]))
+    ff = f * f
+    p_hi = f * _INVLN2_HI
+    p_lo = _fma(f, np.full_like(f, _INVLN2_HI), -p_hi)
+    p_lo = _fma(f, np.full_like(f, _INVLN2_LO), p_lo)
+    u = _fma(ff, q, p_lo)
+    s1 = p_hi + u
+    c1 = (p_hi - s1) + u
+    s = e + s1
+    c2 = (e - s) + s1
+    l = c1 + c2
+    with np.errstate(all="ignore"):
+        t_hi = y * s
+        t_lo = _fma(y, l, _fma(y, s, -t_hi))
+        fast = ((b - np.uint32(0x00800000)) < np.uint32(0x7f000000)) & (np.abs(t_hi) < 125)
+        p = np.exp2(np.where(fast, t_hi, 0).astype(np.float64)).astype(F)  # the hardware 2^t: at most 2^-22 off, allowed for below
+        r = _fma(p, t_lo * _LN2, p)
+    return r, fast
+
+
+def test_fast_pow_is_within_tolerance_of_the_exact_power():
+    rng = np.random.default_rng(0)
+    n = 1_000_000
+    cases = {
+        "ordinary": (rng.uniform(0.1, 4, n), rng.uniform(-3, 3, n)),
+        "wide x": (np.exp(rng.uniform(-80, 80, n)), rng.uniform(-1.5, 1.5, n)),
+        "x near 1, huge y": (1 + rng.uniform(-1e-3, 1e-3, n), rng.uniform(-1e5, 1e5, n)),
+        "every mantissa region, large y": (1 + rng.uniform(-0.3, 0.42, n), rng.uniform(-250, 250, n)),
+        "integer y": (rng.uniform(0.5, 30, n), rng.integers(-12, 13, n).astype(np.float64)),
+    }
+    for name, (x, y) in cases.items():
+        x, y = x.astype(np.float32), y.astype(np.float32)
+        r, fast = _pow_fast(x, y)
+        ref = np.power(x.astype(np.float64), y.astype(np.float64))
+        rel = np.abs(r[fast].astype(np.float64) - ref[fast]) / ref[fast]
+        assert fast.mean() > 0.9, name
+        assert rel.max() + 2.0 ** -22 < 4e-6, (name, rel.max())   # 2^-22: the hardware exponential's own error
+
+
+def test_fast_pow_hands_special_arguments_to_the_library():
+    x = np.array([0.0, -2.0, np.inf, np.nan, 1e-40, 2.0, 2.0, 2.0, 1.0, 3.0, 1.5], dtype=np.float32)
+    y = np.array([2.0, 3.0, 1.0, 1.0, 2.0, np.inf, np.nan, 200.0, np.nan, -90.0, 0.0], dtype=np.float32)
+    r, fast = _pow_fast(x, y)
+    assert fast.tolist() == [False, False, False, False, False, False, False, False, False, False, True]
+    assert r[-1] == 1.0
+    # exact cases stay exact: x = 1, y = 0, powers of two with integer exponents
+    x = np.array([1.0, 7.3, 2.0, 4.0, 0.5, 8.0], dtype=np.float32)
+    y = np.array([123.0, 0.0, 10.0, 0.5, 3.0, -1.0], dtype=np.float32)
+    r, fast = _pow_fast(x, y)
+    assert fast.all() and r.tolist() == [1.0, 1.0, 1024.0, 2.0, 0.125, 0.125]

@@ -120,3 +120,109 @@ def test_reduce_with_fused_exchange_on_one_rank(dtype):
             N.check(N.lib.dx_comm_status(h, None))
             assert np.array_equal(to_np(plain).view(np.uint8), to_np(fused).view(np.uint8)), (dtype, shape, dims, op)
     N.lib.dx_comm_destroy(h)
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16", "int64", "int8"])
+def test_split_exchange_publish_then_combine(world, dtype):
+    """The exchange as two launches — publish (stores + flags), then other work, then combine (bounded wait +
+    rank-order combine): the form a deferred cross-rank reduction uses.  Same bits as the one-launch form, round
+    after round (the epoch only advances in the combine), with a kernel on the stream in between."""
+    from deepx_b200.comm import EmulatedComm
+    comm = EmulatedComm(world)
+    rng = np.random.default_rng(seed_of("split", world, dtype))
+    es = np.dtype(NP_DTYPES[dtype]).itemsize
+    other = torch.zeros(1 << 20, device="cuda:0")
+    for round_, (op, n) in enumerate([(o, n) for o in ("sum", "reducemax", "reducemin") for n in (1, 4096 // es + 3, 2 * 4096 // es)]):
+        parts = [make(rng, dtype, (n,), -4.0, 4.0) for _ in range(world)]
+        bufs = [to_gpu(p) for p in parts]
+        comm.publish(bufs, op)
+        other.add_(1.0)                       # independent work between the two halves
+        comm.combine(bufs, op)
+        comm.status()
+        want = rank_order_combine(parts, op, dtype)
+        for r in range(world):
+            assert np.array_equal(to_np(bufs[r]).view(np.uint8), want.view(np.uint8)), f"{dtype} {op} n={n} round {round_} rank {r}"
+        # alternate with the one-launch form: both advance the same epochs
+        bufs = [to_gpu(p) for p in parts]
+        comm.allreduce(bufs, op)
+        comm.status()
+        assert np.array_equal(to_np(bufs[world - 1]).view(np.uint8), want.view(np.uint8))
+    comm.close()
+
+
+def test_split_exchange_absent_rank_times_out_in_the_combine():
+    from deepx_b200 import _native as N
+    from deepx_b200.comm import EmulatedComm
+    comm = EmulatedComm(4)
+    comm.set_timeout_ms(50)
+    parts = [np.full(100, r + 1, dtype=np.float32) for r in range(4)]
+    bufs = [to_gpu(p) for p in parts]
+    comm.publish(bufs, "sum", active=3)       # rank 3 never publishes
+    comm.combine(bufs, "sum", active=3)
+    with pytest.raises(N.DxError, match="gave up waiting for rank 3"):
+        comm.status()
+    for r in range(4):
+        assert np.array_equal(to_np(bufs[r]), parts[r])   # nothing combined, local data untouched
+    comm.close()
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("rows,row_elems,dtype", [(8, 5, "float32"), (17, 33, "int8"), (64, 4096, "float32"), (3, 100001, "bfloat16"),
+                                                  (2048, 1, "float32"), (1, 7, "int64")])
+def test_allgather_rows_on_emulated_ranks(world, rows, row_elems, dtype):
+    """Every rank holds the whole tensor with only its own block of rows filled in (the rest poisoned); after the
+    gather every rank holds every block, bit for bit.  Uneven splits (rows % world != 0), ranks without any row,
+    unaligned row sizes and blocks larger than a mailbox slot (several rounds) included."""
+    from deepx_b200.comm import EmulatedComm, shard_rows
+    rng = np.random.default_rng(seed_of("gather", world, rows, row_elems, dtype))
+    full = make(rng, dtype, (rows, row_elems))
+    comm = EmulatedComm(world)
+    bufs = []
+    for r in range(world):
+        r0, n = shard_rows(rows, r, world)
+        mine = np.full_like(full, 99)
+        mine[r0:r0 + n] = full[r0:r0 + n]
+        bufs.append(to_gpu(mine))
+    assert sum(shard_rows(rows, r, world)[1] for r in range(world)) == rows
+    for _ in range(2):   # twice: epochs stay in step although ranks publish different numbers of chunks
+        comm.allgather_rows(bufs)
+        comm.status()
+        for r in range(world):
+            assert np.array_equal(to_np(bufs[r]).view(np.uint8), full.view(np.uint8)), f"rank {r}"
+    # and the all-reduce still works on the same mailboxes afterwards
+    parts = [np.full(10, r + 1, dtype=np.float32) for r in range(world)]
+    ab = [to_gpu(p) for p in parts]
+    comm.allreduce(ab, "sum")
+    comm.status()
+    assert np.array_equal(to_np(ab[0]), np.full(10, world * (world + 1) // 2, dtype=np.float32))
+    comm.close()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "int32"])
+def test_deferred_reduce_on_one_rank(dtype):
+    """dx_reduce_allreduce_begin + dx_comm_allreduce_finish against the own mailbox (a world of one): the output is the
+    plain reduction once finished; a second begin finishes the first by itself; dx_comm_pending tracks it."""
+    import ctypes as C
+    from deepx_b200 import _native as N
+    from deepx_b200 import tensorfunc as TF
+    h = N.lib.dx_comm_create(0, 1, 0)
+    rng = np.random.default_rng(seed_of("defer", dtype))
+    a = make(rng, dtype, (512, 4096), 0.0, 1.0)
+    b = make(rng, dtype, (300, 1000), 0.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    want_a, want_b = torch.empty(1, dtype=A.dtype, device="cuda:0"), torch.empty(1000, dtype=A.dtype, device="cuda:0")
+    TF.sum(A, [0, 1], False, want_a)
+    TF.reducemax(B, [0], False, want_b)
+    out_a, out_b = torch.empty_like(want_a), torch.empty_like(want_b)
+    TF._reduce(N.SUM, A, [0, 1], False, out_a, comm_handle=h, defer=True)        # one-CTA finish: published by the reduce kernel
+    p = C.c_void_p()
+    assert N.lib.dx_comm_pending(h, C.byref(p)) == 1 and p.value == out_a.data_ptr()
+    TF._reduce(N.RMAX, B, [0], False, out_b, comm_handle=h, defer=True)          # finishes the first, begins the second
+    assert N.lib.dx_comm_pending(h, C.byref(p)) == 1 and p.value == out_b.data_ptr()
+    N.check(N.lib.dx_comm_allreduce_finish(h, torch.cuda.current_stream().cuda_stream))
+    assert N.lib.dx_comm_pending(h, None) == 0
+    N.check(N.lib.dx_comm_status(h, None))
+    assert np.array_equal(to_np(out_a).view(np.uint8), to_np(want_a).view(np.uint8))
+    assert np.array_equal(to_np(out_b).view(np.uint8), to_np(want_b).view(np.uint8))
+    N.lib.dx_comm_destroy(h)

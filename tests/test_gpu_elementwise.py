@@ -92,6 +92,66 @@ def test_pow(mods, dtype):
         TF.pow(X, X, torch.empty_like(X))
 
 
+def _pow_grid_check(got, want, what):
+    """pow against the CPU's std::pow: the same class everywhere (NaN, ±inf, ±0), relative 1e-5 on normal results,
+    and on subnormal results the same 1e-5 plus one unit of the subnormal grid (2^-149), which is all that is there."""
+    assert np.array_equal(np.isnan(got), np.isnan(want)), what + ": NaN pattern"
+    ok = ~np.isnan(want)
+    assert np.array_equal(np.isinf(got[ok]), np.isinf(want[ok])), what + ": infinities"
+    inf = np.isinf(want) & ok
+    assert np.array_equal(np.signbit(got[inf]), np.signbit(want[inf])), what + ": sign of infinities"
+    fin = np.isfinite(want)
+    g, w = got[fin].astype(np.float64), want[fin].astype(np.float64)
+    bad = np.abs(g - w) > 1e-5 * np.abs(w) + 2.0 ** -149
+    assert not bad.any(), f"{what}: {int(bad.sum())} of {g.size} outside 1e-5; worst rel {np.max(np.abs(g - w) / np.maximum(np.abs(w), 1e-300))}"
+    assert np.array_equal(np.signbit(got[fin]), np.signbit(want[fin])) or np.array_equal(np.signbit(g[w != 0]), np.signbit(w[w != 0])), what + ": signs"
+
+
+def test_pow_float32_dense_grid(mods):
+    """Every combination of a dense set of bases (subnormals, the whole normal range, values hugging 1, zero,
+    negatives, inf, NaN) and exponents (fractions, integers, huge, ±inf, NaN, ±0) through pow, powscalar and
+    rpowscalar: the fast path and the hand-over to the library routine must both stay within 1e-5."""
+    TF, O = mods
+    rng = np.random.default_rng(77)
+    xs = np.concatenate([
+        np.float32(2.0) ** np.arange(-149, 128, 3, dtype=np.float32),                  # powers of two, subnormals included
+        np.exp(rng.uniform(-87, 88, 700)).astype(np.float32),                           # the normal range
+        (1 + rng.uniform(-0.3, 0.42, 500)).astype(np.float32),                           # every mantissa region
+        (1 + np.float32(2.0) ** -np.arange(1, 24, dtype=np.float32)), (1 - np.float32(2.0) ** -np.arange(1, 25, dtype=np.float32)),
+        np.array([0.0, -0.0, 1.0, -1.0, -2.0, -0.5, -3.7, np.inf, -np.inf, np.nan, 1e-45, 1.1754944e-38, 3.4028235e38], dtype=np.float32),
+    ]).astype(np.float32)
+    ys = np.concatenate([
+        rng.uniform(-4, 4, 300).astype(np.float32), rng.uniform(-200, 200, 300).astype(np.float32),
+        np.arange(-12, 13, dtype=np.float32), np.float32(2.0) ** np.arange(-30, 40, 3, dtype=np.float32),
+        np.array([0.0, -0.0, 0.5, -0.5, 1.0 / 3, 1e5, -1e5, 3e6, 1e30, -1e30, np.inf, -np.inf, np.nan, 1.0, 2.0, 3.0, -1.0], dtype=np.float32),
+    ]).astype(np.float32)
+    X, Y = np.meshgrid(xs, ys, indexing="ij")
+    a, b = np.ascontiguousarray(X.ravel()), np.ascontiguousarray(Y.ravel())
+    A, B = to_gpu(a), to_gpu(b)
+    Cc = torch.empty_like(A)
+    TF.pow(A, B, Cc)
+    with np.errstate(all="ignore"):
+        want = O.pow(a, b)
+    _pow_grid_check(to_np(Cc), want, "pow<float32> grid")
+    # the scalar tail (one element at a time) must give the very bits of the vector body
+    odd = a.size - 3
+    Cs = torch.empty(odd, dtype=torch.float32, device="cuda:0")
+    TF.pow(A[3:], B[3:], Cs)   # starts 12 bytes into the allocation: the unaligned, element-wise kernel
+    assert_bit_exact(to_np(Cs), to_np(Cc)[3:], "pow<float32>: element-wise path vs vector path")
+    XA = to_gpu(xs)
+    Cx = torch.empty_like(XA)
+    for s in (2.5, -1.5, 0.5, 1.0 / 3, 7.0, -12.0, 100.0, 0.0):
+        TF.powscalar(XA, s, Cx)
+        with np.errstate(all="ignore"):
+            _pow_grid_check(to_np(Cx), O.powscalar(xs, s), f"powscalar<float32>({s}) grid")
+    YA = to_gpu(ys)
+    Cy = torch.empty_like(YA)
+    for s in (1.7, 2.0, 0.3, 10.0, 1e-30, 3e38, 1.0, 0.0, -2.0, 1e-45):
+        TF.rpowscalar(s, YA, Cy)
+        with np.errstate(all="ignore"):
+            _pow_grid_check(to_np(Cy), O.rpowscalar(s, ys), f"rpowscalar<float32>({s}) grid")
+
+
 @pytest.mark.parametrize("dtype", ["float64", "float32"])
 @pytest.mark.parametrize("k", [2, 3, 1, -1])
 def test_powscalar_small_integer_exponents(mods, dtype, k):
