@@ -3,7 +3,8 @@
 ``python -m deepx_b200.build`` compiles every ``csrc/kernels/*.cu`` into
 ``deepx_b200/libdeepx_b200.so`` (the C ABI declared in ``include/dx_kernels.h``)
 and every ``csrc/host/*.cpp`` + ``csrc/host/*.cu`` into ``deepx_b200/libdeepx_exec.so``
-and the ``deepx_b200/deepx-op-b200`` executor binary.  nvcc cross-compiles
+and the executables ``deepx_b200/deepx-op-b200`` (the executor) and ``deepx_b200/deepx-heapmem``
+(the heap-tensor service).  nvcc cross-compiles
 without a GPU.  Objects are cached under ``build/`` by source mtime.
 """
 from __future__ import annotations
@@ -29,6 +30,9 @@ COMMON = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC,-Wall,-Wno-unus
 KERNEL_LIB = PKG / "libdeepx_b200.so"
 EXEC_LIB = PKG / "libdeepx_exec.so"
 EXEC_BIN = PKG / "deepx-op-b200"
+HEAP_BIN = PKG / "deepx-heapmem"
+# one executable per csrc/host/*_main.cpp
+MAIN_BINARIES = {"host_udp_main.o": EXEC_BIN, "host_heapmem_main.o": HEAP_BIN}
 
 
 def _newest_header() -> float:
@@ -83,9 +87,12 @@ def build(verbose: bool = False, ptxas_info: bool = False) -> dict[str, Path]:
         main_objs = [o for o in hobjs if o.name.endswith("_main.o")]
         _link(lib_objs + kobjs, EXEC_LIB, True, ["-lpthread"], verbose)
         out["exec"] = EXEC_LIB
-        if main_objs:
-            _link(main_objs + lib_objs + kobjs, EXEC_BIN, False, ["-lpthread"], verbose)
-            out["bin"] = EXEC_BIN
+        for m in main_objs:
+            target = MAIN_BINARIES.get(m.name)
+            if target is None:
+                raise RuntimeError(f"no executable name for {m.name}: add it to MAIN_BINARIES")
+            _link([m] + lib_objs + kobjs, target, False, ["-lpthread"], verbose)
+            out["bin" if target == EXEC_BIN else target.name] = target
     return out
 
 

@@ -3,11 +3,20 @@
 // (registry/registry.h:11-51, registry.cpp:11-86, runtime/lifecycle.cpp:9-85, README.md:13-46).
 // Interface and field list: include/dx_heapmem.h.
 //
-// The store below keeps exactly what the reference would keep in Redis — one string→string map per
-// `tensor:<name>` key and one list of JSON commands — so the registry code reads like its
-// Redis-backed counterpart (HSET/HGETALL/DEL, LPUSH/BRPOP) and only `Store` would change.
+// What the reference keeps in Redis — one string→string map per `tensor:<name>` key and one list of
+// JSON commands — sits behind `Store` (HSET/HGETALL/DEL/KEYS, LPUSH/BRPOP).  Two stores exist: an
+// in-process one, and a Redis server reached with the Redis wire protocol (RESP2) over a plain TCP socket
+// (no client library).  With the server between them, the SERVICE process (`deepx-heapmem`, or any
+// process that calls dx_heap_run_once in a loop) is the only writer of the hashes: it pops commands off
+// the list one at a time, so create-or-get, refcount+1 and refcount-1 are atomic without the Lua scripts
+// the reference's registry evaluates (registry.cpp:24-66; the scripts themselves are not in its tree).
+// Clients in other processes push commands (dx_heap_request) and read hashes (dx_heap_lookup).
 #include <cuda_runtime.h>
+#include <arpa/inet.h>
+#include <netdb.h>
+#include <netinet/tcp.h>
 #include <signal.h>
+#include <sys/socket.h>
 #include <unistd.h>
 
 #include <cctype>
@@ -18,7 +27,9 @@
 #include <cstring>
 #include <deque>
 #include <map>
+#include <memory>
 #include <mutex>
+#include <stdexcept>
 #include <string>
 #include <vector>
 
@@ -34,23 +45,210 @@ int fail(int code, const std::string &msg) {
 
 using Hash = std::map<std::string, std::string>;
 
-struct Store {  // the part Redis would play
+struct Store {  // the part Redis plays
+    virtual ~Store() = default;
+    virtual bool hgetall(const std::string &key, Hash &out) = 0;  // false: no such key
+    virtual void hset(const std::string &key, const Hash &fields) = 0;
+    virtual void del(const std::string &key) = 0;
+    virtual std::vector<std::string> keys(const std::string &prefix) = 0;
+    virtual void lpush(const std::string &list, const std::string &v) = 0;
+    virtual bool brpop(const std::string &list, int timeout_ms, std::string &out) = 0;
+};
+
+struct LocalStore : Store {
     std::mutex mu;
     std::condition_variable cv;
     std::map<std::string, Hash> hashes;
-    std::deque<std::string> list;  // tensor_lifecycle: pushed at the front, popped at the back
-    void lpush(const std::string &v) {
-        { std::lock_guard<std::mutex> lk(mu); list.push_front(v); }
+    std::map<std::string, std::deque<std::string>> lists;  // pushed at the front, popped at the back
+    bool hgetall(const std::string &key, Hash &out) override {
+        std::lock_guard<std::mutex> lk(mu);
+        auto it = hashes.find(key);
+        if (it == hashes.end()) return false;
+        out = it->second;
+        return true;
+    }
+    void hset(const std::string &key, const Hash &fields) override {
+        std::lock_guard<std::mutex> lk(mu);
+        Hash &h = hashes[key];
+        for (auto &kv : fields) h[kv.first] = kv.second;
+    }
+    void del(const std::string &key) override {
+        std::lock_guard<std::mutex> lk(mu);
+        hashes.erase(key);
+    }
+    std::vector<std::string> keys(const std::string &prefix) override {
+        std::lock_guard<std::mutex> lk(mu);
+        std::vector<std::string> out;
+        for (auto &kv : hashes)
+            if (kv.first.compare(0, prefix.size(), prefix) == 0) out.push_back(kv.first);
+        return out;
+    }
+    void lpush(const std::string &list, const std::string &v) override {
+        { std::lock_guard<std::mutex> lk(mu); lists[list].push_front(v); }
         cv.notify_one();
     }
-    bool brpop(int timeout_ms, std::string &out) {
+    bool brpop(const std::string &list, int timeout_ms, std::string &out) override {
         std::unique_lock<std::mutex> lk(mu);
-        if (!cv.wait_for(lk, std::chrono::milliseconds(timeout_ms), [&] { return !list.empty(); })) return false;
-        out = list.back();
-        list.pop_back();
+        auto &q = lists[list];
+        if (!cv.wait_for(lk, std::chrono::milliseconds(timeout_ms), [&] { return !q.empty(); })) return false;
+        out = q.back();
+        q.pop_back();
         return true;
     }
 };
+
+// ---- RESP2 over TCP: the subset the registry needs (PING, HSET, HGETALL, DEL, KEYS, LPUSH, BRPOP) --------------
+struct RespReply {
+    enum Kind { NIL, TEXT, INTEGER, ARRAY, ERROR } kind = NIL;
+    std::string text;
+    long long integer = 0;
+    std::vector<RespReply> items;
+};
+
+class RespClient {
+  public:
+    RespClient(const std::string &host, int port, int timeout_ms) : timeout_ms_(timeout_ms) {
+        addrinfo hints{}, *res = nullptr;
+        hints.ai_family = AF_UNSPEC;
+        hints.ai_socktype = SOCK_STREAM;
+        if (getaddrinfo(host.c_str(), std::to_string(port).c_str(), &hints, &res) != 0 || !res) throw std::runtime_error("cannot resolve " + host);
+        for (addrinfo *a = res; a; a = a->ai_next) {
+            fd_ = socket(a->ai_family, a->ai_socktype, a->ai_protocol);
+            if (fd_ < 0) continue;
+            if (connect(fd_, a->ai_addr, a->ai_addrlen) == 0) break;
+            close(fd_);
+            fd_ = -1;
+        }
+        freeaddrinfo(res);
+        if (fd_ < 0) throw std::runtime_error("cannot connect to " + host + ":" + std::to_string(port));
+        int one = 1;
+        setsockopt(fd_, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+        set_timeout(timeout_ms_);
+    }
+    ~RespClient() { if (fd_ >= 0) close(fd_); }
+    RespClient(const RespClient &) = delete;
+    RespClient &operator=(const RespClient &) = delete;
+
+    // `extra_wait_ms`: a blocking command may take that much longer than the usual reply
+    RespReply command(const std::vector<std::string> &args, int extra_wait_ms = 0) {
+        std::string out = "*" + std::to_string(args.size()) + "\r\n";
+        for (const auto &a : args) out += "$" + std::to_string(a.size()) + "\r\n" + a + "\r\n";
+        size_t done = 0;
+        while (done < out.size()) {
+            const ssize_t n = send(fd_, out.data() + done, out.size() - done, MSG_NOSIGNAL);
+            if (n <= 0) throw std::runtime_error("connection to the store lost while sending");
+            done += size_t(n);
+        }
+        if (extra_wait_ms) set_timeout(timeout_ms_ + extra_wait_ms);
+        RespReply r;
+        try {
+            r = read_reply();
+        } catch (...) {
+            if (extra_wait_ms) set_timeout(timeout_ms_);
+            throw;
+        }
+        if (extra_wait_ms) set_timeout(timeout_ms_);
+        if (r.kind == RespReply::ERROR) throw std::runtime_error("store: " + r.text);
+        return r;
+    }
+
+  private:
+    int fd_ = -1, timeout_ms_;
+    std::string buf_;
+    size_t pos_ = 0;
+    void set_timeout(int ms) {
+        timeval tv{ms / 1000, (ms % 1000) * 1000};
+        setsockopt(fd_, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+    }
+    void fill() {
+        if (pos_ > 0 && pos_ == buf_.size()) { buf_.clear(); pos_ = 0; }
+        char tmp[4096];
+        ssize_t n;
+        do n = recv(fd_, tmp, sizeof(tmp), 0);
+        while (n < 0 && errno == EINTR);
+        if (n <= 0) throw std::runtime_error(n == 0 ? "the store closed the connection" : "no reply from the store in time");
+        buf_.append(tmp, size_t(n));
+    }
+    std::string line() {
+        for (;;) {
+            const size_t e = buf_.find("\r\n", pos_);
+            if (e != std::string::npos) {
+                std::string l = buf_.substr(pos_, e - pos_);
+                pos_ = e + 2;
+                return l;
+            }
+            fill();
+        }
+    }
+    RespReply read_reply() {
+        const std::string l = line();
+        if (l.empty()) throw std::runtime_error("malformed reply from the store");
+        RespReply r;
+        const std::string rest = l.substr(1);
+        switch (l[0]) {
+            case '+': r.kind = RespReply::TEXT; r.text = rest; return r;
+            case '-': r.kind = RespReply::ERROR; r.text = rest; return r;
+            case ':': r.kind = RespReply::INTEGER; r.integer = std::atoll(rest.c_str()); return r;
+            case '$': {
+                const long long n = std::atoll(rest.c_str());
+                if (n < 0) return r;  // nil
+                while (buf_.size() - pos_ < size_t(n) + 2) fill();
+                r.kind = RespReply::TEXT;
+                r.text = buf_.substr(pos_, size_t(n));
+                pos_ += size_t(n) + 2;
+                return r;
+            }
+            case '*': {
+                const long long n = std::atoll(rest.c_str());
+                if (n < 0) return r;  // nil array (BRPOP timeout)
+                r.kind = RespReply::ARRAY;
+                for (long long i = 0; i < n; ++i) r.items.push_back(read_reply());
+                return r;
+            }
+            default: throw std::runtime_error("malformed reply from the store");
+        }
+    }
+};
+
+struct RedisStore : Store {
+    RespClient client;
+    RedisStore(const std::string &host, int port) : client(host, port, 5000) {
+        const RespReply r = client.command({"PING"});
+        if (r.text != "PONG") throw std::runtime_error("the store did not answer PING with PONG");
+    }
+    bool hgetall(const std::string &key, Hash &out) override {
+        const RespReply r = client.command({"HGETALL", key});
+        out.clear();
+        for (size_t i = 0; i + 1 < r.items.size(); i += 2) out[r.items[i].text] = r.items[i + 1].text;
+        return !out.empty();
+    }
+    void hset(const std::string &key, const Hash &fields) override {
+        std::vector<std::string> cmd{"HSET", key};
+        for (auto &kv : fields) {
+            cmd.push_back(kv.first);
+            cmd.push_back(kv.second);
+        }
+        if (cmd.size() > 2) client.command(cmd);
+    }
+    void del(const std::string &key) override { client.command({"DEL", key}); }
+    std::vector<std::string> keys(const std::string &prefix) override {
+        const RespReply r = client.command({"KEYS", prefix + "*"});
+        std::vector<std::string> out;
+        for (auto &it : r.items) out.push_back(it.text);
+        return out;
+    }
+    void lpush(const std::string &list, const std::string &v) override { client.command({"LPUSH", list, v}); }
+    bool brpop(const std::string &list, int timeout_ms, std::string &out) override {
+        // BRPOP counts in seconds (0 = for ever): at least one, rounded up
+        const int secs = timeout_ms <= 0 ? 1 : (timeout_ms + 999) / 1000;
+        const RespReply r = client.command({"BRPOP", list, std::to_string(secs)}, secs * 1000);
+        if (r.kind != RespReply::ARRAY || r.items.size() < 2) return false;
+        out = r.items[1].text;
+        return true;
+    }
+};
+
+const char *const LIFECYCLE_LIST = "tensor_lifecycle";  // executor/heapmem-cuda/README.md:13
 
 struct Command {  // LifecycleCommand, lifecycle.h:12-20, with the shape as numbers
     std::string op, name, dtype, node;
@@ -155,12 +353,13 @@ bool from_hex(const std::string &s, void *p, size_t n) {
 struct dx_heap {
     std::string node;
     int backing;
-    Store store;
-    std::map<std::string, void *> ptrs;  // owner-side pointers; guarded by store.mu
+    std::unique_ptr<Store> store;
+    std::mutex mu;                       // one command at a time in this process
+    std::map<std::string, void *> ptrs;  // owner-side pointers; guarded by mu
 
     static std::string key(const std::string &name) { return "tensor:" + name; }  // Registry::Key, registry.cpp:13-15
 
-    std::string render(const std::string &name, const Hash &h) const {
+    static std::string render(const std::string &name, const Hash &h) {
         auto f = [&](const char *k) { auto it = h.find(k); return it == h.end() ? std::string() : it->second; };
         auto num = [&](const char *k) { const std::string v = f(k); return v.empty() ? std::string("0") : v; };
         return "{\"name\":\"" + name + "\",\"dtype\":\"" + f("dtype") + "\",\"shape\":" + (f("shape").empty() ? "[]" : f("shape")) +
@@ -178,36 +377,44 @@ struct dx_heap {
             *handle_hex = to_hex(fake, sizeof(fake));
             return 0;
         }
+        int prev = -1;
+        cudaGetDevice(&prev);
         cudaError_t e = cudaSetDevice(int(device));
         if (e == cudaSuccess) e = cudaMalloc(ptr, bytes ? bytes : 1);
-        if (e != cudaSuccess) return fail(-4, std::string("cudaMalloc: ") + cudaGetErrorString(e));
         cudaIpcMemHandle_t hd;
-        e = cudaIpcGetMemHandle(&hd, *ptr);
-        if (e != cudaSuccess) {
-            cudaFree(*ptr);
-            *ptr = nullptr;
-            return fail(-4, std::string("cudaIpcGetMemHandle: ") + cudaGetErrorString(e));
+        if (e == cudaSuccess) {
+            e = cudaIpcGetMemHandle(&hd, *ptr);
+            if (e != cudaSuccess) {
+                cudaFree(*ptr);
+                *ptr = nullptr;
+            }
         }
+        if (prev >= 0 && prev != int(device)) cudaSetDevice(prev);
+        if (e != cudaSuccess) return fail(-4, std::string("heap tensor allocation: ") + cudaGetErrorString(e));
         *handle_hex = to_hex(&hd, sizeof(hd));
         return 0;
     }
+
     void release(void *ptr, long long device) {
         if (!ptr) return;
         if (backing == DX_HEAP_HOST_FAKE) {
             std::free(ptr);
             return;
         }
+        int prev = -1;
+        cudaGetDevice(&prev);
         cudaSetDevice(int(device));
         cudaFree(ptr);
+        if (prev >= 0 && prev != int(device)) cudaSetDevice(prev);
     }
 
-    // drop hash + memory; store.mu held
+    // drop hash + memory; mu held
     void drop_locked(const std::string &name) {
-        auto it = store.hashes.find(key(name));
+        Hash h;
         long long device = 0;
-        if (it != store.hashes.end()) {
-            device = std::atoll(it->second["device"].c_str());
-            store.hashes.erase(it);
+        if (store->hgetall(key(name), h)) {
+            device = std::atoll(h["device"].c_str());
+            store->del(key(name));
         }
         auto p = ptrs.find(name);
         if (p != ptrs.end()) {
@@ -227,14 +434,15 @@ struct dx_heap {
     int handle(const Command &c, std::string *reply) {
         if (!plain_text(c.name) || !plain_text(c.dtype) || !plain_text(c.node))
             return fail(-3, "name, dtype and node must not contain quotes, backslashes or control characters");
-        std::lock_guard<std::mutex> lk(store.mu);
-        auto it = store.hashes.find(key(c.name));
+        std::lock_guard<std::mutex> lk(mu);
+        Hash h;
+        const bool exists = store->hgetall(key(c.name), h);
         if (c.op == "create") {
-            if (it != store.hashes.end()) {  // create-or-get
-                Hash &h = it->second;
+            if (exists) {  // create-or-get (Registry::CreateOrGet, registry.cpp:24-45)
                 if ((!c.dtype.empty() && dtype_bytes(c.dtype) != dtype_bytes(h["dtype"])) || (c.has_shape && shape_text(c.shape) != h["shape"]))
                     return fail(-2, "tensor " + c.name + " exists as " + h["dtype"] + h["shape"] + ", asked for " + c.dtype + shape_text(c.shape));
                 h["refcount"] = std::to_string(std::atoll(h["refcount"].c_str()) + 1);
+                store->hset(key(c.name), {{"refcount", h["refcount"]}});
                 if (reply) *reply = render(c.name, h);
                 return 0;
             }
@@ -251,7 +459,7 @@ struct dx_heap {
             void *ptr = nullptr;
             std::string hex;
             if (int e = allocate(c.device, nbytes, &ptr, &hex)) return e;
-            Hash h;
+            h.clear();
             h["dtype"] = c.dtype;
             h["shape"] = shape_text(c.shape);
             h["ctime"] = std::to_string(std::chrono::duration_cast<std::chrono::seconds>(std::chrono::system_clock::now().time_since_epoch()).count());
@@ -261,16 +469,16 @@ struct dx_heap {
             h["ipc_handle"] = hex;
             h["refcount"] = "1";
             h["state"] = "ready";
-            h["owner_pid"] = std::to_string(c.pid ? c.pid : (long long)getpid());
-            store.hashes[key(c.name)] = h;
+            h["owner_pid"] = std::to_string(c.pid ? c.pid : (long long)getpid());  // whose death releases the tensor (dx_heap_gc_sweep)
+            store->hset(key(c.name), h);
             ptrs[c.name] = ptr;
             if (reply) *reply = render(c.name, h);
             return 0;
         }
-        if (it == store.hashes.end()) return fail(-1, c.op + ": no tensor named " + c.name);
-        Hash &h = it->second;
+        if (!exists) return fail(-1, c.op + ": no tensor named " + c.name);
         if (c.op == "get") {  // Registry::RefInc, registry.cpp:47-52
             h["refcount"] = std::to_string(std::atoll(h["refcount"].c_str()) + 1);
+            store->hset(key(c.name), {{"refcount", h["refcount"]}});
             if (reply) *reply = render(c.name, h);
             return 0;
         }
@@ -282,7 +490,10 @@ struct dx_heap {
                 h["ipc_handle"] = "";
                 if (reply) *reply = render(c.name, h);
                 drop_locked(c.name);
-            } else if (reply) *reply = render(c.name, h);
+            } else {
+                store->hset(key(c.name), {{"refcount", h["refcount"]}});
+                if (reply) *reply = render(c.name, h);
+            }
             return 0;
         }
         return fail(-3, "unknown op '" + c.op + "' (create|get|delete)");
@@ -308,6 +519,12 @@ int put(const std::string &s, char *out, size_t cap) {
 }
 }  // namespace
 
+static std::string host_name() {
+    char buf[256] = {0};
+    gethostname(buf, sizeof(buf) - 1);
+    return buf;
+}
+
 extern "C" {
 
 dx_heap *dx_heap_create(const char *node, int backing) {
@@ -317,22 +534,38 @@ dx_heap *dx_heap_create(const char *node, int backing) {
     }
     auto *h = new dx_heap();
     h->backing = backing;
-    if (node && *node) h->node = node;
-    else {
-        char buf[256] = {0};
-        gethostname(buf, sizeof(buf) - 1);
-        h->node = buf;
-    }
+    h->store = std::make_unique<LocalStore>();
+    h->node = node && *node ? node : host_name();
     return h;
+}
+
+dx_heap *dx_heap_create_redis(const char *node, int backing, const char *host, int port) {
+    if (backing != DX_HEAP_DEVICE && backing != DX_HEAP_HOST_FAKE) {
+        fail(-3, "unknown backing");
+        return nullptr;
+    }
+    try {
+        auto store = std::make_unique<RedisStore>(host && *host ? host : "127.0.0.1", port > 0 ? port : 6379);
+        auto *h = new dx_heap();
+        h->backing = backing;
+        h->store = std::move(store);
+        h->node = node && *node ? node : host_name();
+        return h;
+    } catch (const std::exception &e) {
+        fail(-4, e.what());
+        return nullptr;
+    }
 }
 
 void dx_heap_destroy(dx_heap *h) {
     if (!h) return;
-    {
-        std::lock_guard<std::mutex> lk(h->store.mu);
+    try {
+        std::lock_guard<std::mutex> lk(h->mu);
         std::vector<std::string> names;
         for (auto &p : h->ptrs) names.push_back(p.first);
         for (auto &n : names) h->drop_locked(n);
+    } catch (const std::exception &) {
+        // the store is unreachable: the memory is released with the process
     }
     delete h;
 }
@@ -344,42 +577,62 @@ int dx_heap_command(dx_heap *h, const char *json, char *reply, size_t cap) {
     Command c;
     if (!parse_command(json, c)) return fail(-3, "command needs \"op\" and \"name\"");
     std::string text;
-    if (int e = h->handle(c, &text)) return e;
+    try {
+        if (int e = h->handle(c, &text)) return e;
+    } catch (const std::exception &e) {
+        return fail(-4, e.what());
+    }
     return put(text, reply, cap);
 }
 
 int dx_heap_push(dx_heap *h, const char *json) {
     if (!h || !json) return fail(-3, "null heap or command");
-    h->store.lpush(json);
+    try {
+        h->store->lpush(LIFECYCLE_LIST, json);
+    } catch (const std::exception &e) {
+        return fail(-4, e.what());
+    }
     return 0;
 }
 
 int dx_heap_run_once(dx_heap *h, int timeout_ms) {
     if (!h) return fail(-3, "null heap");
     std::string msg;
-    if (!h->store.brpop(timeout_ms < 0 ? 0 : timeout_ms, msg)) return 0;
-    Command c;
-    if (parse_command(msg, c)) h->handle(c, nullptr);  // a worker has nobody to report to: bad commands are dropped (lifecycle.cpp:68-71)
+    try {
+        if (!h->store->brpop(LIFECYCLE_LIST, timeout_ms < 0 ? 0 : timeout_ms, msg)) return 0;
+        Command c;
+        if (parse_command(msg, c)) h->handle(c, nullptr);  // a worker has nobody to report to: bad commands are dropped (lifecycle.cpp:68-71)
+    } catch (const std::exception &e) {
+        return fail(-4, e.what());
+    }
     return 1;
 }
 
 int dx_heap_meta(dx_heap *h, const char *name, char *out, size_t cap) {
     if (!h || !name) return fail(-3, "null heap or name");
-    std::lock_guard<std::mutex> lk(h->store.mu);
-    auto it = h->store.hashes.find(dx_heap::key(name));
-    if (it == h->store.hashes.end()) return fail(-1, std::string("no tensor named ") + name);
-    return put(h->render(name, it->second), out, cap);
+    try {
+        std::lock_guard<std::mutex> lk(h->mu);
+        Hash f;
+        if (!h->store->hgetall(dx_heap::key(name), f)) return fail(-1, std::string("no tensor named ") + name);
+        return put(dx_heap::render(name, f), out, cap);
+    } catch (const std::exception &e) {
+        return fail(-4, e.what());
+    }
 }
 
 int dx_heap_count(dx_heap *h) {
     if (!h) return 0;
-    std::lock_guard<std::mutex> lk(h->store.mu);
-    return int(h->store.hashes.size());
+    try {
+        std::lock_guard<std::mutex> lk(h->mu);
+        return int(h->store->keys("tensor:").size());
+    } catch (const std::exception &) {
+        return 0;
+    }
 }
 
 void *dx_heap_ptr(dx_heap *h, const char *name) {
     if (!h || !name) return nullptr;
-    std::lock_guard<std::mutex> lk(h->store.mu);
+    std::lock_guard<std::mutex> lk(h->mu);
     auto it = h->ptrs.find(name);
     return it == h->ptrs.end() ? nullptr : it->second;
 }
@@ -387,17 +640,47 @@ void *dx_heap_ptr(dx_heap *h, const char *name) {
 int64_t dx_heap_gc_sweep(dx_heap *h, const char *node) {
     if (!h) return 0;
     const std::string which = node && *node ? node : h->node;
-    std::lock_guard<std::mutex> lk(h->store.mu);
-    std::vector<std::string> dead;
-    for (auto &kv : h->store.hashes) {
-        Hash &f = kv.second;
-        if (f["node"] != which) continue;
-        const long long pid = std::atoll(f["owner_pid"].c_str());
-        const bool owner_gone = which == h->node && pid > 0 && kill(pid_t(pid), 0) != 0 && errno == ESRCH;
-        if (std::atoll(f["refcount"].c_str()) <= 0 || owner_gone) dead.push_back(kv.first.substr(7));
+    try {
+        std::lock_guard<std::mutex> lk(h->mu);
+        std::vector<std::string> dead;
+        for (const auto &k : h->store->keys("tensor:")) {
+            Hash f;
+            if (!h->store->hgetall(k, f) || f["node"] != which) continue;
+            const long long pid = std::atoll(f["owner_pid"].c_str());
+            const bool owner_gone = which == h->node && pid > 0 && kill(pid_t(pid), 0) != 0 && errno == ESRCH;
+            if (std::atoll(f["refcount"].c_str()) <= 0 || owner_gone) dead.push_back(k.substr(7));
+        }
+        for (auto &n : dead) h->drop_locked(n);
+        return int64_t(dead.size());
+    } catch (const std::exception &e) {
+        return fail(-4, e.what());
     }
-    for (auto &n : dead) h->drop_locked(n);
-    return int64_t(dead.size());
+}
+
+// ---- the client side of a store-backed service: other processes of the machine -------------------------------
+int dx_heap_request(const char *host, int port, const char *json) {
+    if (!json) return fail(-3, "null command");
+    Command c;
+    if (!parse_command(json, c)) return fail(-3, "command needs \"op\" and \"name\"");
+    try {
+        RedisStore store(host && *host ? host : "127.0.0.1", port > 0 ? port : 6379);
+        store.lpush(LIFECYCLE_LIST, json);
+        return 0;
+    } catch (const std::exception &e) {
+        return fail(-4, e.what());
+    }
+}
+
+int dx_heap_lookup(const char *host, int port, const char *name, char *out, size_t cap) {
+    if (!name) return fail(-3, "null name");
+    try {
+        RedisStore store(host && *host ? host : "127.0.0.1", port > 0 ? port : 6379);
+        Hash f;
+        if (!store.hgetall(dx_heap::key(name), f)) return fail(-1, std::string("no tensor named ") + name);
+        return put(dx_heap::render(name, f), out, cap);
+    } catch (const std::exception &e) {
+        return fail(-4, e.what());
+    }
 }
 
 void *dx_heap_open(const char *ipc_handle_hex, int device) {

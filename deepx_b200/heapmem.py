@@ -15,6 +15,9 @@ from .executor import lib as _exec_lib
 _vp, _i, _sz, _cp = C.c_void_p, C.c_int, C.c_size_t, C.c_char_p
 SIGNATURES = {
     "dx_heap_create": (_vp, [_cp, _i]),
+    "dx_heap_create_redis": (_vp, [_cp, _i, _cp, _i]),
+    "dx_heap_request": (_i, [_cp, _i, _cp]),
+    "dx_heap_lookup": (_i, [_cp, _i, _cp, C.c_char_p, _sz]),
     "dx_heap_destroy": (None, [_vp]),
     "dx_heap_last_error": (_cp, []),
     "dx_heap_command": (_i, [_vp, _cp, C.c_char_p, _sz]),
@@ -55,8 +58,13 @@ def _err() -> str:
 class Heap:
     """The owner side: registry + allocations.  ``backing=HOST_FAKE`` runs the registry without a GPU."""
 
-    def __init__(self, node: str | None = None, backing: int = DEVICE):
-        self._h = lib().dx_heap_create(node.encode() if node else None, backing)
+    def __init__(self, node: str | None = None, backing: int = DEVICE, redis: tuple[str, int] | None = None):
+        """`redis` = (host, port): hashes and the command list live in that Redis server (the service side of a
+        multi-process set-up, what the ``deepx-heapmem`` daemon is); None keeps them in this process."""
+        if redis is None:
+            self._h = lib().dx_heap_create(node.encode() if node else None, backing)
+        else:
+            self._h = lib().dx_heap_create_redis(node.encode() if node else None, backing, redis[0].encode(), int(redis[1]))
         if not self._h:
             raise HeapError(_err())
         self._buf = C.create_string_buffer(1 << 14)
@@ -104,6 +112,24 @@ class Heap:
 
     def gc_sweep(self, node: str | None = None) -> int:
         return int(lib().dx_heap_gc_sweep(self._h, node.encode() if node else None))
+
+
+def request(redis: tuple[str, int], cmd: dict | str) -> None:
+    """Client side: push one lifecycle command for the service process behind `redis` = (host, port)."""
+    text = cmd if isinstance(cmd, str) else json.dumps(cmd)
+    if lib().dx_heap_request(redis[0].encode(), int(redis[1]), text.encode()) != 0:
+        raise HeapError(_err())
+
+
+def lookup(redis: tuple[str, int], name: str) -> dict:
+    """Client side: the tensor's hash (KeyError while the service has not created it yet)."""
+    buf = C.create_string_buffer(1 << 14)
+    rc = lib().dx_heap_lookup(redis[0].encode(), int(redis[1]), name.encode(), buf, len(buf))
+    if rc == -1:
+        raise KeyError(name)
+    if rc != 0:
+        raise HeapError(_err())
+    return json.loads(buf.value.decode())
 
 
 def open_handle(ipc_handle_hex: str, device: int = 0) -> int:

@@ -12,10 +12,15 @@
  * with  create = allocate → cudaIpcGetMemHandle → hash(state=ready, refcount=1),
  *       get    = read hash → refcount+1 (the caller maps the memory with cudaIpcOpenMemHandle),
  *       delete = refcount-1, at 0 free the memory and drop the hash.
- * The reference keeps hash and list in Redis (redis++ is not in this image and the reference
- * ships neither its client wrapper nor its Lua scripts); here the same keys and fields live in an
- * in-process store behind the same operations, so a Redis transport can be put under it without
- * changing this interface.  Every heap tensor is its own cudaMalloc allocation: CUDA IPC exports
+ * The reference keeps hash and list in a Redis server.  Two stores are offered here behind the same
+ * operations: an in-process one (dx_heap_create: registry and its users in one process), and a Redis
+ * server spoken to with the Redis wire protocol over a plain TCP socket (dx_heap_create_redis: no
+ * client library is needed; redis++ and the reference's Lua scripts are not in its tree).  With a
+ * server, ONE service process owns the allocations and is the only writer of the hashes — the
+ * `deepx-heapmem` daemon, which pops commands off `tensor_lifecycle` one at a time — so create-or-get
+ * and the refcount changes are atomic without scripts; every other process pushes commands
+ * (dx_heap_request) and reads hashes (dx_heap_lookup), then maps the memory with dx_heap_open.
+ * Every heap tensor is its own cudaMalloc allocation: CUDA IPC exports
  * whole allocations, so heap tensors never come from the sub-allocating pool (README.md:48-52).
  *
  * All functions return 0 (or a count) on success and a negative value on failure; the text of the
@@ -40,6 +45,9 @@ enum {
 
 /* `node` is this machine's name as it appears in the `node` field (NULL = the host name). */
 dx_heap *dx_heap_create(const char *node, int backing);
+/* The same service with its hashes and its command list in a Redis server at host:port (NULL / 0 =
+ * 127.0.0.1:6379).  NULL when the server cannot be reached (dx_heap_last_error). */
+dx_heap *dx_heap_create_redis(const char *node, int backing, const char *host, int port);
 void dx_heap_destroy(dx_heap *h); /* frees every tensor still registered */
 const char *dx_heap_last_error(void);
 
@@ -65,6 +73,11 @@ void *dx_heap_ptr(dx_heap *h, const char *name);
 /* Registry::GcSweep (registry.cpp:61-66): drops the tensors of `node` (NULL = this node) whose
  * refcount is not positive or whose owning process no longer exists; returns how many. */
 int64_t dx_heap_gc_sweep(dx_heap *h, const char *node);
+
+/* Client side of a server-backed service: push one lifecycle command onto `tensor_lifecycle` (the daemon
+ * handles it), and read a tensor's hash as the JSON object above (-1 when there is no such tensor yet). */
+int dx_heap_request(const char *host, int port, const char *json);
+int dx_heap_lookup(const char *host, int port, const char *name, char *out, size_t cap);
 
 /* Consumer side, in ANOTHER process than the owner: map / unmap the memory behind an ipc_handle
  * (hex text from the hash) on `device` (cudaIpcOpenMemHandle / cudaIpcCloseMemHandle), and copy

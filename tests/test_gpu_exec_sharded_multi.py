@@ -85,7 +85,6 @@ WORKER = textwrap.dedent("""
     assert len(set(every)) == 1, "replicated results differ between ranks"
 
     # a replicated operand of the same global shape is used through its rows; a replicated output is completed by a gather
-    ex2 = None
     new("xs", "float32", (R, 4)); new("ys", "float32", (R, 4))        # 976 bytes: replicated
     assert not ex.shard("xs")[0]
     XS = rng.uniform(-1, 1, (R, 4)).astype(np.float32)
@@ -161,3 +160,55 @@ def test_executor_ranks_on_real_gpus():
     outs = [p.communicate(timeout=600)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and f"rank {r} ok" in o, f"rank {r}:\n{o}"
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_udp_process_over_two_devices(tmp_path):
+    """deepx-op-b200 with DEEPX_DEVICES=0,1: one port, one reply per IR line, the tensors partitioned over two worker
+    processes behind it.  The files `save` leaves are those a single GPU would write."""
+    import socket
+    import numpy as np
+    from deepx_b200.executor import BIN_PATH
+    port = 23000 + os.getpid() % 20000
+    env = dict(os.environ, DEEPX_PORT=str(port), DEEPX_DEVICES="0,1", DEEPX_SHARD_MIN_BYTES="4096", NCCL_NVLS_ENABLE="0")
+    proc = subprocess.Popen([str(BIN_PATH)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        first = proc.stdout.readline()
+        assert "listening" in first and "devices 0,1" in first, first
+        sock = socket.socket(socket.AF_INET, socket.SOCK_DGRAM)
+        sock.settimeout(60)
+
+        def send(text):
+            sock.sendto(text.encode(), ("127.0.0.1", port))
+            return [sock.recvfrom(65536)[0].decode() for _ in [l for l in text.split("\n") if l.strip()]]
+
+        f = "tensor<float32>"
+        replies = send("\n".join([
+            f"newtensor(vector<int32>:[64 1000])->({f}:a) // id=1",
+            f"newtensor(vector<int32>:[64 1000])->({f}:b) // id=2",
+            f"newtensor(vector<int32>:[1])->({f}:s) // id=3",
+            f"newtensor(vector<int32>:[1000])->({f}:c) // id=4",
+            f"arange(var<float32>:0, var<float32>:1)->({f}:a) // author=miaobyte id=5",
+            f"mulscalar({f}:a, var<float32>:0.5)->({f}:b) // author=miaobyte id=6",
+            f"sum({f}:b, vector<int32>:[0 1], var<bool>:false)->({f}:s) // author=miaobyte id=7",
+            f"reducemax({f}:b, vector<int32>:[0], var<bool>:false)->({f}:c) // author=miaobyte id=8",
+            f"save({f}:b, var<string>:{tmp_path / 'b'})->() // id=9",
+            f"save({f}:s, var<string>:{tmp_path / 's'})->() // id=10",
+            f"save({f}:c, var<string>:{tmp_path / 'c'})->() // id=11"]))
+        assert len(replies) == 11 and all(" ok" in r.split("//")[0] for r in replies), replies
+        assert [int(r.split()[0]) for r in replies] == list(range(1, 12))
+        want = (np.arange(64000, dtype=np.float32) * np.float32(0.5)).reshape(64, 1000)
+        assert np.array_equal(np.fromfile(tmp_path / "b.data", dtype=np.float32).reshape(64, 1000), want)
+        s = np.fromfile(tmp_path / "s.data", dtype=np.float32)
+        assert abs(float(s[0]) - want.astype(np.float64).sum()) <= 1e-5 * want.astype(np.float64).sum()
+        assert np.array_equal(np.fromfile(tmp_path / "c.data", dtype=np.float32), want.max(0))
+        # an op without a row-wise form on a partitioned tensor: one error reply, and the process carries on
+        bad = send(f"newtensor(vector<int32>:[1000 64])->({f}:bt) // id=20\ntranspose({f}:b, vector<int32>:[1 0])->({f}:bt) // author=miaobyte id=21")
+        assert " ok" in bad[0].split("//")[0] and " error" in bad[1].split("//")[0] and "row-partitioned" in bad[1]
+        assert " ok" in send(f"addscalar({f}:b, var<float32>:1)->({f}:b) // author=miaobyte id=22")[0].split("//")[0]
+    finally:
+        proc.terminate()
+        try:
+            proc.communicate(timeout=30)
+        except Exception:
+            proc.kill()
