@@ -432,6 +432,19 @@ def op_cases(torch, TF, dev):
         Cm = torch.empty(8192, 4096, device=dev)
         return [lambda: TF.matmul(A, B, Cm)], 0, 2 * 8192 * 4096 * 4096
 
+    def pow_f32(kind):
+        def build():  # 256 MiB per tensor, as in --sweep: what the profiler captures of the pow kernels are taken on
+            n = (256 << 20) // 4
+            a = [(torch.rand(n, device=dev, generator=g) * 1.5 + 0.5) for _ in range(R)]
+            b = [(torch.rand(n, device=dev, generator=g) * 1.5 + 0.5) for _ in range(R)]
+            c = [torch.empty(n, device=dev) for _ in range(R)]
+            if kind == "pow":
+                return [lambda i=i: TF.pow(a[i], b[i], c[i]) for i in range(R)], 3 * n * 4, None
+            if kind == "powscalar":
+                return [lambda i=i: TF.powscalar(a[i], 2.5, c[i]) for i in range(R)], 2 * n * 4, None
+            return [lambda i=i: TF.rpowscalar(1.7, a[i], c[i]) for i in range(R)], 2 * n * 4, None
+        return build
+
     def rms_fused():
         x = nrm(16, 2048, 896, n=R)
         w = nrm(896)[0]
@@ -501,6 +514,7 @@ def op_cases(torch, TF, dev):
         "transpose_f32_8192x8192_10": transpose_inner(torch.float32), "transpose_bf16_8192x8192_10": transpose_inner(torch.bfloat16), "concat_4x_f32_8x1024x4096_axis1": concat_f32,
         "broadcastTo_f32_1x4096_to_8192x4096": broadcast_f32, "indexselect_f32_151936x896_by_8x2048": indexselect_f32,
         "matmul_bf16_8192x4096x4096": matmul_bf16, "matmul_f32_8192x4096x4096": matmul_f32,
+        "pow_f32_64Mi": pow_f32("pow"), "powscalar_2.5_f32_64Mi": pow_f32("powscalar"), "rpowscalar_1.7_f32_64Mi": pow_f32("rpowscalar"),
         "rmsnorm_fused_f32_16x2048x896": rms_fused, "softmax_fused_f32_32768x2048": softmax_fused,
         "rmsnorm_ten_single_ops_f32_16x2048x896": rms_single_ops,
         "rmsnorm_mul_xx_f32_16x2048x896": rms("mul"), "rmsnorm_sum_last_f32_16x2048x896": rms("sum"),

@@ -426,16 +426,24 @@ __global__ void __launch_bounds__(CB) indexselect_inner_smem_kernel(const E *__r
         }
         __syncthreads();
         E *dst = out + r0 * p.J;
-        for (int v = threadIdx.x; v < nr * jvec; v += CB) {
-            const int lr = v / jvec, j0 = (v - lr * jvec) * VEC;
-            const E *row = srow + lr * p.K;
-            Pack<E, VEC> o;
+        // A thread keeps the VEC indices of ITS output column group in registers and walks the staged rows with
+        // them: one shared-memory read per element (the picked value) instead of two (index and value).
+        auto pick_rows = [&](int c, int lr_first, int lr_step) {
+            int32_t ix[VEC];
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) {
-                const int32_t ix = sidx[j0 + j];
-                o.v[j] = ix >= 0 ? row[ix] : E(0);
+            for (int j = 0; j < VEC; ++j) ix[j] = sidx[c * VEC + j];
+            for (int lr = lr_first; lr < nr; lr += lr_step) {
+                const E *row = srow + lr * p.K;
+                Pack<E, VEC> o;
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) o.v[j] = ix[j] >= 0 ? row[ix[j]] : E(0);
+                st_stream<E, VEC>(dst + int64_t(lr) * p.J + c * VEC, o);
             }
-            st_stream<E, VEC>(dst + int64_t(lr) * p.J + j0, o);
+        };
+        if (jvec <= CB && CB % jvec == 0) {
+            pick_rows(threadIdx.x % jvec, threadIdx.x / jvec, CB / jvec);  // several rows per sweep of the CTA
+        } else {
+            for (int c = threadIdx.x; c < jvec; c += CB) pick_rows(c, 0, 1);
         }
     }
 }
