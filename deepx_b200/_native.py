@@ -83,6 +83,8 @@ SIGNATURES = {
     "dx_indexselect": (_i, [_i, _vp, _pi64, _i, _i, _vp, _pi64, _i, _i, _vp, _vp, _vp]),
     "dx_repeat": (_i, [_i, _vp, _pi64, _i, _pi64, _vp, _vp]),
     "dx_matmul": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp]),
+    "dx_matmul_workspace_bytes": (_sz, [_i, _i64, _i64, _i64, _i64]),
+    "dx_matmul_ws": (_i, [_i, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _vp, _sz, _vp]),
     "dx_matmul_status": (_i, [_vp]),
     "dx_pool_create": (_vp, [_i, _sz]),
     "dx_pool_destroy": (None, [_vp]),

@@ -551,7 +551,19 @@ struct MatMulTF : TF {
         const int64_t batch = (m * k) ? A->shape.size / (m * k) : 0;
         if (C->shape.size != batch * m * n) throw std::invalid_argument("shape mismatch");
         if (C->data == A->data || C->data == B->data) { error = "matmul: output tensor is an input tensor"; return 1; }
-        dx_check(dx_matmul(A->dx(), A->data, B->data, C->data, batch, m, n, k, mem.stream()));
+        // a few rows of tiles: the K range is split over independent CTA pairs through scratch memory
+        // (a captured program keeps using the path it was captured with: the scratch cannot grow then)
+        size_t need = dx_matmul_workspace_bytes(A->dx(), batch, m, n, k);
+        void *ws = nullptr;
+        if (need) {
+            try {
+                ws = mem.scratch(need);
+            } catch (const std::exception &) {
+                ws = nullptr;  // no room (or capturing): the kernels that need no scratch
+                need = 0;
+            }
+        }
+        dx_check(dx_matmul_ws(A->dx(), A->data, B->data, C->data, batch, m, n, k, ws, need, mem.stream()));
         return 0;
     }
 };

@@ -208,55 +208,62 @@ constexpr int EPI_BYTES = 8 * EPI_WARP_BYTES;            // 32 KiB for the eight
 // (A TMA store of the same block costs the issuing lane about 300 cycles per 4 KiB, measured, and the
 // wait before its buffer may be reused another 200; the plain stores need neither.)
 // Without `staged` each lane stores its own row from registers.
+// The second half of the way out: a warp's block of 32 rows × 64 columns, one row per lane in r[2][32] as fp32 bit
+// patterns, rounded once and written to C (turned round in shared memory when `staged`, else row by row).
+template <typename T>
+__device__ __forceinline__ void emit_block(const uint32_t (&r)[2][32], T *C, bool staged, uint32_t stage_smem, int M, int N, int b, int row0,
+                                           int col, int lane) {
+    const int row = row0 + lane;
+    if (row0 >= M || col >= N) return;  // the whole block lies outside C (same answer in every lane)
+    if (staged) {
+        const uint32_t mine = stage_smem + lane * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                const int chunk = h * 4 + v;
+                st_shared_v4(mine + ((chunk ^ (lane & 7)) << 4),
+                             pack2<T>(__uint_as_float(r[h][8 * v + 0]), __uint_as_float(r[h][8 * v + 1])),
+                             pack2<T>(__uint_as_float(r[h][8 * v + 2]), __uint_as_float(r[h][8 * v + 3])),
+                             pack2<T>(__uint_as_float(r[h][8 * v + 4]), __uint_as_float(r[h][8 * v + 5])),
+                             pack2<T>(__uint_as_float(r[h][8 * v + 6]), __uint_as_float(r[h][8 * v + 7])));
+            }
+        __syncwarp();
+        // lane → (row lane/8 of a group of four rows, chunk lane%8): 4 rows × 128 bytes per instruction
+        const int chunk = lane & 7;
+        const int gcol = col + chunk * 8;
+        uint4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3);
+            v[i] = ld_shared_v4(stage_smem + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int rr = i * 4 + (lane >> 3);
+            if (row0 + rr < M && gcol < N) *reinterpret_cast<uint4 *>(C + (size_t(b) * M + row0 + rr) * N + gcol) = v[i];
+        }
+        __syncwarp();  // the block is in registers / on its way before the next one overwrites the buffer
+    } else if (row < M) {
+        T *crow = C + (size_t(b) * M + row) * N;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (col + 32 * h + j < N) crow[col + 32 * h + j] = from_compute<T>(__uint_as_float(r[h][j]));
+    }
+}
+
 template <typename T>
 __device__ __forceinline__ void drain_accumulator(uint32_t tmem_acc, int width, T *C, bool staged, uint32_t stage_smem, int M, int N,
                                                   int b, int row0, int col0, int lane) {
-    const int row = row0 + lane;
 #pragma unroll 1
     for (int c0 = 0; c0 < width; c0 += EPI_COLS) {
         uint32_t r[2][32];
         tmem_ld_32x32b_x32(tmem_acc + c0, r[0]);
         tmem_ld_32x32b_x32(tmem_acc + c0 + 32, r[1]);
         tmem_ld_wait();
-        const int col = col0 + c0;
-        if (row0 >= M || col >= N) continue;  // the whole block lies outside C (same answer in every lane)
-        if (staged) {
-            const uint32_t mine = stage_smem + lane * 128;
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    const int chunk = h * 4 + v;
-                    st_shared_v4(mine + ((chunk ^ (lane & 7)) << 4),
-                                 pack2<T>(__uint_as_float(r[h][8 * v + 0]), __uint_as_float(r[h][8 * v + 1])),
-                                 pack2<T>(__uint_as_float(r[h][8 * v + 2]), __uint_as_float(r[h][8 * v + 3])),
-                                 pack2<T>(__uint_as_float(r[h][8 * v + 4]), __uint_as_float(r[h][8 * v + 5])),
-                                 pack2<T>(__uint_as_float(r[h][8 * v + 6]), __uint_as_float(r[h][8 * v + 7])));
-                }
-            __syncwarp();
-            // lane → (row lane/8 of a group of four rows, chunk lane%8): 4 rows × 128 bytes per instruction
-            const int chunk = lane & 7;
-            const int gcol = col + chunk * 8;
-            uint4 v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int rr = i * 4 + (lane >> 3);
-                v[i] = ld_shared_v4(stage_smem + rr * 128 + ((chunk ^ (rr & 7)) << 4));
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int rr = i * 4 + (lane >> 3);
-                if (row0 + rr < M && gcol < N) *reinterpret_cast<uint4 *>(C + (size_t(b) * M + row0 + rr) * N + gcol) = v[i];
-            }
-            __syncwarp();  // the block is in registers / on its way before the next one overwrites the buffer
-        } else if (row < M) {
-            T *crow = C + (size_t(b) * M + row) * N;
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    if (col + 32 * h + j < N) crow[col + 32 * h + j] = from_compute<T>(__uint_as_float(r[h][j]));
-        }
+        emit_block<T>(r, C, staged, stage_smem, M, N, b, row0, col0 + c0, lane);
     }
 }
 
@@ -1056,6 +1063,205 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
         }
     }
+    // the pair frees its TMEM together
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, BN);
+    }
+}
+
+// ---- a few rows of tiles, K split over INDEPENDENT pairs through a workspace ----------------------------
+// The cluster form above pays two cluster barriers, a late start (clusters of 4–8 CTAs must find room in one GPC)
+// and the exchange of partials, about 8 µs, so it only helps when K is long.  Here every (tile, K slice) is an
+// ordinary CTA pair of its own: the pair runs the cta_group::2 main loop over its slice, writes its fp32 partial
+// to the caller's workspace in the order the values come out of TMEM (every store instruction of a warp covers 512
+// contiguous bytes), and counts itself in on a per-(tile, half) counter.  The CTA that arrives LAST adds the KS
+// partials of its 128 rows in slice order — whoever finishes, the sum has the same order, so the same bits — rounds
+// once and writes C through the block-turning epilogue, then puts the counter back to zero.  No CTA waits for
+// another, no atomics on data.  Workspace: tiles × KS × 256 × 256 floats.
+struct PairWsParams {
+    int M, N, K, batch;
+    int tiles_m, tiles_n, k_blocks, kb_per_slice, ks;
+    int c_staged;
+    int *status;
+    float *partial;          // [tile][slice][half][128 rows × 256 columns in TMEM order]
+    unsigned int *counters;  // [tile][half], zero between launches
+};
+constexpr int WS_HALF_FLOATS = BM * BN;  // 32768 floats = 128 KiB per CTA and slice
+__device__ unsigned int g_wsk_counters[512];
+
+template <typename T>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+    gemm_tcgen05_pair_wsk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                                 T *__restrict__ C, PairWsParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (smem_base - smem_u32(smem_raw));
+    constexpr int BAR_OFF = P_STAGES * P_STAGE_BYTES;
+    const uint32_t bars = smem_base + BAR_OFF;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (P_STAGES + s); };
+    const uint32_t tfull_bar = bars + 8u * (2 * P_STAGES);
+    constexpr int SLOT_OFF = 8 * (2 * P_STAGES + 1);
+    const uint32_t tmem_slot = bars + SLOT_OFF;
+    volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + BAR_OFF + SLOT_OFF);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + BAR_OFF + SLOT_OFF + 8);
+    volatile int *last_flag = reinterpret_cast<volatile int *>(gen_base + BAR_OFF + SLOT_OFF + 12);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t half = cluster_ctarank();  // which 128 rows of the pair tile; rank 0 issues the MMAs
+    const int unit = blockIdx.x >> 1;         // (tile, slice)
+    const int tile = unit / p.ks;
+    const int slice = unit - tile * p.ks;
+    const int per_batch = p.tiles_m * p.tiles_n;
+    const int b = tile / per_batch;
+    const int tm = (tile - b * per_batch) / p.tiles_n;
+    const int tn = tile - b * per_batch - tm * p.tiles_n;
+    const int kb0 = slice * p.kb_per_slice;
+    const int kb1 = min(p.k_blocks, kb0 + p.kb_per_slice);
+    const int nkb = max(kb1 - kb0, 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) {
+            mbar_init(full_bar(s), 1);   // used in the leader only
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(tfull_bar, 1);
+        *abort_flag = 0;
+        *last_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) tmem_alloc_pair(tmem_slot, BN);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();  // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            for (int kb = kb0; kb < kb1; ++kb) {
+                if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_EMPTY); }
+                    break;
+                }
+                const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+                const uint32_t sb = sa + A_STAGE_BYTES;
+                const uint32_t leader_full = mapa_u32(full_bar(stage), 0);
+                if (half == 0) mbar_expect_tx(full_bar(stage), 2 * P_STAGE_BYTES);  // both CTAs' bytes
+                tma_load_3d_pair(sa, &tmap_a, leader_full, kb * BK, tm * PBM + int(half) * BM, b);
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+                    tma_load_3d_pair(sb + j * B_BOX_BYTES, &tmap_b, leader_full, tn * BN + int(half) * 128 + j * B_BOX_N, kb * BK, b);
+                if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (*abort_flag) {
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000ll) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && half == 0 && nkb > 0) {
+            constexpr uint32_t idesc = make_idesc_pair(std::is_same<T, bf16>::value ? 1 : 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+                    if (!*abort_flag) { *abort_flag = 1; atomicExch(p.status, GEMM_TIMEOUT_FULL); }
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_base + stage * P_STAGE_BYTES;
+                const uint32_t sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint64_t adesc = make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024);
+                    const uint64_t bdesc = make_smem_desc(sb + k * (UMMA_K * 128), B_BOX_BYTES, 1024);
+                    umma_f16_pair(tmem_base, adesc, bdesc, idesc, (kb | k) != 0);
+                }
+                umma_commit_pair(empty_bar(stage), 0x3);
+                if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (ok) umma_commit_pair(tfull_bar, 0x3);  // both CTAs' accumulators complete
+        }
+    } else {
+        // ---- this pair's partial: TMEM → workspace, in the order it comes (lane = row, 32 columns per load) ----
+        bool have = false;
+        if (nkb > 0) {
+            if (mbar_wait(tfull_bar, 0, abort_flag)) {
+                tc_fence_after();
+                have = true;
+            } else if (lane == 0 && !*abort_flag) {
+                *abort_flag = 1;
+                atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL);
+            }
+        }
+        const int q = warp & 3;
+        float4 *mine = reinterpret_cast<float4 *>(p.partial + ((size_t(tile) * p.ks + slice) * 2 + half) * WS_HALF_FLOATS);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            if (have) {
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + c0, r);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) r[j] = 0u;
+            }
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+                mine[((q * 8 + (c0 >> 5)) * 8 + v) * 32 + lane] =
+                    make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+        }
+        __threadfence();  // the partial is visible device-wide before this CTA counts itself in
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int old = atomicAdd(p.counters + tile * 2 + half, 1u);
+        *last_flag = (old == unsigned(p.ks - 1)) ? 1 : 0;
+        __threadfence();
+    }
+    __syncthreads();
+    if (*last_flag && warp >= 2) {
+        // ---- the last of the KS pairs to arrive finishes its 128 rows: partials in slice order, round once, write C ----
+        const int q = warp & 3;
+        const uint32_t stage_smem = smem_base + (warp - 2) * EPI_WARP_BYTES;  // the ring is drained: reuse it for turning the blocks
+        const float4 *base = reinterpret_cast<const float4 *>(p.partial + (size_t(tile) * p.ks * 2 + half) * WS_HALF_FLOATS);
+        const size_t slice_stride = size_t(2) * WS_HALF_FLOATS / 4;  // float4s between consecutive slices of this half
+        const int row0 = tm * PBM + int(half) * BM + q * 32;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += EPI_COLS) {
+            uint32_t r[2][32];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                    const size_t at = size_t(((q * 8 + ((c0 >> 5) + h)) * 8 + v) * 32 + lane);
+                    float4 acc = __ldcg(base + at);
+                    for (int sl = 1; sl < p.ks; ++sl) {
+                        const float4 t = __ldcg(base + sl * slice_stride + at);
+                        acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
+                    }
+                    r[h][4 * v + 0] = __float_as_uint(acc.x);
+                    r[h][4 * v + 1] = __float_as_uint(acc.y);
+                    r[h][4 * v + 2] = __float_as_uint(acc.z);
+                    r[h][4 * v + 3] = __float_as_uint(acc.w);
+                }
+            emit_block<T>(r, C, p.c_staged != 0, stage_smem, p.M, p.N, b, row0, tn * BN + c0, lane);
+        }
+    }
+    __syncthreads();
+    if (*last_flag && threadIdx.x == 0) p.counters[tile * 2 + half] = 0;  // ready for the next launch on this stream
     // the pair frees its TMEM together
     tc_fence_before();
     __syncthreads();
@@ -2002,6 +2208,118 @@ int launch_pair_splitk(const T *A, const T *B, T *C, int64_t batch, int64_t M, i
     return check_launch("matmul(tcgen05 pair split-K)");
 }
 
+// A few rows of 256 x 256 tiles, K split over independent pairs through the caller's workspace.
+// plan: how many K slices (0 = not a shape for it) and the workspace that needs.
+template <typename T> int pair_wsk_slots(int dev) {
+    static int known[64][2] = {};  // 0 unknown, else clusters + 1
+    const int ti = std::is_same<T, bf16>::value ? 0 : 1;
+    std::lock_guard<std::mutex> lk(g_setup_mu);
+    if (known[dev][ti] == 0) {
+        int n = 0;
+        if (cudaFuncSetAttribute(gemm_tcgen05_pair_wsk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(2 * sm_count()), 1, 1);
+            cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+            cfg.dynamicSmemBytes = PS_SMEM_BYTES;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_wsk_kernel<T>, &cfg) != cudaSuccess) n = 0;
+        }
+        if (n <= 0) { n = 0; cudaGetLastError(); }
+        known[dev][ti] = n + 1;
+    }
+    return known[dev][ti] - 1;
+}
+
+// K slices for a shape (0: the other kernels do it), given how many pairs run at once.
+int wsk_slices(int64_t batch, int64_t M, int64_t N, int64_t K, int slots) {
+    static const int forced = [] {  // DX_GEMM_WSK=0 turns the path off, 2..8 forces that many slices where they fit
+        const char *e = std::getenv("DX_GEMM_WSK");
+        return e ? std::atoi(e) : -1;
+    }();
+    if (forced == 0 || slots <= 0 || M <= BM) return 0;
+    const int64_t tiles = ((M + PBM - 1) / PBM) * ((N + BN - 1) / BN) * batch;
+    const int64_t k_blocks = (K + BK - 1) / BK;
+    if (tiles * 2 > slots || tiles * 2 > 512) return 0;  // enough tiles for the persistent kernels (or more than there are counters)
+    int64_t ks = std::min<int64_t>(std::min<int64_t>(8, slots / tiles), k_blocks / 4);
+    if (forced >= 2) ks = std::min<int64_t>(forced, std::min<int64_t>(slots / tiles, k_blocks));
+    while (ks >= 2 && (ks - 1) * ((k_blocks + ks - 1) / ks) >= k_blocks) --ks;  // no slice without a K block
+    if (ks < 2) return 0;
+    // what splitting saves in main-loop time has to outweigh writing, re-reading and adding the partials (~3 µs)
+    if (forced < 2 && k_blocks * (ks - 1) / ks < 10) return 0;
+    return int(ks);
+}
+
+template <typename T>
+int launch_pair_wsk(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64_t N, int64_t K, void *ws, size_t ws_bytes, cudaStream_t st) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) return fail(DX_E_CUDA, "matmul: device index %d out of range", dev);
+    const int ks = wsk_slices(batch, M, N, K, pair_wsk_slots<T>(dev));
+    if (!ks) return DX_E_UNSUPPORTED;
+    const int64_t tiles_m = (M + PBM - 1) / PBM, tiles_n = (N + BN - 1) / BN;
+    const int64_t tiles = tiles_m * tiles_n * batch;
+    const size_t need = size_t(tiles) * ks * 2 * WS_HALF_FLOATS * sizeof(float);
+    if (!ws || ws_bytes < need || !aligned_to(ws, 16)) return DX_E_UNSUPPORTED;  // the caller gave no (or too little) workspace: the other kernels
+    int *status;
+    unsigned int *counters;
+    {
+        std::lock_guard<std::mutex> lk(g_setup_mu);
+        if (!g_status_ptr[dev]) {
+            void *sym = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&sym, g_gemm_status);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            g_status_ptr[dev] = static_cast<int *>(sym);
+        }
+        status = g_status_ptr[dev];
+        static unsigned int *counter_ptr[64] = {};
+        if (!counter_ptr[dev]) {
+            void *sym = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&sym, g_wsk_counters);
+            if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            counter_ptr[dev] = static_cast<unsigned int *>(sym);
+        }
+        counters = counter_ptr[dev];
+    }
+    const CUtensorMapDataType dt = std::is_same<T, bf16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap ma, mb;
+    if (int e = make_map(&ma, dt, A, (uint64_t)K, (uint64_t)M, (uint64_t)batch, BK, BM)) return e;
+    if (int e = make_map(&mb, dt, B, (uint64_t)N, (uint64_t)K, (uint64_t)batch, B_BOX_N, BK)) return e;
+    static const bool staged_on = [] { const char *e = std::getenv("DX_GEMM_STAGED_STORE"); return !(e && e[0] == '0'); }();
+    const int64_t k_blocks = (K + BK - 1) / BK;
+    PairWsParams p;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K; p.batch = (int)batch;
+    p.tiles_m = (int)tiles_m;
+    p.tiles_n = (int)tiles_n;
+    p.k_blocks = (int)k_blocks;
+    p.ks = ks;
+    p.kb_per_slice = (int)((k_blocks + ks - 1) / ks);
+    p.c_staged = (staged_on && aligned_to(C, 16)) ? 1 : 0;
+    p.status = status;
+    p.partial = static_cast<float *>(ws);
+    p.counters = counters;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(tiles * ks * 2), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = PS_SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_wsk_kernel<T>, ma, mb, C, p);
+    if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 pair, K split through the workspace): %s", cudaGetErrorString(e));
+    return check_launch("matmul(tcgen05 pair, K split through the workspace)");
+}
+
 // float32 through the tensor cores (three TF32 products per product).
 bool g_tf32_attr[64] = {};
 int g_tf32_pair_slots[64] = {};
@@ -2132,8 +2450,24 @@ extern "C" int dx_matmul_status(void *stream) {
     return DX_OK;
 }
 
+extern "C" size_t dx_matmul_workspace_bytes(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K) {
+    if ((dtype != DX_BF16 && dtype != DX_F16) || batch <= 0 || M <= 0 || N <= 0 || K <= 0 || (K % 8) || (N % 8)) return 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 0; }
+    const int slots = dtype == DX_BF16 ? pair_wsk_slots<bf16>(dev) : pair_wsk_slots<f16>(dev);
+    const int ks = wsk_slices(batch, M, N, K, slots);
+    if (!ks) return 0;
+    const int64_t tiles = ((M + PBM - 1) / PBM) * ((N + BN - 1) / BN) * batch;
+    return size_t(tiles) * ks * 2 * WS_HALF_FLOATS * sizeof(float);
+}
+
 extern "C" int dx_matmul(int dtype, const void *A, const void *B, void *C, int64_t batch, int64_t M, int64_t N, int64_t K,
                          void *stream) {
+    return dx_matmul_ws(dtype, A, B, C, batch, M, N, K, nullptr, 0, stream);
+}
+
+extern "C" int dx_matmul_ws(int dtype, const void *A, const void *B, void *C, int64_t batch, int64_t M, int64_t N, int64_t K,
+                            void *workspace, size_t workspace_bytes, void *stream) {
     cudaStream_t st = as_stream(stream);
     if (batch < 0 || M < 0 || N < 0 || K < 0) return fail(DX_E_SHAPE, "matmul: negative extent");
     if (batch == 0 || M == 0 || N == 0) return DX_OK;
@@ -2162,6 +2496,11 @@ extern "C" int dx_matmul(int dtype, const void *A, const void *B, void *C, int64
                                                     : launch_splitk<f16>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, st);
                     if (rc != DX_E_UNSUPPORTED) return rc;
                 }
+            }
+            if (tma_ok && M > BM && workspace) {
+                const int rc = dtype == DX_BF16 ? launch_pair_wsk<bf16>((const bf16 *)A, (const bf16 *)B, (bf16 *)C, batch, M, N, K, workspace, workspace_bytes, st)
+                                                : launch_pair_wsk<f16>((const f16 *)A, (const f16 *)B, (f16 *)C, batch, M, N, K, workspace, workspace_bytes, st);
+                if (rc != DX_E_UNSUPPORTED) return rc;
             }
             if (tma_ok && M > BM) {
                 const char *psplit_env = std::getenv("DX_GEMM_PAIR_SPLITK");

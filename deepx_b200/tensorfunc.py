@@ -391,6 +391,9 @@ def check_matmul_shape(a: Sequence[int], b: Sequence[int]) -> bool:
     return all(a[i] == b[i] for i in range(len(a) - 2))
 
 
+_matmul_workspace: dict[torch.device, torch.Tensor] = {}
+
+
 def matmul(A: torch.Tensor, B: torch.Tensor, Cc: torch.Tensor) -> None:
     _dev(A, B, Cc)
     _same_dtype(A, B, Cc)
@@ -401,4 +404,13 @@ def matmul(A: torch.Tensor, B: torch.Tensor, Cc: torch.Tensor) -> None:
     if list(Cc.shape) != list(A.shape[:-1]) + [Nn]:
         raise ValueError("shape mismatch")
     with torch.cuda.device(A.device):
-        N.check(N.lib.dx_matmul(dtype_code(A), A.data_ptr(), B.data_ptr(), Cc.data_ptr(), batch, M, Nn, K, _stream(A)))
+        code = dtype_code(A)
+        need = N.lib.dx_matmul_workspace_bytes(code, batch, M, Nn, K)  # > 0 for a few rows of tiles: K split through scratch memory
+        if need:
+            ws = _matmul_workspace.get(A.device)
+            if ws is None or ws.numel() < need:
+                ws = torch.empty(builtins.max(int(need), 32 << 20), dtype=torch.uint8, device=A.device)
+                _matmul_workspace[A.device] = ws
+            N.check(N.lib.dx_matmul_ws(code, A.data_ptr(), B.data_ptr(), Cc.data_ptr(), batch, M, Nn, K, ws.data_ptr(), ws.numel(), _stream(A)))
+        else:
+            N.check(N.lib.dx_matmul(code, A.data_ptr(), B.data_ptr(), Cc.data_ptr(), batch, M, Nn, K, _stream(A)))

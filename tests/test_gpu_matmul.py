@@ -391,3 +391,39 @@ def test_config_matmul_bf16_8192x4096x4096(mods):
     rhs = a.astype(np.float64) @ b.astype(np.float64).sum(axis=1)
     # each of the 4096 outputs in a row carries ≤ 2^-9 relative rounding of |c|
     assert (np.abs(lhs - rhs) <= 2.0 ** -8 * np.abs(got).sum(axis=1) + 1e-9).all()
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
+@pytest.mark.parametrize("shape", [
+    (1, 512, 4096, 4096), (1, 256, 4096, 4096), (1, 768, 2048, 8192), (1, 1024, 1024, 1024),   # the few-rows-of-tiles shapes
+    (1, 300, 520, 1096), (1, 257, 264, 1024), (3, 260, 264, 640), (1, 129, 8, 2048),            # ragged rows, columns, last K slice; batch
+])
+def test_matmul_16bit_k_split_through_workspace(mods, shape, dtype):
+    """A few rows of 256 x 256 tiles: dx_matmul_ws splits each tile's K range over independent CTA pairs whose fp32
+    partials meet in the caller's workspace and are added in slice order by the pair that arrives last.  Against the
+    float64 product; the same bits on every run (the arrival order must not show); the same answer from dx_matmul,
+    which has no workspace, within the bound; and the arrival counters are back at zero for the next call."""
+    TF, O, N = mods
+    batch, M, Nn, K = shape
+    code = {"bfloat16": N.BF16, "float16": N.F16}[dtype]
+    need = int(N.lib.dx_matmul_workspace_bytes(code, batch, M, Nn, K))
+    assert need > 0, "this shape is meant to take the workspace path on this device"
+    rng = np.random.default_rng(seed_of("mmws", shape, dtype))
+    a = make(rng, dtype, (batch, M, K) if batch > 1 else (M, K), -1.0, 1.0)
+    b = make(rng, dtype, (batch, K, Nn) if batch > 1 else (K, Nn), -1.0, 1.0)
+    first = check(TF, N, a, b, dtype, f"matmul<{dtype}> {shape} (workspace)")       # tensorfunc.matmul passes a workspace
+    again = check(TF, N, a, b, dtype, f"matmul<{dtype}> {shape} (workspace, second call)")
+    assert np.array_equal(first, again), "two runs of the K-split kernel differ: the order of arrival shows in the result"
+    A, B = to_gpu(a), to_gpu(b)
+    plain = torch.empty(first.shape, dtype=TORCH_DTYPES[dtype], device="cuda:0")
+    N.check(N.lib.dx_matmul(code, A.data_ptr(), B.data_ptr(), plain.data_ptr(), batch, M, Nn, K, None))   # no workspace: the other kernels
+    small = torch.empty(1024, dtype=torch.uint8, device="cuda:0")
+    short = torch.empty_like(plain)
+    N.check(N.lib.dx_matmul_ws(code, A.data_ptr(), B.data_ptr(), short.data_ptr(), batch, M, Nn, K, small.data_ptr(), small.numel(), None))
+    N.check(N.lib.dx_matmul_status(None))
+    assert torch.equal(plain, short), "too small a workspace must fall back to what dx_matmul does"
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    scale = np.abs(a.astype(np.float64)) @ np.abs(b.astype(np.float64))
+    assert (np.abs(to_np(plain).astype(np.float64) - ref) <= TOL[dtype] * np.abs(ref) + 1e-6 * scale + 1e-300).all()
+    # an unrelated shape that takes the persistent kernels still works afterwards
+    check(TF, N, make(rng, dtype, (384, 512), -1.0, 1.0), make(rng, dtype, (512, 2048), -1.0, 1.0), dtype, "after the K-split kernel")
