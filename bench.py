@@ -65,6 +65,26 @@ def download_into(ex, name: str, out) -> None:
         raise RuntimeError(E.lib().dx_exec_last_error().decode())
 
 
+def host_l3_note(working_set_bytes: int) -> str:
+    """The sample's working set beside the host's last-level cache (a sample that fits it flatters the CPU)."""
+    try:
+        base = Path("/sys/devices/system/cpu")
+        seen, total = set(), 0
+        for idx in base.glob("cpu[0-9]*/cache/index3"):
+            shared = (idx / "shared_cpu_list").read_text().strip()
+            if shared in seen:
+                continue
+            seen.add(shared)
+            txt = (idx / "size").read_text().strip()
+            total += int(txt[:-1]) * (1 << 10 if txt.endswith("K") else 1 << 20) if txt[-1] in "KM" else int(txt)
+        if total:
+            return (f"working set {working_set_bytes / 2**20:.0f} MiB (x, y, t, z of the sample) against {total / 2**20:.0f} MiB of L3 "
+                    f"in {len(seen)} slice(s): {'larger than' if working_set_bytes > total else 'WITHIN'} the cache")
+    except Exception:
+        pass
+    return f"working set {working_set_bytes / 2**20:.0f} MiB; host L3 size not readable"
+
+
 def measured_peaks() -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -158,7 +178,7 @@ def run_reference(args) -> None:
         step()
     dt = (time.perf_counter() - t0) / args.steps
     gbs = chain_bytes(rows) / dt / 1e9
-    sample = f"{rows} of {ROWS} rows of the same chain per step (f32 [{rows},{COLS}])"
+    sample = f"{rows} of {ROWS} rows of the same chain per step (f32 [{rows},{COLS}]); " + host_l3_note(4 * rows * COLS * 4)
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong",
@@ -237,7 +257,7 @@ def cpu_baseline_leg() -> dict:
         n += 1
     dt = (time.perf_counter() - t0) / n
     return {"value": round(chain_bytes(rows) / dt / 1e9, 3), "unit": UNIT, "cores": O.num_threads(), "kind": "port",
-            "sample": f"{n} passes over {rows} of {ROWS} rows of the same chain (f32 [{rows},{COLS}])"}
+            "sample": f"{n} passes over {rows} of {ROWS} rows of the same chain (f32 [{rows},{COLS}]); " + host_l3_note(4 * rows * COLS * 4)}
 
 
 def cpu_ops_table(budget_s: float = 25.0) -> dict:

@@ -1241,22 +1241,31 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         const int row0 = tm * PBM + int(half) * BM + q * 32;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += EPI_COLS) {
+            // 16 float4 per slice and thread, all loads of a slice issued before the first add: the partials come out
+            // of L2 (written by other SMs), and a chain of dependent loads would cost their latency sixteen times over
+            float4 acc[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+                acc[i] = __ldcg(base + size_t(((q * 8 + ((c0 >> 5) + (i >> 3))) * 8 + (i & 7)) * 32 + lane));
+#pragma unroll 1
+            for (int sl = 1; sl < p.ks; ++sl) {
+                float4 t[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i)
+                    t[i] = __ldcg(base + sl * slice_stride + size_t(((q * 8 + ((c0 >> 5) + (i >> 3))) * 8 + (i & 7)) * 32 + lane));
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    acc[i].x += t[i].x; acc[i].y += t[i].y; acc[i].z += t[i].z; acc[i].w += t[i].w;
+                }
+            }
             uint32_t r[2][32];
 #pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                    const size_t at = size_t(((q * 8 + ((c0 >> 5) + h)) * 8 + v) * 32 + lane);
-                    float4 acc = __ldcg(base + at);
-                    for (int sl = 1; sl < p.ks; ++sl) {
-                        const float4 t = __ldcg(base + sl * slice_stride + at);
-                        acc.x += t.x; acc.y += t.y; acc.z += t.z; acc.w += t.w;
-                    }
-                    r[h][4 * v + 0] = __float_as_uint(acc.x);
-                    r[h][4 * v + 1] = __float_as_uint(acc.y);
-                    r[h][4 * v + 2] = __float_as_uint(acc.z);
-                    r[h][4 * v + 3] = __float_as_uint(acc.w);
-                }
+            for (int i = 0; i < 16; ++i) {
+                r[i >> 3][4 * (i & 7) + 0] = __float_as_uint(acc[i].x);
+                r[i >> 3][4 * (i & 7) + 1] = __float_as_uint(acc[i].y);
+                r[i >> 3][4 * (i & 7) + 2] = __float_as_uint(acc[i].z);
+                r[i >> 3][4 * (i & 7) + 3] = __float_as_uint(acc[i].w);
+            }
             emit_block<T>(r, C, p.c_staged != 0, stage_smem, p.M, p.N, b, row0, tn * BN + c0, lane);
         }
     }
@@ -2250,8 +2259,11 @@ int wsk_slices(int64_t batch, int64_t M, int64_t N, int64_t K, int slots) {
     if (forced >= 2) ks = std::min<int64_t>(forced, std::min<int64_t>(slots / tiles, k_blocks));
     while (ks >= 2 && (ks - 1) * ((k_blocks + ks - 1) / ks) >= k_blocks) --ks;  // no slice without a K block
     if (ks < 2) return 0;
-    // what splitting saves in main-loop time has to outweigh writing, re-reading and adding the partials (~3 µs)
-    if (forced < 2 && k_blocks * (ks - 1) / ks < 10) return 0;
+    // What splitting saves in main-loop time has to outweigh what the partials cost: writing them, the fence and the
+    // count-in, and the finishing pair reading ks x 128 KiB out of L2 and adding — measured at 10–12 µs, i.e. some 35 K
+    // blocks of main loop (1024^3: 8.7 -> 16.4 µs and 512 x 4096 x 4096: 23.9 -> 24.9 µs with the split, but
+    // 768 x 2048 x 8192: 33.6 -> 28.8 µs).  So only long K ranges are split.
+    if (forced < 2 && k_blocks * (ks - 1) / ks < 40) return 0;
     return int(ks);
 }
 

@@ -395,8 +395,8 @@ def test_config_matmul_bf16_8192x4096x4096(mods):
 
 @pytest.mark.parametrize("dtype", ["bfloat16", "float16"])
 @pytest.mark.parametrize("shape", [
-    (1, 512, 4096, 4096), (1, 256, 4096, 4096), (1, 768, 2048, 8192), (1, 1024, 1024, 1024),   # the few-rows-of-tiles shapes
-    (1, 300, 520, 1096), (1, 257, 264, 1024), (3, 260, 264, 640), (1, 129, 8, 2048),            # ragged rows, columns, last K slice; batch
+    (1, 768, 2048, 8192), (1, 512, 4096, 8192), (1, 256, 1024, 16384),                           # few rows of tiles, long K
+    (1, 300, 520, 8008), (1, 257, 264, 4096), (3, 260, 264, 4096), (1, 129, 8, 4096),            # ragged rows, columns, last K slice; batch
 ])
 def test_matmul_16bit_k_split_through_workspace(mods, shape, dtype):
     """A few rows of 256 x 256 tiles: dx_matmul_ws splits each tile's K range over independent CTA pairs whose fp32
