@@ -29,6 +29,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <vector>
 
 #include "common.cuh"
 
@@ -121,6 +122,15 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -1076,25 +1086,82 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 // ---- a few rows of tiles, K split over INDEPENDENT pairs through a workspace ----------------------------
 // The cluster form above pays two cluster barriers, a late start (clusters of 4–8 CTAs must find room in one GPC)
 // and the exchange of partials, about 8 µs, so it only helps when K is long.  Here every (tile, K slice) is an
-// ordinary CTA pair of its own: the pair runs the cta_group::2 main loop over its slice, writes its fp32 partial
-// to the caller's workspace in the order the values come out of TMEM (every store instruction of a warp covers 512
-// contiguous bytes), and counts itself in on a per-(tile, half) counter.  The CTA that arrives LAST adds the KS
-// partials of its 128 rows in slice order — whoever finishes, the sum has the same order, so the same bits — rounds
-// once and writes C through the block-turning epilogue, then puts the counter back to zero.  No CTA waits for
-// another, no atomics on data.  Workspace: tiles × KS × 256 × 256 floats.
+// ordinary CTA pair of its own, launched cooperatively so that all of them are resident: the pair runs the
+// cta_group::2 main loop over its slice, and then the KS pairs of a tile share out the finishing — pair s finishes
+// the s-th share of the tile's 32-column blocks.  A CTA writes the blocks that OTHER pairs finish to the caller's
+// workspace in the order the values come out of TMEM (every store instruction of a warp covers 512 contiguous
+// bytes), counts itself in on a per-(tile, half) counter, waits (bounded) until all KS have, then adds, for its
+// own blocks, the partials in slice order — its own straight from TMEM, the others out of L2 — rounds once and
+// writes C.  What bounds this phase is what one SM can push into and pull out of L2 (about 32 and 64 bytes per
+// clock, measured); sharing it out means a CTA moves (KS-1)/KS of a 128 KiB partial each way instead of one CTA
+// pulling KS-1 whole partials.  The sum has the same order whoever runs first, so the same bits.  No atomics on
+// data.  Workspace: tiles × KS × 256 × 256 floats.
 struct PairWsParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, k_blocks, kb_per_slice, ks;
     int c_staged;
     int *status;
     float *partial;          // [tile][slice][half][128 rows × 256 columns in TMEM order]
-    unsigned int *counters;  // [tile][half], zero between launches
+    unsigned long long *counters;  // [tile][half]: grows by WSK_ROUND per launch
 };
+constexpr int W_THREADS = 256;          // eight warps; warps 0 and 1 feed the main loop first, then all eight store and finish
 constexpr int WS_HALF_FLOATS = BM * BN;  // 32768 floats = 128 KiB per CTA and slice
-__device__ unsigned int g_wsk_counters[512];
+constexpr int GEMM_TIMEOUT_SLICES = 7;
+constexpr unsigned int WSK_ROUND = 840;  // divisible by every KS up to 8
+constexpr int WSK_BANKS = 8;             // one set of counters per stream that launches this kernel
+__device__ unsigned long long g_wsk_counters[WSK_BANKS][512];
+
+__device__ __forceinline__ unsigned long long ld_acquire_gpu(const unsigned long long *p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void red_release_add(unsigned long long *p, unsigned long long v) {
+    asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// A warp's block of 32 rows × 32 columns, one row per lane in r[32] as fp32 bit patterns, rounded once and written
+// to C: turned round in 2 KiB of shared memory (rows of 64 bytes, their 16-byte chunks XOR-swizzled by half the row
+// number: no bank conflicts either way) and stored with four lanes per row when `staged`, else row by row.
+template <typename T>
+__device__ __forceinline__ void emit_chunk32(const uint32_t (&r)[32], T *C, bool staged, uint32_t stage_smem, int M, int N, int b, int row0,
+                                             int col, int lane) {
+    if (row0 >= M || col >= N) return;
+    if (staged) {
+        const uint32_t mine = stage_smem + lane * 64;
+        const int sw = (lane >> 1) & 3;
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+            st_shared_v4(mine + ((v ^ sw) << 4),
+                         pack2<T>(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1])),
+                         pack2<T>(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3])),
+                         pack2<T>(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5])),
+                         pack2<T>(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7])));
+        __syncwarp();
+        const int chunk = lane & 3;
+        const int gcol = col + chunk * 8;
+        uint4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rr = i * 8 + (lane >> 2);
+            v[i] = ld_shared_v4(stage_smem + rr * 64 + ((chunk ^ ((rr >> 1) & 3)) << 4));
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int rr = i * 8 + (lane >> 2);
+            if (row0 + rr < M && gcol < N) *reinterpret_cast<uint4 *>(C + (size_t(b) * M + row0 + rr) * N + gcol) = v[i];
+        }
+        __syncwarp();
+    } else if (row0 + lane < M) {
+        T *crow = C + (size_t(b) * M + row0 + lane) * N;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (col + j < N) crow[col + j] = from_compute<T>(__uint_as_float(r[j]));
+    }
+}
 
 template <typename T>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(W_THREADS, 1)
     gemm_tcgen05_pair_wsk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                                  T *__restrict__ C, PairWsParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -1109,7 +1176,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     const uint32_t tmem_slot = bars + SLOT_OFF;
     volatile uint32_t *tmem_slot_ptr = reinterpret_cast<volatile uint32_t *>(gen_base + BAR_OFF + SLOT_OFF);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(gen_base + BAR_OFF + SLOT_OFF + 8);
-    volatile int *last_flag = reinterpret_cast<volatile int *>(gen_base + BAR_OFF + SLOT_OFF + 12);
+    volatile int *go_flag = reinterpret_cast<volatile int *>(gen_base + BAR_OFF + SLOT_OFF + 12);
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t half = cluster_ctarank();  // which 128 rows of the pair tile; rank 0 issues the MMAs
@@ -1131,7 +1198,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
         }
         mbar_init(tfull_bar, 1);
         *abort_flag = 0;
-        *last_flag = 0;
+        *go_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
@@ -1142,6 +1209,13 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
     cluster_sync_all();  // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
+    // The counter of this (tile, half) only ever grows, by WSK_ROUND per launch whatever KS is.  Read before this
+    // CTA has counted itself in, it lies in [base, base + WSK_ROUND) with base the value the last launch left, so the
+    // value to wait for is known now and the count-in itself needs no answer from L2.
+    unsigned long long *arrived = p.counters + tile * 2 + half;
+    unsigned long long target = 0;
+    if (threadIdx.x == 0) target = (ld_acquire_gpu(arrived) / WSK_ROUND + 1ull) * WSK_ROUND;
+    bool have = false;  // this CTA's accumulator is complete
 
     if (warp == 0) {
         if (lane == 0) {
@@ -1193,25 +1267,32 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
             if (ok) umma_commit_pair(tfull_bar, 0x3);  // both CTAs' accumulators complete
         }
-    } else {
-        // ---- this pair's partial: TMEM → workspace, in the order it comes (lane = row, 32 columns per load) ----
-        bool have = false;
-        if (nkb > 0) {
-            if (mbar_wait(tfull_bar, 0, abort_flag)) {
-                tc_fence_after();
-                have = true;
-            } else if (lane == 0 && !*abort_flag) {
-                *abort_flag = 1;
-                atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL);
-            }
+    }
+    __syncwarp();  // lane 0 of warps 0 and 1 is back from its loop: all eight warps take part from here on
+    if (nkb > 0) {
+        if (mbar_wait(tfull_bar, 0, abort_flag)) {
+            tc_fence_after();
+            have = true;
+        } else if (lane == 0 && !*abort_flag) {
+            *abort_flag = 1;
+            atomicExch(p.status, GEMM_TIMEOUT_TMEM_FULL);
         }
-        const int q = warp & 3;
+    }
+    // two warps per TMEM lane quarter; they take the 32-column blocks of a list in turn
+    const int q = warp & 3, wh = warp >> 2;
+    const uint32_t tmem_row = tmem_base + (uint32_t(q * 32) << 16);
+    const int my_c0 = (8 * slice) / p.ks, my_c1 = (8 * (slice + 1)) / p.ks;  // the blocks this pair finishes (KS <= 8: at least one)
+    {
+        // ---- the blocks other pairs finish: TMEM → this slice's place in the workspace ----
         float4 *mine = reinterpret_cast<float4 *>(p.partial + ((size_t(tile) * p.ks + slice) * 2 + half) * WS_HALF_FLOATS);
+        int n = 0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 32) {
+        for (int c = 0; c < 8; ++c) {
+            if (c >= my_c0 && c < my_c1) continue;
+            if ((n++ & 1) != wh) continue;
             uint32_t r[32];
             if (have) {
-                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + c0, r);
+                tmem_ld_32x32b_x32(tmem_row + c * 32, r);
                 tmem_ld_wait();
             } else {
 #pragma unroll
@@ -1219,58 +1300,106 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
             }
 #pragma unroll
             for (int v = 0; v < 8; ++v)
-                mine[((q * 8 + (c0 >> 5)) * 8 + v) * 32 + lane] =
+                mine[((q * 8 + c) * 8 + v) * 32 + lane] =
                     make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
         }
-        __threadfence();  // the partial is visible device-wide before this CTA counts itself in
     }
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned int old = atomicAdd(p.counters + tile * 2 + half, 1u);
-        *last_flag = (old == unsigned(p.ks - 1)) ? 1 : 0;
-        __threadfence();
+        // The barrier orders every warp's stores before this release, and a release is cumulative: they are visible
+        // device-wide before the count.  All KS pairs of the tile are resident (a cooperative launch) and none waits
+        // before it has counted itself in, so the wait ends; it is bounded all the same.
+        red_release_add(arrived, WSK_ROUND / unsigned(p.ks));
+        const long long t0 = clock64();
+        bool ok = true;
+        while (ld_acquire_gpu(arrived) < target) {
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) { ok = false; break; }
+        }
+        if (!ok) atomicExch(p.status, GEMM_TIMEOUT_SLICES);
+        *go_flag = ok ? 1 : 0;
     }
     __syncthreads();
-    if (*last_flag && warp >= 2) {
-        // ---- the last of the KS pairs to arrive finishes its 128 rows: partials in slice order, round once, write C ----
-        const int q = warp & 3;
-        const uint32_t stage_smem = smem_base + (warp - 2) * EPI_WARP_BYTES;  // the ring is drained: reuse it for turning the blocks
+    if (*go_flag) {
+        // ---- this pair's own blocks: partials in slice order, rounded once, written to C ----
+        tc_fence_after();
+        const uint32_t stage_smem = smem_base + warp * EPI_WARP_BYTES;  // the ring is drained: reuse it for turning the blocks
         const float4 *base = reinterpret_cast<const float4 *>(p.partial + (size_t(tile) * p.ks * 2 + half) * WS_HALF_FLOATS);
         const size_t slice_stride = size_t(2) * WS_HALF_FLOATS / 4;  // float4s between consecutive slices of this half
         const int row0 = tm * PBM + int(half) * BM + q * 32;
+        // A batch = the 8 float4 a thread needs of one of its blocks from one other slice.  Up to four batches are
+        // requested before the first is added, so the trip to L2 (some 2000 cycles with every SM storing and loading
+        // at once) is paid once per four, not once each; the adding keeps slice order, this pair's own slice coming
+        // straight from TMEM at its place in that order.
+        const int others = p.ks - 1;
+        const int my_blocks = (my_c1 - my_c0 - wh + 1) >> 1;  // blocks my_c0 + wh, + 2, ...
+        const int batches = my_blocks * others;
+        constexpr int NB = 4;
+        float4 acc[8];
+        bool started = false, own_done = false;
+        auto fold = [&](const float4(&x)[8]) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                if (!started) acc[v] = x[v];
+                else { acc[v].x += x[v].x; acc[v].y += x[v].y; acc[v].z += x[v].z; acc[v].w += x[v].w; }
+            }
+            started = true;
+        };
+        auto fold_own = [&](int c) {
+            uint32_t u[32];
+            if (have) {
+                tmem_ld_32x32b_x32(tmem_row + c * 32, u);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) u[j] = 0u;
+            }
+            float4 x[8];
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+                x[v] = make_float4(__uint_as_float(u[4 * v + 0]), __uint_as_float(u[4 * v + 1]), __uint_as_float(u[4 * v + 2]), __uint_as_float(u[4 * v + 3]));
+            fold(x);
+            own_done = true;
+        };
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += EPI_COLS) {
-            // 16 float4 per slice and thread, all loads of a slice issued before the first add: the partials come out
-            // of L2 (written by other SMs), and a chain of dependent loads would cost their latency sixteen times over
-            float4 acc[16];
+        for (int j0 = 0; j0 < batches; j0 += NB) {
+            float4 t[NB][8];
 #pragma unroll
-            for (int i = 0; i < 16; ++i)
-                acc[i] = __ldcg(base + size_t(((q * 8 + ((c0 >> 5) + (i >> 3))) * 8 + (i & 7)) * 32 + lane));
-#pragma unroll 1
-            for (int sl = 1; sl < p.ks; ++sl) {
-                float4 t[16];
+            for (int s = 0; s < NB; ++s) {
+                const int j = j0 + s;
+                if (j < batches) {
+                    const int bi = j / others, oi = j - bi * others;
+                    const int sl = oi + (oi >= slice ? 1 : 0), c = my_c0 + wh + 2 * bi;
+                    const float4 *src = base + sl * slice_stride + size_t(((q * 8 + c) * 8) * 32 + lane);
 #pragma unroll
-                for (int i = 0; i < 16; ++i)
-                    t[i] = __ldcg(base + sl * slice_stride + size_t(((q * 8 + ((c0 >> 5) + (i >> 3))) * 8 + (i & 7)) * 32 + lane));
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    acc[i].x += t[i].x; acc[i].y += t[i].y; acc[i].z += t[i].z; acc[i].w += t[i].w;
+                    for (int v = 0; v < 8; ++v) t[s][v] = __ldcg(src + v * 32);
                 }
             }
-            uint32_t r[2][32];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                r[i >> 3][4 * (i & 7) + 0] = __float_as_uint(acc[i].x);
-                r[i >> 3][4 * (i & 7) + 1] = __float_as_uint(acc[i].y);
-                r[i >> 3][4 * (i & 7) + 2] = __float_as_uint(acc[i].z);
-                r[i >> 3][4 * (i & 7) + 3] = __float_as_uint(acc[i].w);
+            for (int s = 0; s < NB; ++s) {
+                const int j = j0 + s;
+                if (j < batches) {
+                    const int bi = j / others, oi = j - bi * others;
+                    const int sl = oi + (oi >= slice ? 1 : 0), c = my_c0 + wh + 2 * bi;
+                    if (oi == 0) { started = false; own_done = false; }
+                    if (!own_done && slice < sl) fold_own(c);
+                    fold(t[s]);
+                    if (oi == others - 1) {
+                        if (!own_done) fold_own(c);
+                        uint32_t r[32];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            r[4 * i + 0] = __float_as_uint(acc[i].x);
+                            r[4 * i + 1] = __float_as_uint(acc[i].y);
+                            r[4 * i + 2] = __float_as_uint(acc[i].z);
+                            r[4 * i + 3] = __float_as_uint(acc[i].w);
+                        }
+                        emit_chunk32<T>(r, C, p.c_staged != 0, stage_smem, p.M, p.N, b, row0, tn * BN + c * 32, lane);
+                    }
+                }
             }
-            emit_block<T>(r, C, p.c_staged != 0, stage_smem, p.M, p.N, b, row0, tn * BN + c0, lane);
         }
     }
-    __syncthreads();
-    if (*last_flag && threadIdx.x == 0) p.counters[tile * 2 + half] = 0;  // ready for the next launch on this stream
     // the pair frees its TMEM together
     tc_fence_before();
     __syncthreads();
@@ -2219,6 +2348,18 @@ int launch_pair_splitk(const T *A, const T *B, T *C, int64_t batch, int64_t M, i
 
 // A few rows of 256 x 256 tiles, K split over independent pairs through the caller's workspace.
 // plan: how many K slices (0 = not a shape for it) and the workspace that needs.
+unsigned long long *g_wsk_counter_ptr[64] = {};
+// Launches of this kernel on different streams may overlap, and each needs counters of its own: a stream gets a bank
+// the first time it launches the kernel and keeps it.  -1: all banks belong to other streams (the other kernels run).
+std::vector<cudaStream_t> g_wsk_bank_streams[64];
+int wsk_bank(int dev, cudaStream_t st) {  // caller holds g_setup_mu
+    auto &v = g_wsk_bank_streams[dev];
+    for (size_t i = 0; i < v.size(); ++i)
+        if (v[i] == st) return int(i);
+    if (v.size() >= size_t(WSK_BANKS)) return -1;
+    v.push_back(st);
+    return int(v.size()) - 1;
+}
 template <typename T> int pair_wsk_slots(int dev) {
     static int known[64][2] = {};  // 0 unknown, else clusters + 1
     const int ti = std::is_same<T, bf16>::value ? 0 : 1;
@@ -2228,15 +2369,17 @@ template <typename T> int pair_wsk_slots(int dev) {
         if (cudaFuncSetAttribute(gemm_tcgen05_pair_wsk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, PS_SMEM_BYTES) == cudaSuccess) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)(2 * sm_count()), 1, 1);
-            cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+            cfg.blockDim = dim3(W_THREADS, 1, 1);
             cfg.dynamicSmemBytes = PS_SMEM_BYTES;
-            cudaLaunchAttribute attr[1];
+            cudaLaunchAttribute attr[2];
             attr[0].id = cudaLaunchAttributeClusterDimension;
             attr[0].val.clusterDim.x = 2;
             attr[0].val.clusterDim.y = 1;
             attr[0].val.clusterDim.z = 1;
+            attr[1].id = cudaLaunchAttributeCooperative;
+            attr[1].val.cooperative = 1;
             cfg.attrs = attr;
-            cfg.numAttrs = 1;
+            cfg.numAttrs = 2;
             if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_pair_wsk_kernel<T>, &cfg) != cudaSuccess) n = 0;
         }
         if (n <= 0) { n = 0; cudaGetLastError(); }
@@ -2256,14 +2399,16 @@ int wsk_slices(int64_t batch, int64_t M, int64_t N, int64_t K, int slots) {
     const int64_t k_blocks = (K + BK - 1) / BK;
     if (tiles * 2 > slots || tiles * 2 > 512) return 0;  // enough tiles for the persistent kernels (or more than there are counters)
     int64_t ks = std::min<int64_t>(std::min<int64_t>(8, slots / tiles), k_blocks / 4);
-    if (forced >= 2) ks = std::min<int64_t>(forced, std::min<int64_t>(slots / tiles, k_blocks));
+    if (forced >= 2) ks = std::min<int64_t>(std::min<int64_t>(forced, 8), std::min<int64_t>(slots / tiles, k_blocks));
     while (ks >= 2 && (ks - 1) * ((k_blocks + ks - 1) / ks) >= k_blocks) --ks;  // no slice without a K block
     if (ks < 2) return 0;
-    // What splitting saves in main-loop time has to outweigh what the partials cost: writing them, the fence and the
-    // count-in, and the finishing pair reading ks x 128 KiB out of L2 and adding — measured at 10–12 µs, i.e. some 35 K
-    // blocks of main loop (1024^3: 8.7 -> 16.4 µs and 512 x 4096 x 4096: 23.9 -> 24.9 µs with the split, but
-    // 768 x 2048 x 8192: 33.6 -> 28.8 µs).  So only long K ranges are split.
-    if (forced < 2 && k_blocks * (ks - 1) / ks < 40) return 0;
+    // What splitting saves in main-loop time has to outweigh what the exchange costs: storing the blocks other pairs
+    // finish (an SM pushes about 32 bytes per clock into L2), the release, the count-in and the wait for the slowest
+    // pair (three trips to L2, about 1.5 µs), reading the others' blocks and the larger launch — together some 5 µs,
+    // i.e. about 18 K blocks of main loop.  Measured, bf16, µs without -> with the split: 512 x 4096 x 4096 24.1 ->
+    // 18.5, 256 x 4096 x 4096 22.3 -> 14.4, 768 x 2048 x 8192 32.5 -> 23.5, 256 x 1024 x 16384 33.3 -> 19.8,
+    // 300 x 520 x 8008 36.2 -> 16.5, 512 x 2048 x 2048 13.0 -> 11.9, but 1024^3 (12 blocks saved) 8.1 -> 10.5.
+    if (forced < 2 && k_blocks * (ks - 1) / ks < 20) return 0;
     return int(ks);
 }
 
@@ -2279,7 +2424,7 @@ int launch_pair_wsk(const T *A, const T *B, T *C, int64_t batch, int64_t M, int6
     const size_t need = size_t(tiles) * ks * 2 * WS_HALF_FLOATS * sizeof(float);
     if (!ws || ws_bytes < need || !aligned_to(ws, 16)) return DX_E_UNSUPPORTED;  // the caller gave no (or too little) workspace: the other kernels
     int *status;
-    unsigned int *counters;
+    unsigned long long *counters;
     {
         std::lock_guard<std::mutex> lk(g_setup_mu);
         if (!g_status_ptr[dev]) {
@@ -2289,14 +2434,15 @@ int launch_pair_wsk(const T *A, const T *B, T *C, int64_t batch, int64_t M, int6
             g_status_ptr[dev] = static_cast<int *>(sym);
         }
         status = g_status_ptr[dev];
-        static unsigned int *counter_ptr[64] = {};
-        if (!counter_ptr[dev]) {
+        if (!g_wsk_counter_ptr[dev]) {
             void *sym = nullptr;
             cudaError_t e = cudaGetSymbolAddress(&sym, g_wsk_counters);
             if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-            counter_ptr[dev] = static_cast<unsigned int *>(sym);
+            g_wsk_counter_ptr[dev] = static_cast<unsigned long long *>(sym);
         }
-        counters = counter_ptr[dev];
+        const int bank = wsk_bank(dev, st);
+        if (bank < 0) return DX_E_UNSUPPORTED;
+        counters = g_wsk_counter_ptr[dev] + size_t(bank) * 512;
     }
     const CUtensorMapDataType dt = std::is_same<T, bf16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     CUtensorMap ma, mb;
@@ -2317,16 +2463,18 @@ int launch_pair_wsk(const T *A, const T *B, T *C, int64_t batch, int64_t M, int6
     p.counters = counters;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(tiles * ks * 2), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.blockDim = dim3(W_THREADS, 1, 1);
     cfg.dynamicSmemBytes = PS_SMEM_BYTES;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeCooperative;  // the pairs of a tile wait for one another: all of them must be resident
+    attr[1].val.cooperative = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_wsk_kernel<T>, ma, mb, C, p);
     if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 pair, K split through the workspace): %s", cudaGetErrorString(e));
     return check_launch("matmul(tcgen05 pair, K split through the workspace)");
@@ -2457,6 +2605,7 @@ extern "C" int dx_matmul_status(void *stream) {
         return fail(DX_E_CUDA, "matmul: cannot read the status word: %s", cudaGetErrorString(cudaGetLastError()));
     if (h != 0) {
         cudaMemsetAsync(g_status_ptr[dev], 0, sizeof(int), st);
+        if (g_wsk_counter_ptr[dev]) cudaMemsetAsync(g_wsk_counter_ptr[dev], 0, sizeof(unsigned long long) * WSK_BANKS * 512, st);  // a K-split launch that gave up may have left its counts behind
         return fail(DX_E_CUDA, "matmul: tensor-core pipeline wait %d expired", h);
     }
     return DX_OK;

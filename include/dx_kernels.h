@@ -312,11 +312,13 @@ int dx_repeat(int dtype, const void *a, const int64_t *a_shape, int ndim, const 
 int dx_matmul(int dtype, const void *A, const void *B, void *C, int64_t batch, int64_t M, int64_t N, int64_t K,
               void *stream);
 /* The same with scratch memory from the caller.  A matrix with a few rows of 256 x 256 tiles (M of a few hundred)
- * gives too few tiles for the SMs; with a workspace the K range of each tile is split over several independent
- * CTA pairs, whose fp32 partials meet in the workspace and are added in a fixed order by the pair that arrives
- * last (same bits every run, no atomics on data).  dx_matmul_workspace_bytes says how much that takes for a
- * shape on the current device (0: the shape does not use a workspace); with less (or NULL) the call does what
- * dx_matmul does.  One such call at a time per device: the arrival counters are shared. */
+ * gives too few tiles for the SMs; with a workspace the K range of each tile is split over several CTA pairs
+ * (a cooperative launch: all of them resident), whose fp32 partials meet in the workspace; every pair finishes
+ * its share of the tile's columns, adding in a fixed order (same bits every run, no atomics on data).
+ * dx_matmul_workspace_bytes says how much that takes for a shape on the current device (0: the shape does not
+ * use a workspace); with less (or NULL) the call does what dx_matmul does.  A workspace serves one stream at a
+ * time; calls on different streams, each with its own workspace, may overlap (up to 8 streams per device take
+ * this path, further ones do what dx_matmul does). */
 size_t dx_matmul_workspace_bytes(int dtype, int64_t batch, int64_t M, int64_t N, int64_t K);
 int dx_matmul_ws(int dtype, const void *A, const void *B, void *C, int64_t batch, int64_t M, int64_t N, int64_t K,
                  void *workspace, size_t workspace_bytes, void *stream);

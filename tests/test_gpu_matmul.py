@@ -400,9 +400,10 @@ def test_config_matmul_bf16_8192x4096x4096(mods):
 ])
 def test_matmul_16bit_k_split_through_workspace(mods, shape, dtype):
     """A few rows of 256 x 256 tiles: dx_matmul_ws splits each tile's K range over independent CTA pairs whose fp32
-    partials meet in the caller's workspace and are added in slice order by the pair that arrives last.  Against the
-    float64 product; the same bits on every run (the arrival order must not show); the same answer from dx_matmul,
-    which has no workspace, within the bound; and the arrival counters are back at zero for the next call."""
+    partials meet in the caller's workspace; every pair finishes its share of the tile's columns, adding in slice
+    order.  Against the float64 product; the same bits on every run (the arrival order must not show); the same answer
+    from dx_matmul, which has no workspace, within the bound; and the counters the pairs meet on serve the next call,
+    whatever its number of slices (the shapes of this list follow one another in one process)."""
     TF, O, N = mods
     batch, M, Nn, K = shape
     code = {"bfloat16": N.BF16, "float16": N.F16}[dtype]
@@ -427,3 +428,29 @@ def test_matmul_16bit_k_split_through_workspace(mods, shape, dtype):
     assert (np.abs(to_np(plain).astype(np.float64) - ref) <= TOL[dtype] * np.abs(ref) + 1e-6 * scale + 1e-300).all()
     # an unrelated shape that takes the persistent kernels still works afterwards
     check(TF, N, make(rng, dtype, (384, 512), -1.0, 1.0), make(rng, dtype, (512, 2048), -1.0, 1.0), dtype, "after the K-split kernel")
+
+
+def test_matmul_k_split_on_two_streams_at_once(mods):
+    """Launches of the K-split kernel on different streams may overlap: each stream has its own workspace (the caller's)
+    and its own set of counters (the library's), so both give the bits a launch alone gives."""
+    TF, O, N = mods
+    shapes = [(256, 1024, 8192), (300, 520, 8008)]
+    rng = np.random.default_rng(77)
+    jobs = []
+    for M, Nn, K in shapes:
+        assert int(N.lib.dx_matmul_workspace_bytes(N.BF16, 1, M, Nn, K)) > 0
+        a, b = make(rng, "bfloat16", (M, K), -1.0, 1.0), make(rng, "bfloat16", (K, Nn), -1.0, 1.0)
+        A, B = to_gpu(a), to_gpu(b)
+        alone = torch.empty(M, Nn, dtype=torch.bfloat16, device="cuda:0")
+        ws = torch.empty(int(N.lib.dx_matmul_workspace_bytes(N.BF16, 1, M, Nn, K)), dtype=torch.uint8, device="cuda:0")
+        N.check(N.lib.dx_matmul_ws(N.BF16, A.data_ptr(), B.data_ptr(), alone.data_ptr(), 1, M, Nn, K, ws.data_ptr(), ws.numel(), None))
+        jobs.append((A, B, alone, ws, torch.cuda.Stream(), [torch.empty_like(alone) for _ in range(8)], (M, Nn, K)))
+    torch.cuda.synchronize()
+    for i in range(8):
+        for A, B, alone, ws, st, outs, (M, Nn, K) in jobs:
+            N.check(N.lib.dx_matmul_ws(N.BF16, A.data_ptr(), B.data_ptr(), outs[i].data_ptr(), 1, M, Nn, K, ws.data_ptr(), ws.numel(), st.cuda_stream))
+    torch.cuda.synchronize()
+    N.check(N.lib.dx_matmul_status(None))
+    for A, B, alone, ws, st, outs, shape in jobs:
+        for o in outs:
+            assert torch.equal(o, alone), f"{shape}: a launch that overlapped another stream's differs from a launch alone"
