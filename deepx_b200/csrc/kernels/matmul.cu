@@ -194,6 +194,12 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
     return v;
 }
 
+// Programmatic dependent launch: a kernel launched with the stream-serialisation attribute may be scheduled while
+// the kernel before it on the stream drains; everything it does before this wait (barrier set-up, TMEM allocation,
+// descriptor prefetch) touches no global memory, and nothing after it runs before the earlier kernel has completed
+// and its writes are visible.  Without the attribute the instruction returns at once.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
 template <> __device__ __forceinline__ uint32_t pack2<bf16>(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -345,6 +351,7 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    griddep_wait();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     if (warp == 0) {
@@ -570,6 +577,7 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     __syncthreads();
     cluster_sync_all();  // the peer's barriers exist before anything signals them
     tc_fence_after();
+    griddep_wait();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     auto tile_coords = [&](int tile, int &b, int &tm, int &tn) { grouped_tile_coords(tile, p.tiles_m, p.tiles_n, p.raster, b, tm, tn); };
@@ -2056,6 +2064,12 @@ template <typename T> int pair_slots(int dev) {
 }
 
 // Persistent single-CTA kernel at tile width BN_.
+// DX_GEMM_PDL=0 launches the persistent kernels without programmatic stream serialisation.
+bool pdl_on() {
+    static const bool on = [] { const char *e = std::getenv("DX_GEMM_PDL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 template <typename T, int BN_>
 int launch_single(const CUtensorMap &ma, const CUtensorMap &mb, T *C, int64_t batch, int64_t M, int64_t N, int64_t K, bool c_staged,
                   int *status, int dev, cudaStream_t st) {
@@ -2081,7 +2095,18 @@ int launch_single(const CUtensorMap &ma, const CUtensorMap &mb, T *C, int64_t ba
     p.raster = raster_group(M, N, K, (int)sizeof(T), p.tiles_m);
     p.c_staged = c_staged ? 1 : 0;
     const int grid = (int)std::min<int64_t>(tiles, sm_count());
-    gemm_tcgen05_kernel<T, BN_><<<grid, G_THREADS, Cfg::SMEM, st>>>(ma, mb, C, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3(G_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_on() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_kernel<T, BN_>, ma, mb, C, p);
+    if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05): %s", cudaGetErrorString(e));
     return check_launch("matmul(tcgen05)");
 }
 
@@ -2170,13 +2195,15 @@ int launch_tcgen05(const T *A, const T *B, T *C, int64_t batch, int64_t M, int64
         cfg.blockDim = dim3(G_THREADS, 1, 1);
         cfg.dynamicSmemBytes = P_SMEM_BYTES;
         cfg.stream = st;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[1].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = pdl_on() ? 2 : 1;
         cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<T>, ma, mb, C, pp);
         if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 pair): %s", cudaGetErrorString(e));
         return check_launch("matmul(tcgen05 pair)");
