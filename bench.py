@@ -710,9 +710,29 @@ def run_ours(args) -> None:
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
+    if ops.peer is not None:
+        ops.peer.wait_stats(reset=True)
     l0 = N.lib.dx_launch_count()
-    ms_total = timed(lambda: chain(True), args.steps)
+    # the dominant kernel is timed with a pair of events on a few of the timed steps (first, middle, last): an event
+    # between two kernels costs their boundary the overlapped launch (a few µs), so not on every step
+    sampled = sorted({0, args.steps // 2, args.steps - 1})
+    step_no = [0]
+
+    def timed_step():
+        chain(step_no[0] in sampled)
+        step_no[0] += 1
+
+    ms_total = timed(timed_step, args.steps)
     launches = N.lib.dx_launch_count() - l0
+    # what the rendezvous cost inside the timed region: the flag waits of this rank's combine CTAs (worst rank reported)
+    exchange = None
+    if ops.peer is not None:
+        wait_us, waits = ops.peer.wait_stats(reset=True)
+        w = torch.tensor([wait_us], dtype=torch.float64, device=dev)
+        dist.all_reduce(w, op=dist.ReduceOp.MAX)
+        exchange = {"flag_wait_us_per_step": round(float(w.item()) / args.steps, 2), "waits_per_step": waits / args.steps,
+                    "what": "SM time the combine CTAs of the slowest-waiting rank spent polling peers' flags (dx_comm_wait_stats); "
+                            "a wait that finds the flags set still counts the round trip of its acquire loads"}
     # nvidia-smi cannot sample faster than every few tens of ms; a short timed region (many GPUs, few
     # steps) may pass between two samples.  Keep the same chain running, untimed, until a few samples
     # exist, so that the clocks reported are clocks under this load.
@@ -888,7 +908,8 @@ def run_ours(args) -> None:
                      "peak_source": f"MEASURED_PEAKS.json hbm_gbs ({peak_kind})", "unit": "GB/s", "frac": round(achieved / peak, 4),
                      "traffic": round(MUL_TRAFFIC_PER_ROW * my_rows), "traffic_source": "ncu dram read+write of the same kernel on 256 rows "
                      "(profiles/ew2_mul_f32_chain_256x1048576.md), scaled by rows",
-                     "bytes_per_launch": mul_bytes, "us_per_launch": round(mul_ms * 1e3, 2)},
+                     "bytes_per_launch": mul_bytes, "us_per_launch": round(mul_ms * 1e3, 2),
+                     "timed_on": f"CUDA events around the kernel on {len(mul_events)} of the {args.steps} timed steps"},
         "e2e": {"value": round(e2e_value, 1), "unit": UNIT, "h2d_bytes_per_step": 2 * my_rows * COLS * 4 * world,
                 "d2h_bytes_per_step": (4 + my_rows * 4) * world, "ms_per_step": round(e2e_ms, 3), "ms_per_step_host_clock": round(e2e_wall_ms, 3),
                 "steps": e2e_steps,
@@ -905,6 +926,7 @@ def run_ours(args) -> None:
                              "compiled: the same line 200x as one program captured into a CUDA graph (dx_exec_compile), 50 replays; "
                              "udp: the same line as one datagram to the deepx-op-b200 process on loopback, reply awaited, 2000 times"},
         "gpu_launches": int(launches),
+        "exchange": exchange,
         "clocks": clocks,
         "global_sum": got_sum,
         "parity_guard": parity_guard,

@@ -60,6 +60,7 @@ SIGNATURES = {
     "dx_comm_set_timeout_ms": (_i, [_vp, _i]),
     "dx_comm_allreduce": (_i, [_vp, _i, _i, _vp, _i64, _vp]),
     "dx_comm_status": (_i, [_vp, _vp]),
+    "dx_comm_wait_stats": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_longlong), _i, _vp]),
     "dx_comm_destroy": (None, [_vp]),
     "dx_reduce_allreduce": (_i, [_vp, _i, _i, _vp, _pi64, _i, _pi32, _i, _vp, _vp, _sz, _vp]),
     "dx_comm_emulate": (_vp, [_i, _i]),

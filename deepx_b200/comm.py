@@ -112,6 +112,13 @@ class PeerComm:
         """Raises DxError when a wait on a peer expired since the last call (synchronises)."""
         N.check(N.lib.dx_comm_status(self._h, None))
 
+    def wait_stats(self, reset: bool = True) -> tuple[float, int]:
+        """(microseconds this rank's CTAs spent waiting for peers' flags, number of waits) since the last reset."""
+        import ctypes
+        us, n = ctypes.c_double(0.0), ctypes.c_longlong(0)
+        N.check(N.lib.dx_comm_wait_stats(self._h, ctypes.byref(us), ctypes.byref(n), 1 if reset else 0, None))
+        return float(us.value), int(n.value)
+
     def close(self) -> None:
         if getattr(self, "_h", None) and N is not None and getattr(N, "lib", None) is not None:  # the module may be gone at interpreter exit
             N.lib.dx_comm_destroy(self._h)
@@ -164,6 +171,13 @@ class EmulatedComm:
 
     def status(self) -> None:
         N.check(N.lib.dx_comm_status(self._h, None))
+
+    def wait_stats(self, reset: bool = True) -> tuple[float, int]:
+        """(microseconds rank 0's CTAs spent waiting for the other ranks' flags, number of waits) since the last reset."""
+        import ctypes
+        us, n = ctypes.c_double(0.0), ctypes.c_longlong(0)
+        N.check(N.lib.dx_comm_wait_stats(self._h, ctypes.byref(us), ctypes.byref(n), 1 if reset else 0, None))
+        return float(us.value), int(n.value)
 
     def close(self) -> None:
         if getattr(self, "_h", None) and N is not None and getattr(N, "lib", None) is not None:  # the module may be gone at interpreter exit

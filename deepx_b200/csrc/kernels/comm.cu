@@ -51,6 +51,7 @@ __global__ void __launch_bounds__(COMM_THREADS) peer_publish_kernel(Peers peers,
 }
 template <int OP, typename T>
 __global__ void __launch_bounds__(COMM_THREADS) peer_combine_kernel(Peers peers, int rank, T *buf, int64_t n, long long wait_cycles) {
+    griddep_wait();
     exchange_combine<OP, T>(peers, rank, blockIdx.x, buf, n, wait_cycles);
 }
 __global__ void __launch_bounds__(COMM_THREADS) peer_gather_kernel(Peers peers, int rank, unsigned char *buf, GatherPlan plan, long long wait_cycles) {
@@ -128,7 +129,7 @@ template <int OP, typename T> int launch_publish(dx_comm *c, void *buf, int64_t 
 template <int OP, typename T> int launch_combine(dx_comm *c, void *buf, int64_t n, cudaStream_t st) {
     constexpr int PER = COMM_CHUNK / int(sizeof(T));
     const int chunks = int((n + PER - 1) / PER);
-    peer_combine_kernel<OP, T><<<chunks, COMM_THREADS, 0, st>>>(c->peers, c->rank, static_cast<T *>(buf), n, c->wait_cycles);
+    launch_pdl(peer_combine_kernel<OP, T>, dim3(chunks), dim3(COMM_THREADS), 0, st, c->peers, c->rank, static_cast<T *>(buf), n, c->wait_cycles);
     return check_launch("comm combine");
 }
 template <int OP, typename T> int launch_emulated_publish(dx_comm *c, void *const *bufs, int active, int64_t n, cudaStream_t st) {
@@ -372,6 +373,27 @@ extern "C" int dx_comm_allgather_rows(dx_comm *c, void *buf, int64_t global_rows
         peer_gather_kernel<<<chunks, COMM_THREADS, 0, as_stream(stream)>>>(c->peers, c->rank, static_cast<unsigned char *>(buf), g, c->wait_cycles);
         if (int e = check_launch("comm allgather")) return e;
     }
+    return DX_OK;
+}
+
+extern "C" int dx_comm_wait_stats(dx_comm *c, double *microseconds, long long *waits, int reset, void *stream) {
+    if (!c || !microseconds || !waits) return fail(DX_E_ARG, "comm: null argument");
+    cudaStream_t st = as_stream(stream);
+    Mailbox *m = c->emulated.empty() ? c->mine : c->emulated[0];
+    struct { unsigned int waits; unsigned long long cycles; } h = {0u, 0ull};
+    if (cudaMemcpyAsync(&h.waits, &m->waits, sizeof(unsigned int), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaMemcpyAsync(&h.cycles, &m->waited_cycles, sizeof(unsigned long long), cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+        return fail(DX_E_CUDA, "comm: cannot read the wait counters: %s", cudaGetErrorString(cudaGetLastError()));
+    if (reset) {
+        cudaMemsetAsync(&m->waits, 0, sizeof(unsigned int), st);
+        cudaMemsetAsync(&m->waited_cycles, 0, sizeof(unsigned long long), st);
+        cudaStreamSynchronize(st);
+    }
+    int khz = 0;
+    if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device) != cudaSuccess || khz <= 0) khz = 1965000;
+    *microseconds = double(h.cycles) * 1000.0 / double(khz);
+    *waits = (long long)h.waits;
     return DX_OK;
 }
 

@@ -18,7 +18,9 @@ struct Mailbox {
     unsigned int flag[2][COMM_MAX_WORLD][COMM_CHUNKS];  // epoch last published by (rank, chunk)
     unsigned int epoch[COMM_CHUNKS];                    // epochs this rank has completed per chunk
     int status;                                         // 0, or 1 + chunk * 64 + peer of the wait that expired
-    int pad[15];
+    unsigned int waits;                                 // flag waits done by this rank's CTAs, and
+    unsigned long long waited_cycles;                   // the SM cycles they took (the longest thread of each CTA)
+    int pad[12];
     alignas(256) unsigned char slot[2][COMM_MAX_WORLD][COMM_SLOT];
 };
 
@@ -88,10 +90,11 @@ __device__ void exchange_publish(const Peers &peers, int rank, int chunk, const 
 // when a wait ran into its limit.  All threads of the CTA call it and get the same answer.
 __device__ __forceinline__ bool exchange_wait(const Peers &peers, int rank, int chunk, long long wait_cycles, unsigned int *epoch_out) {
     __shared__ int gave_up;
+    __shared__ unsigned long long longest;
     Mailbox *mine = peers.box[rank];
     const unsigned int e = mine->epoch[chunk] + 1;
     const int par = int(e & 1u);
-    if (threadIdx.x == 0) gave_up = 0;
+    if (threadIdx.x == 0) { gave_up = 0; longest = 0ull; }
     __syncthreads();
     if (threadIdx.x < peers.world) {
         const int p = threadIdx.x;
@@ -103,8 +106,13 @@ __device__ __forceinline__ bool exchange_wait(const Peers &peers, int rank, int 
                 break;
             }
         }
+        atomicMax(&longest, (unsigned long long)(clock64() - t0));
     }
     __syncthreads();
+    if (threadIdx.x == 0) {  // what the rendezvous cost this CTA: dx_comm_wait_stats adds these up
+        atomicAdd(&mine->waited_cycles, longest);
+        atomicAdd(&mine->waits, 1u);
+    }
     *epoch_out = e;
     return gave_up == 0;
 }

@@ -20,6 +20,31 @@ int check_launch(const char *what);  // cudaGetLastError → DX_E_CUDA
 
 inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s); }
 
+// ---- programmatic dependent launch -----------------------------------------------
+// A kernel launched through launch_pdl may be scheduled while the kernel before it on the stream drains: its CTAs
+// become resident and run up to griddep_wait(), which returns once the earlier kernel has completed and its writes
+// are visible.  Every kernel launched this way calls griddep_wait() before its first access to global memory, so
+// the order of the stream is kept exactly; what is saved is the launch latency at every kernel boundary.  Without
+// the launch attribute the instruction returns at once.  DX_PDL=0 launches everything the ordinary way.
+bool pdl_enabled();
+#ifdef __CUDACC__
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // an error stays for check_launch to find
+}
+#endif
+
 // ---- dtype ↔ C++ type ----------------------------------------------------------
 using f16 = __half;
 using bf16 = __nv_bfloat16;

@@ -25,6 +25,7 @@ template <typename F> struct functor_has_vector_check<F, std::void_t<decltype(F:
 
 template <int VEC, typename TA, typename TC, typename F>
 __global__ void __launch_bounds__(EW_BLOCK) ew1_kernel(const TA *a, TC *c, int64_t n, F f) {
+    griddep_wait();
     constexpr int64_t TILE = int64_t(EW_BLOCK) * EW_UNROLL * VEC;
     const int64_t base = int64_t(blockIdx.x) * TILE;
     if (base + TILE <= n) {
@@ -60,6 +61,7 @@ __global__ void __launch_bounds__(EW_BLOCK) ew1_kernel(const TA *a, TC *c, int64
 template <int VEC, typename TA, typename TB, typename TC, typename F>
 __global__ void __launch_bounds__(EW_BLOCK)
     ew2_kernel(const TA *a, const TB *b, TC *c, int64_t n, F f) {
+    griddep_wait();
     constexpr int64_t TILE = int64_t(EW_BLOCK) * EW_UNROLL * VEC;
     const int64_t base = int64_t(blockIdx.x) * TILE;
     if (base + TILE <= n) {
@@ -128,10 +130,10 @@ int launch_ew1(const TA *a, TC *c, int64_t n, F f, cudaStream_t st, const char *
     int64_t grid;
     if (aligned_to(a, sizeof(TA) * VEC) && aligned_to(c, sizeof(TC) * VEC)) {
         if (int e = ew_grid(n, VEC, &grid)) return e;
-        ew1_kernel<VEC, TA, TC, F><<<(unsigned)grid, EW_BLOCK, 0, st>>>(a, c, n, f);
+        launch_pdl(ew1_kernel<VEC, TA, TC, F>, dim3((unsigned)grid), dim3(EW_BLOCK), 0, st, a, c, n, f);
     } else {
         if (int e = ew_grid(n, 1, &grid)) return e;
-        ew1_kernel<1, TA, TC, F><<<(unsigned)grid, EW_BLOCK, 0, st>>>(a, c, n, f);
+        launch_pdl(ew1_kernel<1, TA, TC, F>, dim3((unsigned)grid), dim3(EW_BLOCK), 0, st, a, c, n, f);
     }
     return check_launch(what);
 }
@@ -144,10 +146,10 @@ int launch_ew2(const TA *a, const TB *b, TC *c, int64_t n, F f, cudaStream_t st,
     int64_t grid;
     if (aligned_to(a, sizeof(TA) * VEC) && aligned_to(b, sizeof(TB) * VEC) && aligned_to(c, sizeof(TC) * VEC)) {
         if (int e = ew_grid(n, VEC, &grid)) return e;
-        ew2_kernel<VEC, TA, TB, TC, F><<<(unsigned)grid, EW_BLOCK, 0, st>>>(a, b, c, n, f);
+        launch_pdl(ew2_kernel<VEC, TA, TB, TC, F>, dim3((unsigned)grid), dim3(EW_BLOCK), 0, st, a, b, c, n, f);
     } else {
         if (int e = ew_grid(n, 1, &grid)) return e;
-        ew2_kernel<1, TA, TB, TC, F><<<(unsigned)grid, EW_BLOCK, 0, st>>>(a, b, c, n, f);
+        launch_pdl(ew2_kernel<1, TA, TB, TC, F>, dim3((unsigned)grid), dim3(EW_BLOCK), 0, st, a, b, c, n, f);
     }
     return check_launch(what);
 }

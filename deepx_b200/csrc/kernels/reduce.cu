@@ -96,6 +96,7 @@ struct ColsParams {
 template <int OP, typename T, int VEC>
 __global__ void __launch_bounds__(RB) rows_block_kernel(const T *__restrict__ in, T *__restrict__ out,
                                                         acc_t<T> *__restrict__ partial, RowsParams p) {
+    griddep_wait();
     using A = acc_t<T>;
     const uint32_t o = blockIdx.x / p.split;
     const uint32_t c = blockIdx.x - o * p.split;
@@ -192,10 +193,39 @@ __global__ void __launch_bounds__(RB) rows_team_kernel(const T *__restrict__ in,
     if (live && lane == 0) out[o] = narrow<T>(r);
 }
 
+// One output whose partials are many (a single output split over several waves of CTAs): the whole CTA adds them,
+// thread t taking partials t, t + RB, ..., then lanes, then warps, always in the same order.  The value is in thread 0.
+constexpr uint32_t FINISH_WIDE_FROM = 128;  // partials per output from which a CTA, not a warp, finishes an output
+template <int OP, typename T>
+__device__ __forceinline__ acc_t<T> cta_combine_partials(const acc_t<T> *__restrict__ p, uint32_t split) {
+    using A = acc_t<T>;
+    __shared__ A wide_part[RB / 32];
+    A r = identity<OP, T>();
+    for (uint32_t c = threadIdx.x; c < split; c += RB) r = combine<OP>(r, p[c]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) r = combine<OP>(r, shfl_down(r, d, 32));
+    __syncthreads();  // a previous output's wide_part has been read
+    if ((threadIdx.x & 31) == 0) wide_part[threadIdx.x >> 5] = r;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        r = wide_part[0];
+#pragma unroll
+        for (int w = 1; w < RB / 32; ++w) r = combine<OP>(r, wide_part[w]);
+    }
+    return r;
+}
+template <int OP, typename T>
+__global__ void __launch_bounds__(RB) rows_finish_wide_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out, uint32_t split) {
+    griddep_wait();
+    const acc_t<T> r = cta_combine_partials<OP, T>(partial + size_t(blockIdx.x) * split, split);
+    if (threadIdx.x == 0) out[blockIdx.x] = narrow<T>(r);
+}
+
 // partial[nout][split] → out[nout]; one warp per output, fixed order.
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) rows_finish_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out,
                                                          uint32_t nout, uint32_t split) {
+    griddep_wait();
     using A = acc_t<T>;
     const uint32_t o = blockIdx.x * (RB / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -310,6 +340,7 @@ __global__ void __launch_bounds__(RB) cols_kernel(const T *__restrict__ in, T *_
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) cols_finish_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out,
                                                          int64_t nout, uint32_t split) {
+    griddep_wait();
     using A = acc_t<T>;
     const int64_t o = int64_t(blockIdx.x) * RB + threadIdx.x;
     if (o >= nout) return;
@@ -335,10 +366,16 @@ struct PeerTail {
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) rows_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, uint32_t nout, uint32_t split,
                                                               PeerTail tail) {
+    griddep_wait();
     using A = acc_t<T>;
     const uint32_t o = threadIdx.x >> 5;  // one CTA, one warp per output
     const int lane = threadIdx.x & 31;
-    if (o < nout) {
+    if (split >= FINISH_WIDE_FROM) {  // many partials per output: the CTA takes the outputs one after the other
+        for (uint32_t w = 0; w < nout; ++w) {
+            const A r = cta_combine_partials<OP, T>(partial + size_t(w) * split, split);
+            if (threadIdx.x == 0) out[w] = narrow<T>(r);
+        }
+    } else if (o < nout) {
         A r = identity<OP, T>();
         for (uint32_t c = lane; c < split; c += 32) r = combine<OP>(r, partial[size_t(o) * split + c]);
 #pragma unroll
@@ -352,6 +389,7 @@ __global__ void __launch_bounds__(RB) rows_finish_peer_kernel(const acc_t<T> *__
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) cols_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, int64_t nout, uint32_t split,
                                                               PeerTail tail) {
+    griddep_wait();
     using A = acc_t<T>;
     const int64_t o = threadIdx.x;  // one CTA, one thread per output
     if (o < nout) {
@@ -505,7 +543,12 @@ int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, in
             pl->kind = PLAN_ROWS_BLOCK;
             int64_t split = 1;
             if (nout < target_ctas) {
-                const int64_t by_target = target_ctas / nout;  // floor: one wave, no straggler CTAs
+                // Too few outputs for one CTA each to fill the GPU: split every output — over about FOUR waves of
+                // CTAs, not one.  CTAs of a single wave all end at about the same time and the slowest decides
+                // (measured on [256, 1048576] float32: sum 175 µs, row max 161 µs against 154 / 147 µs at the
+                // bandwidth the same kernels reach on 8 times the rows); with several short waves the hardware
+                // scheduler evens that out, like it does for the elementwise kernels' grids.
+                const int64_t by_target = std::max<int64_t>(1, int64_t(target_ctas) * 4 / nout);
                 const int64_t by_work = std::max<int64_t>(1, units / (RB * RUNROLL * 2));
                 split = std::max<int64_t>(1, std::min(by_target, by_work));
             }
@@ -615,16 +658,18 @@ int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cud
         return check_launch("reduce(rows/team)");
     }
     if (pl.kind == PLAN_ROWS_BLOCK) {
-        LAUNCH_VEC(rows_block_kernel, in, out, partial, q.rows);
+        if (vec == FULL) launch_pdl(rows_block_kernel<OP, T, FULL>, dim3(q.grid), dim3(RB), 0, st, in, out, partial, q.rows);
+        else launch_pdl(rows_block_kernel<OP, T, 1>, dim3(q.grid), dim3(RB), 0, st, in, out, partial, q.rows);
         if (int e = check_launch("reduce(rows/block)")) return e;
         if (q.rows.split > 1) {
             const unsigned grid = (q.rows.nout + RB / 32 - 1) / (RB / 32);
             if (tail && grid == 1) {
-                rows_finish_peer_kernel<OP, T><<<1, RB, 0, st>>>(partial, out, q.rows.nout, q.rows.split, *tail);
+                launch_pdl(rows_finish_peer_kernel<OP, T>, dim3(1), dim3(RB), 0, st, partial, out, q.rows.nout, q.rows.split, *tail);
                 if (exchanged) *exchanged = true;
                 return check_launch("reduce(rows/finish + exchange)");
             }
-            rows_finish_kernel<OP, T><<<grid, RB, 0, st>>>(partial, out, q.rows.nout, q.rows.split);
+            if (q.rows.split >= FINISH_WIDE_FROM) launch_pdl(rows_finish_wide_kernel<OP, T>, dim3(q.rows.nout), dim3(RB), 0, st, partial, out, q.rows.split);
+            else launch_pdl(rows_finish_kernel<OP, T>, dim3(grid), dim3(RB), 0, st, partial, out, q.rows.nout, q.rows.split);
             return check_launch("reduce(rows/finish)");
         }
         return DX_OK;

@@ -1,4 +1,5 @@
 // Error reporting, dtype table, device properties.
+#include <cstdlib>
 #include <atomic>
 #include <cstring>
 #include <mutex>
@@ -23,6 +24,11 @@ int fail(int code, const char *fmt, ...) {
     vsnprintf(g_err, sizeof(g_err), fmt, ap);
     va_end(ap);
     return code;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] { const char *e = std::getenv("DX_PDL"); return !(e && e[0] == '0'); }();
+    return on;
 }
 
 int check_launch(const char *what) {

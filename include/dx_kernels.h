@@ -207,6 +207,11 @@ int dx_comm_connect(dx_comm *c, const unsigned char *handles);
 int dx_comm_set_timeout_ms(dx_comm *c, int ms);
 int dx_comm_allreduce(dx_comm *c, int op, int dtype, void *buf, int64_t n, void *stream);
 int dx_comm_status(dx_comm *c, void *stream);
+/* What the rendezvous has cost this rank since the counters were last reset: the number of flag waits its CTAs did
+ * and the time they took (per CTA the longest of its threads, summed; SM cycles at the device's nominal clock,
+ * given in microseconds).  Synchronises the stream.  A wait that finds its flags already set counts a few hundred
+ * nanoseconds: the round trip of the acquire loads. */
+int dx_comm_wait_stats(dx_comm *c, double *microseconds, long long *waits, int reset, void *stream);
 void dx_comm_destroy(dx_comm *c);
 int dx_comm_rank(dx_comm *c);
 int dx_comm_world(dx_comm *c);

@@ -133,7 +133,10 @@ def test_split_exchange_publish_then_combine(world, dtype):
     rng = np.random.default_rng(seed_of("split", world, dtype))
     es = np.dtype(NP_DTYPES[dtype]).itemsize
     other = torch.zeros(1 << 20, device="cuda:0")
+    comm.wait_stats(reset=True)
+    expected_waits = 0
     for round_, (op, n) in enumerate([(o, n) for o in ("sum", "reducemax", "reducemin") for n in (1, 4096 // es + 3, 2 * 4096 // es)]):
+        expected_waits += 2 * -(-n * es // 4096)   # one wait per 4 KiB chunk and exchange (the split one and the one-launch one)
         parts = [make(rng, dtype, (n,), -4.0, 4.0) for _ in range(world)]
         bufs = [to_gpu(p) for p in parts]
         comm.publish(bufs, op)
@@ -148,6 +151,9 @@ def test_split_exchange_publish_then_combine(world, dtype):
         comm.allreduce(bufs, op)
         comm.status()
         assert np.array_equal(to_np(bufs[world - 1]).view(np.uint8), want.view(np.uint8))
+    waited_us, waits = comm.wait_stats()
+    assert waits == expected_waits and 0.0 < waited_us < 1e6, (waits, expected_waits, waited_us)   # the rendezvous is accounted for, per CTA
+    assert comm.wait_stats() == (0.0, 0)
     comm.close()
 
 
