@@ -51,7 +51,7 @@ __global__ void __launch_bounds__(COMM_THREADS) peer_publish_kernel(Peers peers,
 }
 template <int OP, typename T>
 __global__ void __launch_bounds__(COMM_THREADS) peer_combine_kernel(Peers peers, int rank, T *buf, int64_t n, long long wait_cycles) {
-    griddep_wait();
+    griddep_wait_cta();
     exchange_combine<OP, T>(peers, rank, blockIdx.x, buf, n, wait_cycles);
 }
 __global__ void __launch_bounds__(COMM_THREADS) peer_gather_kernel(Peers peers, int rank, unsigned char *buf, GatherPlan plan, long long wait_cycles) {

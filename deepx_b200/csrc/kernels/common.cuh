@@ -29,6 +29,13 @@ inline cudaStream_t as_stream(void *s) { return reinterpret_cast<cudaStream_t>(s
 bool pdl_enabled();
 #ifdef __CUDACC__
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// The whole CTA behind one waiting thread: warps parked in griddepcontrol.wait were measured to slow down the CTAs of
+// the earlier kernel that are still running (a GEMM whose last wave fills a quarter of the SMs: 194 -> 233 µs with
+// every thread of the early-resident CTAs waiting, 199 µs with one), warps parked at a CTA barrier do not.
+__device__ __forceinline__ void griddep_wait_cta() {
+    if (threadIdx.x == 0) griddep_wait();
+    __syncthreads();
+}
 template <typename... KArgs, typename... Args>
 inline void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
     cudaLaunchConfig_t cfg = {};

@@ -25,7 +25,7 @@ template <typename F> struct functor_has_vector_check<F, std::void_t<decltype(F:
 
 template <int VEC, typename TA, typename TC, typename F>
 __global__ void __launch_bounds__(EW_BLOCK) ew1_kernel(const TA *a, TC *c, int64_t n, F f) {
-    griddep_wait();
+    griddep_wait_cta();
     constexpr int64_t TILE = int64_t(EW_BLOCK) * EW_UNROLL * VEC;
     const int64_t base = int64_t(blockIdx.x) * TILE;
     if (base + TILE <= n) {
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(EW_BLOCK) ew1_kernel(const TA *a, TC *c, int64
 template <int VEC, typename TA, typename TB, typename TC, typename F>
 __global__ void __launch_bounds__(EW_BLOCK)
     ew2_kernel(const TA *a, const TB *b, TC *c, int64_t n, F f) {
-    griddep_wait();
+    griddep_wait_cta();
     constexpr int64_t TILE = int64_t(EW_BLOCK) * EW_UNROLL * VEC;
     const int64_t base = int64_t(blockIdx.x) * TILE;
     if (base + TILE <= n) {

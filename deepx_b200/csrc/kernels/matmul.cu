@@ -357,12 +357,12 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    griddep_wait();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     if (warp == 0) {
         // ===== TMA producer =====
         if (lane == 0) {
+            griddep_wait();  // the one thread that first touches global memory; every other role follows its loads
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -583,7 +583,6 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     __syncthreads();
     cluster_sync_all();  // the peer's barriers exist before anything signals them
     tc_fence_after();
-    griddep_wait();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     auto tile_coords = [&](int tile, int &b, int &tm, int &tn) { grouped_tile_coords(tile, p.tiles_m, p.tiles_n, p.raster, b, tm, tn); };
@@ -591,6 +590,7 @@ __global__ void __launch_bounds__(G_THREADS, 1)
     if (warp == 0) {
         // ===== TMA producer (one per CTA; both complete on the LEADER's full barrier) =====
         if (lane == 0) {
+            griddep_wait();  // the one thread that first touches global memory; every other role follows its loads
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;

@@ -96,7 +96,7 @@ struct ColsParams {
 template <int OP, typename T, int VEC>
 __global__ void __launch_bounds__(RB) rows_block_kernel(const T *__restrict__ in, T *__restrict__ out,
                                                         acc_t<T> *__restrict__ partial, RowsParams p) {
-    griddep_wait();
+    griddep_wait_cta();
     using A = acc_t<T>;
     const uint32_t o = blockIdx.x / p.split;
     const uint32_t c = blockIdx.x - o * p.split;
@@ -216,7 +216,7 @@ __device__ __forceinline__ acc_t<T> cta_combine_partials(const acc_t<T> *__restr
 }
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) rows_finish_wide_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out, uint32_t split) {
-    griddep_wait();
+    griddep_wait_cta();
     const acc_t<T> r = cta_combine_partials<OP, T>(partial + size_t(blockIdx.x) * split, split);
     if (threadIdx.x == 0) out[blockIdx.x] = narrow<T>(r);
 }
@@ -225,7 +225,7 @@ __global__ void __launch_bounds__(RB) rows_finish_wide_kernel(const acc_t<T> *__
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) rows_finish_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out,
                                                          uint32_t nout, uint32_t split) {
-    griddep_wait();
+    griddep_wait_cta();
     using A = acc_t<T>;
     const uint32_t o = blockIdx.x * (RB / 32) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(RB) cols_kernel(const T *__restrict__ in, T *_
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) cols_finish_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out,
                                                          int64_t nout, uint32_t split) {
-    griddep_wait();
+    griddep_wait_cta();
     using A = acc_t<T>;
     const int64_t o = int64_t(blockIdx.x) * RB + threadIdx.x;
     if (o >= nout) return;
@@ -366,7 +366,7 @@ struct PeerTail {
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) rows_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, uint32_t nout, uint32_t split,
                                                               PeerTail tail) {
-    griddep_wait();
+    griddep_wait_cta();
     using A = acc_t<T>;
     const uint32_t o = threadIdx.x >> 5;  // one CTA, one warp per output
     const int lane = threadIdx.x & 31;
@@ -389,7 +389,7 @@ __global__ void __launch_bounds__(RB) rows_finish_peer_kernel(const acc_t<T> *__
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) cols_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, int64_t nout, uint32_t split,
                                                               PeerTail tail) {
-    griddep_wait();
+    griddep_wait_cta();
     using A = acc_t<T>;
     const int64_t o = threadIdx.x;  // one CTA, one thread per output
     if (o < nout) {
