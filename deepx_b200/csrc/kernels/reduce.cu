@@ -92,10 +92,52 @@ struct ColsParams {
     int tx;           // threads across columns (power of two ≤ 32); RB/tx rows in flight
 };
 
+// ---- a split reduction that finishes itself -------------------------------------------------------------
+// A reduction split over several CTAs per output leaves partials; adding them up used to be a second, one-CTA
+// launch: a launch boundary (≈3 µs) plus 3–5 µs of a kernel that is all latency.  Instead every CTA counts itself in
+// on its output's counter after its partial is stored and fenced, and the CTA that finds the count complete adds
+// the partials — in index order, so the same bits whichever CTA it is — writes the output and puts the counter
+// back to zero.  When the result is one value that has to be combined across GPUs, that CTA also publishes it to
+// the peers (and combines, unless that is deferred).  The counters are the library's (zero between launches), one
+// bank per stream that uses them.
+constexpr int RED_BANKS = 8, RED_COUNTERS = 2048;
+__device__ unsigned int g_reduce_counters[RED_BANKS][RED_COUNTERS];
+struct PeerTail {
+    Peers peers;
+    int rank;
+    long long wait_cycles;
+    int combine_now;  // 0: the kernel ends after publishing; the combine runs later on the stream (dx_comm_allreduce_finish)
+};
+struct FuseTail {
+    unsigned int *counters;  // one per output
+    int peer;                // 1: the finished value (one output) goes into the exchange
+    PeerTail tail;
+};
+
+// One output whose partials are many (a single output split over several waves of CTAs): the whole CTA adds them,
+// thread t taking partials t, t + RB, ..., then lanes, then warps, always in the same order.  The value is in thread 0.
+constexpr uint32_t FINISH_WIDE_FROM = 128;  // partials per output from which a CTA, not a warp, finishes an output
+template <int OP, typename T>
+__device__ __forceinline__ acc_t<T> cta_combine_partials(const acc_t<T> *__restrict__ p, uint32_t split) {
+    using A = acc_t<T>;
+    __shared__ A wide_part[RB / 32];
+    A r = identity<OP, T>();
+    for (uint32_t c = threadIdx.x; c < split; c += RB) r = combine<OP>(r, __ldcg(p + c));  // L2: other CTAs of this launch may have written them
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) r = combine<OP>(r, shfl_down(r, d, 32));
+    __syncthreads();  // a previous output's wide_part has been read
+    if ((threadIdx.x & 31) == 0) wide_part[threadIdx.x >> 5] = r;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        r = wide_part[0];
+#pragma unroll
+        for (int w = 1; w < RB / 32; ++w) r = combine<OP>(r, wide_part[w]);
+    }
+    return r;
+}
 // ---- rows: one CTA (or 1/split of the work) per output ----------------------------------
-template <int OP, typename T, int VEC>
-__global__ void __launch_bounds__(RB) rows_block_kernel(const T *__restrict__ in, T *__restrict__ out,
-                                                        acc_t<T> *__restrict__ partial, RowsParams p) {
+template <int OP, typename T, int VEC, bool FUSE = false>
+__global__ void __launch_bounds__(RB) rows_block_kernel(const T *__restrict__ in, T *out, acc_t<T> *partial, RowsParams p, FuseTail ft) {
     griddep_wait_cta();
     using A = acc_t<T>;
     const uint32_t o = blockIdx.x / p.split;
@@ -146,6 +188,27 @@ __global__ void __launch_bounds__(RB) rows_block_kernel(const T *__restrict__ in
         if (p.split == 1) out[o] = narrow<T>(r);
         else partial[size_t(o) * p.split + c] = r;
     }
+    if constexpr (FUSE) {
+        __shared__ int last;
+        if (threadIdx.x == 0) {
+            __threadfence();  // the partial is visible device-wide before this CTA counts itself in
+            last = atomicAdd(ft.counters + o, 1u) == p.split - 1 ? 1 : 0;
+        }
+        __syncthreads();
+        if (last) {
+            __threadfence();
+            const A total = cta_combine_partials<OP, T>(partial + size_t(o) * p.split, p.split);
+            if (threadIdx.x == 0) {
+                out[o] = narrow<T>(total);
+                ft.counters[o] = 0u;  // ready for the next launch on this stream
+            }
+            if (ft.peer) {
+                __syncthreads();  // this CTA's own store to `out` is visible to all its threads
+                exchange_publish<T>(ft.tail.peers, ft.tail.rank, 0, out, 1, narrow<T>(identity<OP, T>()));
+                if (ft.tail.combine_now) exchange_combine<OP, T>(ft.tail.peers, ft.tail.rank, 0, out, 1, ft.tail.wait_cycles);
+            }
+        }
+    }
 }
 
 // ---- rows: a team of 1..32 lanes per output -------------------------------------------------
@@ -193,27 +256,6 @@ __global__ void __launch_bounds__(RB) rows_team_kernel(const T *__restrict__ in,
     if (live && lane == 0) out[o] = narrow<T>(r);
 }
 
-// One output whose partials are many (a single output split over several waves of CTAs): the whole CTA adds them,
-// thread t taking partials t, t + RB, ..., then lanes, then warps, always in the same order.  The value is in thread 0.
-constexpr uint32_t FINISH_WIDE_FROM = 128;  // partials per output from which a CTA, not a warp, finishes an output
-template <int OP, typename T>
-__device__ __forceinline__ acc_t<T> cta_combine_partials(const acc_t<T> *__restrict__ p, uint32_t split) {
-    using A = acc_t<T>;
-    __shared__ A wide_part[RB / 32];
-    A r = identity<OP, T>();
-    for (uint32_t c = threadIdx.x; c < split; c += RB) r = combine<OP>(r, p[c]);
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) r = combine<OP>(r, shfl_down(r, d, 32));
-    __syncthreads();  // a previous output's wide_part has been read
-    if ((threadIdx.x & 31) == 0) wide_part[threadIdx.x >> 5] = r;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        r = wide_part[0];
-#pragma unroll
-        for (int w = 1; w < RB / 32; ++w) r = combine<OP>(r, wide_part[w]);
-    }
-    return r;
-}
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) rows_finish_wide_kernel(const acc_t<T> *__restrict__ partial, T *__restrict__ out, uint32_t split) {
     griddep_wait_cta();
@@ -357,12 +399,6 @@ __global__ void __launch_bounds__(RB) cols_finish_kernel(const acc_t<T> *__restr
 // peer's mailbox, wait for theirs, combine in rank order, write `out`.  One launch is both the tail
 // of the reduction and the all-reduce.
 static_assert(RB == COMM_THREADS, "the exchange is written for the reduce kernels' CTA size");
-struct PeerTail {
-    Peers peers;
-    int rank;
-    long long wait_cycles;
-    int combine_now;  // 0: the kernel ends after publishing; the combine runs later on the stream (dx_comm_allreduce_finish)
-};
 template <int OP, typename T>
 __global__ void __launch_bounds__(RB) rows_finish_peer_kernel(const acc_t<T> *__restrict__ partial, T *out, uint32_t nout, uint32_t split,
                                                               PeerTail tail) {
@@ -432,7 +468,7 @@ template <int OP, typename T> Residency residency_t() {
     std::call_once(once, [] {
         constexpr int FULL = 16 / sizeof(T);
         int n = 0;
-        r.rows_block = (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rows_block_kernel<OP, T, FULL>, RB, 0) == cudaSuccess && n > 0) ? n : 8;
+        r.rows_block = (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, rows_block_kernel<OP, T, FULL, true>, RB, 0) == cudaSuccess && n > 0) ? n : 8;
         r.cols = (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, cols_kernel<OP, T, FULL>, RB, 0) == cudaSuccess && n > 0) ? n : 6;
         cudaGetLastError();  // no device (a host-only build check): the defaults stand
     });
@@ -597,6 +633,29 @@ int make_plan(int dtype, const int64_t *shape, int ndim, const int32_t *dims, in
     return DX_OK;
 }
 
+// The counter bank of a stream on the current device (nullptr: all banks belong to other streams, or no device).
+unsigned int *fuse_counters(cudaStream_t st) {
+    static std::mutex mu;
+    static unsigned int *base[64] = {};
+    static std::vector<cudaStream_t> owners[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
+    std::lock_guard<std::mutex> lk(mu);
+    if (!base[dev]) {
+        void *sym = nullptr;
+        if (cudaGetSymbolAddress(&sym, g_reduce_counters) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        base[dev] = static_cast<unsigned int *>(sym);
+    }
+    auto &v = owners[dev];
+    size_t i = 0;
+    while (i < v.size() && v[i] != st) ++i;
+    if (i == v.size()) {
+        if (v.size() >= size_t(RED_BANKS)) return nullptr;
+        v.push_back(st);
+    }
+    return base[dev] + i * RED_COUNTERS;
+}
+
 template <int OP, typename T>
 int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cudaStream_t st, const PeerTail *tail = nullptr,
              bool *exchanged = nullptr) {
@@ -658,8 +717,25 @@ int run_plan(const Plan &pl, const T *in, T *out, void *ws, size_t ws_bytes, cud
         return check_launch("reduce(rows/team)");
     }
     if (pl.kind == PLAN_ROWS_BLOCK) {
-        if (vec == FULL) launch_pdl(rows_block_kernel<OP, T, FULL>, dim3(q.grid), dim3(RB), 0, st, in, out, partial, q.rows);
-        else launch_pdl(rows_block_kernel<OP, T, 1>, dim3(q.grid), dim3(RB), 0, st, in, out, partial, q.rows);
+        // a split reduction finishes itself when there are counters for it: few enough outputs, a bank for this stream,
+        // and — if the result goes on into the exchange — a single output
+        FuseTail ft = {};
+        bool fuse = false;
+        if (q.rows.split > 1 && q.rows.nout <= uint32_t(RED_COUNTERS) && (!tail || q.rows.nout == 1)) {
+            if (unsigned int *bank = fuse_counters(st)) {
+                fuse = true;
+                ft.counters = bank;
+                if (tail) { ft.peer = 1; ft.tail = *tail; }
+            }
+        }
+        if (fuse) {
+            if (vec == FULL) launch_pdl(rows_block_kernel<OP, T, FULL, true>, dim3(q.grid), dim3(RB), 0, st, in, out, partial, q.rows, ft);
+            else launch_pdl(rows_block_kernel<OP, T, 1, true>, dim3(q.grid), dim3(RB), 0, st, in, out, partial, q.rows, ft);
+            if (tail && exchanged) *exchanged = true;
+            return check_launch("reduce(rows/block, finishing itself)");
+        }
+        if (vec == FULL) launch_pdl(rows_block_kernel<OP, T, FULL, false>, dim3(q.grid), dim3(RB), 0, st, in, out, partial, q.rows, ft);
+        else launch_pdl(rows_block_kernel<OP, T, 1, false>, dim3(q.grid), dim3(RB), 0, st, in, out, partial, q.rows, ft);
         if (int e = check_launch("reduce(rows/block)")) return e;
         if (q.rows.split > 1) {
             const unsigned grid = (q.rows.nout + RB / 32 - 1) / (RB / 32);
