@@ -141,8 +141,26 @@ template <typename T, int N> __device__ __forceinline__ void st_stream(T *p, con
     }
 }
 // Cached load for data that is re-read (broadcast sources, gather tables).
+// (Read as ONE word of the pack's size: a pack of 1-byte elements copied as a struct came out as byte loads.)
 template <typename T, int N> __device__ __forceinline__ Pack<T, N> ld_cached(const T *p) {
-    return *reinterpret_cast<const Pack<T, N> *>(p);
+    constexpr int B = sizeof(T) * N;
+    Pack<T, N> r;
+    if constexpr (B == 16) {
+        const int4 t = *reinterpret_cast<const int4 *>(p);
+        r = *reinterpret_cast<const Pack<T, N> *>(&t);
+    } else if constexpr (B == 8) {
+        const int2 t = *reinterpret_cast<const int2 *>(p);
+        r = *reinterpret_cast<const Pack<T, N> *>(&t);
+    } else if constexpr (B == 4) {
+        const int t = *reinterpret_cast<const int *>(p);
+        r = *reinterpret_cast<const Pack<T, N> *>(&t);
+    } else if constexpr (B == 2) {
+        const short t = *reinterpret_cast<const short *>(p);
+        r = *reinterpret_cast<const Pack<T, N> *>(&t);
+    } else {
+        r = *reinterpret_cast<const Pack<T, N> *>(p);
+    }
+    return r;
 }
 
 // Makes `dev` the current device for a scope and puts the caller's device back afterwards.
