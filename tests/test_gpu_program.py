@@ -120,3 +120,46 @@ def test_stale_program_is_detected(ex):
     with pytest.raises(IRError, match="stale"):
         prog.run()
     prog.free()
+
+
+def test_k_split_matmul_and_self_finishing_reduction_inside_a_compiled_program(ex):
+    """A program whose matmul takes the K split over cooperating CTA pairs (a cooperative launch, counters inside the
+    library) and whose global sum finishes itself (last-CTA form): both must be capturable and replay to the same bits
+    as the lines run one by one."""
+    import ml_dtypes  # noqa: F401  (numpy bfloat16)
+    from deepx_b200 import _native as N
+    from deepx_b200.executor import Executor
+    M, K, Nn = 256, 8192, 1024
+    assert int(N.lib.dx_matmul_workspace_bytes(N.BF16, 1, M, Nn, K)) > 0, "this shape is meant to take the K-split path"
+    B = "tensor<bfloat16>"
+    program = "\n".join([
+        f"matmul({B}:a, {B}:b)->({B}:c)",
+        f"sum({B}:c, vector<int32>:[0 1], var<bool>:false)->({B}:s)",
+        f"mulscalar({B}:a, var<float32>:0.5)->({B}:a)",
+    ])
+    rng = np.random.default_rng(5)
+    a = (rng.standard_normal((M, K), dtype=np.float32) * 0.1).astype(ml_dtypes.bfloat16)
+    b = (rng.standard_normal((K, Nn), dtype=np.float32) * 0.1).astype(ml_dtypes.bfloat16)
+    ref = Executor(0)
+    for e in (ex, ref):
+        e.put("a", a)
+        e.put("b", b)
+        e.new("c", "bfloat16", (M, Nn))
+        e.new("s", "bfloat16", (1,))
+    for line in program.splitlines():   # once line by line on both: the executor's scratch has its size before the capture
+        ex.run(line)
+        ref.run(line)
+    prog = ex.compile(program)          # runs the program once more
+    for line in program.splitlines():
+        ref.run(line)
+    for _ in range(3):
+        prog.run()
+        for line in program.splitlines():
+            ref.run(line)
+    ex.sync()
+    ref.sync()
+    for name in ("a", "c", "s"):
+        assert np.array_equal(ex.download(name).view(np.uint16), ref.download(name).view(np.uint16)), name
+    assert np.abs(ex.download("c").astype(np.float32)).max() > 0
+    prog.free()
+    ref.close()
