@@ -186,17 +186,6 @@ __device__ __forceinline__ void grouped_tile_coords(int tile, int tiles_m, int t
 
 // ---- the way out: TMEM → registers → C ----------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// Untiled bulk copy shared -> global (both 16-byte aligned, size a multiple of 16), tracked by the thread's bulk group.
-__device__ __forceinline__ void bulk_store(void *dst, uint32_t src_smem, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src_smem), "r"(bytes) : "memory");
-}
-// All bulk copies this thread issued have been written (not merely read out of shared memory), and what the async
-// proxy wrote is ordered before this thread's later generic-proxy operations.
-__device__ __forceinline__ void bulk_store_drain() {
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    asm volatile("fence.proxy.async;" ::: "memory");
-}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
@@ -1113,7 +1102,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 struct PairWsParams {
     int M, N, K, batch;
     int tiles_m, tiles_n, k_blocks, kb_per_slice, ks;
-    int c_staged, tma_store;
+    int c_staged;
     int *status;
     float *partial;          // [tile][slice][half][128 rows × 256 columns in TMEM order]
     unsigned long long *counters;  // [tile][half]: grows by WSK_ROUND per launch
@@ -1312,23 +1301,11 @@ __global__ void __launch_bounds__(W_THREADS, 1)
 #pragma unroll
                 for (int j = 0; j < 32; ++j) r[j] = 0u;
             }
-            if (p.tma_store) {
-                // through shared memory and one 4 KiB bulk copy per block: the copy engine takes what the store path
-                // of the SM (about 32 bytes per clock) would be busy with
-                const uint32_t buf = smem_base + (warp * 4 + (n >> 1)) * 4096;  // the ring is drained; n counts this quarter's blocks
 #pragma unroll
-                for (int v = 0; v < 8; ++v) st_shared_v4(buf + (v * 32 + lane) * 16, r[4 * v + 0], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) bulk_store(mine + ((q * 8 + c) * 8) * 32, buf, 4096);
-            } else {
-#pragma unroll
-                for (int v = 0; v < 8; ++v)
-                    mine[((q * 8 + c) * 8 + v) * 32 + lane] =
-                        make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
-            }
+            for (int v = 0; v < 8; ++v)
+                mine[((q * 8 + c) * 8 + v) * 32 + lane] =
+                    make_float4(__uint_as_float(r[4 * v + 0]), __uint_as_float(r[4 * v + 1]), __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
         }
-        if (p.tma_store && lane == 0) bulk_store_drain();
     }
     tc_fence_before();
     __syncthreads();
@@ -2503,7 +2480,6 @@ int launch_pair_wsk(const T *A, const T *B, T *C, int64_t batch, int64_t M, int6
     p.ks = ks;
     p.kb_per_slice = (int)((k_blocks + ks - 1) / ks);
     p.c_staged = (staged_on && aligned_to(C, 16)) ? 1 : 0;
-    { const char *e = std::getenv("DX_WSK_TMA_STORE"); p.tma_store = (e && e[0] == '1') ? 1 : 0; }
     p.status = status;
     p.partial = static_cast<float *>(ws);
     p.counters = counters;
