@@ -1105,12 +1105,12 @@ struct PairWsParams {
     int c_staged;
     int *status;
     float *partial;          // [tile][slice][half][128 rows × 256 columns in TMEM order]
-    unsigned long long *counters;  // [tile][half]: grows by WSK_ROUND per launch
+    unsigned long long *counters;  // [tile][half]: grows by WSK_STEP per launch
 };
 constexpr int W_THREADS = 256;          // eight warps; warps 0 and 1 feed the main loop first, then all eight store and finish
 constexpr int WS_HALF_FLOATS = BM * BN;  // 32768 floats = 128 KiB per CTA and slice
 constexpr int GEMM_TIMEOUT_SLICES = 7;
-constexpr unsigned int WSK_ROUND = 840;  // divisible by every KS up to 8
+constexpr unsigned int WSK_STEP = 840;  // divisible by every KS up to 8
 constexpr int WSK_BANKS = 8;             // one set of counters per stream that launches this kernel
 __device__ unsigned long long g_wsk_counters[WSK_BANKS][512];
 
@@ -1212,12 +1212,12 @@ __global__ void __launch_bounds__(W_THREADS, 1)
     cluster_sync_all();  // the peer's barriers exist before anything signals them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
-    // The counter of this (tile, half) only ever grows, by WSK_ROUND per launch whatever KS is.  Read before this
-    // CTA has counted itself in, it lies in [base, base + WSK_ROUND) with base the value the last launch left, so the
+    // The counter of this (tile, half) only ever grows, by WSK_STEP per launch whatever KS is.  Read before this
+    // CTA has counted itself in, it lies in [base, base + WSK_STEP) with base the value the last launch left, so the
     // value to wait for is known now and the count-in itself needs no answer from L2.
     unsigned long long *arrived = p.counters + tile * 2 + half;
     unsigned long long target = 0;
-    if (threadIdx.x == 0) target = (ld_acquire_gpu(arrived) / WSK_ROUND + 1ull) * WSK_ROUND;
+    if (threadIdx.x == 0) target = (ld_acquire_gpu(arrived) / WSK_STEP + 1ull) * WSK_STEP;
     bool have = false;  // this CTA's accumulator is complete
 
     if (warp == 0) {
@@ -1313,7 +1313,7 @@ __global__ void __launch_bounds__(W_THREADS, 1)
         // The barrier orders every warp's stores before this release, and a release is cumulative: they are visible
         // device-wide before the count.  All KS pairs of the tile are resident (a cooperative launch) and none waits
         // before it has counted itself in, so the wait ends; it is bounded all the same.
-        red_release_add(arrived, WSK_ROUND / unsigned(p.ks));
+        red_release_add(arrived, WSK_STEP / unsigned(p.ks));
         const long long t0 = clock64();
         bool ok = true;
         while (ld_acquire_gpu(arrived) < target) {
@@ -2498,6 +2498,10 @@ int launch_pair_wsk(const T *A, const T *B, T *C, int64_t batch, int64_t M, int6
     cfg.attrs = attr;
     cfg.numAttrs = 2;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_wsk_kernel<T>, ma, mb, C, p);
+    if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorLaunchOutOfResources) {
+        cudaGetLastError();          // fewer SMs are free for a cooperative grid than the occupancy query saw (a profiler,
+        return DX_E_UNSUPPORTED;     // another context): the kernels without a K split take the call
+    }
     if (e != cudaSuccess) return fail(DX_E_CUDA, "matmul(tcgen05 pair, K split through the workspace): %s", cudaGetErrorString(e));
     return check_launch("matmul(tcgen05 pair, K split through the workspace)");
 }
