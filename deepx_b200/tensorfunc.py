@@ -228,14 +228,16 @@ def reduced_shape(shape: Sequence[int], dims: Sequence[int], keepdims: bool) -> 
     return out or [1]
 
 
-_workspace: dict[torch.device, torch.Tensor] = {}
+_workspace: dict[tuple, torch.Tensor] = {}
 
 
-def _get_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    ws = _workspace.get(device)
+def _get_workspace(device: torch.device, nbytes: int, floor: int = 1 << 20, what: str = "reduce") -> torch.Tensor:
+    """Scratch memory of (device, current stream, purpose): launches on different streams may overlap, so they must not share it."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream, what)
+    ws = _workspace.get(key)
     if ws is None or ws.numel() < nbytes:
-        ws = torch.empty(builtins.max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
-        _workspace[device] = ws
+        ws = torch.empty(builtins.max(int(nbytes), floor), dtype=torch.uint8, device=device)
+        _workspace[key] = ws
     return ws
 
 
@@ -391,9 +393,6 @@ def check_matmul_shape(a: Sequence[int], b: Sequence[int]) -> bool:
     return all(a[i] == b[i] for i in range(len(a) - 2))
 
 
-_matmul_workspace: dict[torch.device, torch.Tensor] = {}
-
-
 def matmul(A: torch.Tensor, B: torch.Tensor, Cc: torch.Tensor) -> None:
     _dev(A, B, Cc)
     _same_dtype(A, B, Cc)
@@ -407,10 +406,7 @@ def matmul(A: torch.Tensor, B: torch.Tensor, Cc: torch.Tensor) -> None:
         code = dtype_code(A)
         need = N.lib.dx_matmul_workspace_bytes(code, batch, M, Nn, K)  # > 0 for a few rows of tiles: K split through scratch memory
         if need:
-            ws = _matmul_workspace.get(A.device)
-            if ws is None or ws.numel() < need:
-                ws = torch.empty(builtins.max(int(need), 32 << 20), dtype=torch.uint8, device=A.device)
-                _matmul_workspace[A.device] = ws
+            ws = _get_workspace(A.device, need, 32 << 20, "matmul")
             N.check(N.lib.dx_matmul_ws(code, A.data_ptr(), B.data_ptr(), Cc.data_ptr(), batch, M, Nn, K, ws.data_ptr(), ws.numel(), _stream(A)))
         else:
             N.check(N.lib.dx_matmul(code, A.data_ptr(), B.data_ptr(), Cc.data_ptr(), batch, M, Nn, K, _stream(A)))

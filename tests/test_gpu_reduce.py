@@ -152,6 +152,31 @@ def test_deterministic(mods):
     assert_bit_exact(run(TF, O, "sum", a.reshape(1 << 10, 3 << 10), [0], False), first0, "repeat cols")
 
 
+def test_split_reduction_on_many_streams(mods):
+    """A reduction split over several CTAs per output finishes itself on counters inside the library, one bank per
+    stream; a stream beyond the banks takes the form with a finish kernel.  Ten streams at once, two shapes each (one
+    output split 4000-fold, 300 outputs split a few times): every result has the bits of the default stream's."""
+    TF, O = mods
+    rng = np.random.default_rng(21)
+    a = to_gpu(make(rng, "float32", (300, 1 << 19)))
+    want_all = torch.empty(1, dtype=torch.float32, device="cuda:0")
+    want_rows = torch.empty(300, dtype=torch.float32, device="cuda:0")
+    TF.sum(a, [0, 1], False, want_all)
+    TF.reducemax(a, [1], False, want_rows)
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(10)]
+    outs = [(torch.empty_like(want_all), torch.empty_like(want_rows)) for _ in streams]
+    for _ in range(3):
+        for st, (o_all, o_rows) in zip(streams, outs):
+            with torch.cuda.stream(st):
+                TF.sum(a, [0, 1], False, o_all)
+                TF.reducemax(a, [1], False, o_rows)
+    torch.cuda.synchronize()
+    for i, (o_all, o_rows) in enumerate(outs):
+        assert torch.equal(o_all, want_all) and torch.equal(o_rows, want_rows), f"stream {i}"
+    assert_bit_exact(to_np(want_rows), O.reducemax(to_np(a), [1], False), "row max")
+
+
 def test_config_reduce_suite(mods):
     """sum and max over the last axis and over axis 0 of float32 [8192,8192] ~ N(0,1);
     sum over axes (1,2) of int32 [64,1024,1024] in [-100,100] (bit-exact)."""
