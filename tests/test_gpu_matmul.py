@@ -454,3 +454,29 @@ def test_matmul_k_split_on_two_streams_at_once(mods):
     for A, B, alone, ws, st, outs, shape in jobs:
         for o in outs:
             assert torch.equal(o, alone), f"{shape}: a launch that overlapped another stream's differs from a launch alone"
+
+
+def test_matmul_k_split_more_streams_than_counter_banks(mods):
+    """The library keeps eight banks of K-split counters per device; a stream that finds none left gets the kernels
+    without a K split.  Twelve streams, each with its own workspace: every result within the bound of the float64
+    product, whichever kernel the stream got."""
+    TF, O, N = mods
+    M, Nn, K = 256, 1024, 8192
+    need = int(N.lib.dx_matmul_workspace_bytes(N.BF16, 1, M, Nn, K))
+    assert need > 0
+    rng = np.random.default_rng(78)
+    a, b = make(rng, "bfloat16", (M, K), -1.0, 1.0), make(rng, "bfloat16", (K, Nn), -1.0, 1.0)
+    A, B = to_gpu(a), to_gpu(b)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    scale = np.abs(a.astype(np.float64)) @ np.abs(b.astype(np.float64))
+    jobs = [(torch.cuda.Stream(), torch.empty(need, dtype=torch.uint8, device="cuda:0"), torch.empty(M, Nn, dtype=torch.bfloat16, device="cuda:0"))
+            for _ in range(12)]
+    torch.cuda.synchronize()
+    for _ in range(2):
+        for st, ws, out in jobs:
+            N.check(N.lib.dx_matmul_ws(N.BF16, A.data_ptr(), B.data_ptr(), out.data_ptr(), 1, M, Nn, K, ws.data_ptr(), ws.numel(), st.cuda_stream))
+    torch.cuda.synchronize()
+    N.check(N.lib.dx_matmul_status(None))
+    for i, (st, ws, out) in enumerate(jobs):
+        got = to_np(out).astype(np.float64)
+        assert (np.abs(got - ref) <= TOL["bfloat16"] * np.abs(ref) + 1e-6 * scale + 1e-300).all(), f"stream {i}"
